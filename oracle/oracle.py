@@ -1,0 +1,421 @@
+"""CPU oracle, Python side.  TEST INFRASTRUCTURE ONLY.
+
+ctypes wrappers over ``oracle/_ref/libannc_oracle.so`` (the plain-C restatement
+in ``annc_oracle.c``), numpy/OpenBLAS restatements of the GEMM custom calls, and
+a restatement of the ``kn4`` prepacked-weight layout.  Only ``tests/``, the smoke
+test and the ``cpu_baseline`` / ``--impl reference`` legs of ``bench.py`` may
+import this module; the product package never does.
+
+Reference citations are paths inside the ANNC project.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_ref", "libannc_oracle.so")
+_FLAGS_REF_PATH = os.path.join(_HERE, "_ref", "libannc_flags_ref.so")
+
+i64p = C.POINTER(C.c_int64)
+i32p = C.POINTER(C.c_int32)
+f32p = C.POINTER(C.c_float)
+u8p = C.POINTER(C.c_uint8)
+
+
+def build(reference_root: str | None = "/root/reference") -> None:
+    """Compile the C oracle (and the reference's flag parser where its tree exists)."""
+    targets = ["all"]
+    if reference_root and os.path.isdir(reference_root):
+        targets.append("ref")
+    subprocess.run(["make", "-C", _HERE, f"REFERENCE_ROOT={reference_root}"] + targets,
+                   check=True, stdout=subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.oracle_segment_batch.restype = C.c_int64
+        _lib.oracle_sparse_segment_reduce_nonzero.restype = C.c_int64
+        _lib.oracle_fused_gather.restype = C.c_int64
+    return _lib
+
+
+def _p(a: np.ndarray, t):
+    return a.ctypes.data_as(t)
+
+
+def _c(a, dtype) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+# ---------------------------------------------------------------- embedding family
+
+def segment_batch(slice_input: np.ndarray, col: int) -> int:
+    s = _c(slice_input, np.int64)
+    return int(lib().oracle_segment_batch(_p(s, i64p), C.c_int64(s.shape[0]),
+                                          C.c_int64(s.shape[1]), C.c_int32(col)))
+
+
+def sparse_segment_reduce(data, indices, slice_input, begin, begin_1, combiner
+                          ) -> Tuple[np.ndarray, np.int32]:
+    """KPFusedSparseSegmentReduce
+    (annc/tensorflow/kernels/embedding_fused_sparse_segment_reduce.cc:38-152)."""
+    data = _c(data, np.float32)
+    s = _c(slice_input, np.int64)
+    idx = np.ascontiguousarray(indices)
+    idx64 = idx.dtype == np.int64
+    if not idx64:
+        idx = idx.astype(np.int32)
+    col = int(begin[1])
+    batch = segment_batch(s, col)
+    out = np.empty((batch, data.shape[1]), np.float32)
+    so = C.c_int32(0)
+    lib().oracle_sparse_segment_reduce(
+        _p(data, f32p), C.c_int64(data.shape[1]), idx.ctypes.data_as(C.c_void_p),
+        C.c_int(int(idx64)), C.c_int64(idx.shape[0]), _p(s, i64p), C.c_int64(s.shape[1]),
+        C.c_int32(col), C.c_int32(int(begin_1[0])), C.c_int(combiner), _p(out, f32p),
+        C.c_int64(batch), C.byref(so))
+    return out, np.int32(so.value)
+
+
+def sparse_segment_reduce_nonzero(data, indices, slice_input, begin, combiner):
+    """KPFusedSparseSegmentReduceNonzero
+    (annc/tensorflow/kernels/embedding_fused_sparse_segment_reduce_nonzero.cc:39-374)."""
+    data = _c(data, np.float32)
+    rank = data.ndim
+    dim = data.shape[1] if rank == 2 else 1
+    s = _c(slice_input, np.int64)
+    idx = np.ascontiguousarray(indices)
+    idx64 = idx.dtype == np.int64
+    if not idx64:
+        idx = idx.astype(np.int32)
+    nnz = idx.shape[0]
+    cap = max(1, nnz * dim)
+    out_shape = np.zeros(rank, np.int32)
+    out_idx = np.zeros((cap, rank), np.int32)
+    out_val = np.zeros(cap, np.float32)
+    nz = lib().oracle_sparse_segment_reduce_nonzero(
+        _p(data, f32p), C.c_int(rank), C.c_int64(dim), idx.ctypes.data_as(C.c_void_p),
+        C.c_int(int(idx64)), C.c_int64(nnz), _p(s, i64p), C.c_int64(s.shape[1]),
+        C.c_int32(int(begin[1])), C.c_int(combiner), _p(out_shape, i32p), _p(out_idx, i32p),
+        _p(out_val, f32p))
+    return out_shape, out_idx[:nz].copy(), out_val[:nz].copy()
+
+
+def fused_gather(data, keys, begin):
+    """KPFusedGather (annc/tensorflow/kernels/embedding_fused_gather.cc:26-86).
+    Returns (unique_keys, inverse_indices, rows) or raises ValueError with the
+    reference's message."""
+    data = _c(data, np.float32)
+    keys = _c(keys, np.int64)
+    nnz, ncols = keys.shape
+    uniq = np.zeros(max(nnz, 1), np.int64)
+    inv = np.zeros(max(nnz, 1), np.int32)
+    rows = np.zeros((max(nnz, 1), data.shape[1]), np.float32)
+    nu = lib().oracle_fused_gather(
+        _p(data, f32p), C.c_int64(data.shape[0]), C.c_int64(data.shape[1]), _p(keys, i64p),
+        C.c_int64(nnz), C.c_int64(ncols), C.c_int32(int(begin[1])), _p(uniq, i64p),
+        _p(inv, i32p), _p(rows, f32p))
+    if nu < 0:
+        raise ValueError("idx out of table range")
+    return uniq[:nu].copy(), inv[:nnz].copy(), rows[:nu].copy()
+
+
+def sparse_dynamic_stitch(x, tables: Sequence[np.ndarray]) -> np.ndarray:
+    """KPFusedSparseDynamicStitch
+    (annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:31-83)."""
+    x = _c(x, np.int64).reshape(-1)
+    tabs = [_c(t, np.float32) for t in tables]
+    dim = tabs[0].shape[1]
+    ptrs = (f32p * len(tabs))(*[_p(t, f32p) for t in tabs])
+    rows = np.array([t.shape[0] for t in tabs], np.int64)
+    out = np.zeros((x.shape[0], dim), np.float32)
+    rc = lib().oracle_sparse_dynamic_stitch(_p(x, i64p), C.c_int64(x.shape[0]), ptrs,
+                                            _p(rows, i64p), C.c_int(len(tabs)),
+                                            C.c_int64(dim), _p(out, f32p))
+    if rc != 0:
+        raise ValueError("row_id out of range.")
+    return out
+
+
+def hash_bucket(hashes, num_buckets) -> np.ndarray:
+    """uint64 fingerprint % num_buckets
+    (python/tensorflow/kernels/fused_embedding_with_hash_bucket.cc:63-64)."""
+    h = _c(hashes, np.uint64)
+    out = np.zeros(h.shape, np.int64)
+    lib().oracle_hash_bucket(h.ctypes.data_as(C.POINTER(C.c_uint64)), C.c_int64(h.size),
+                             C.c_int64(num_buckets), _p(out, i64p))
+    return out
+
+
+def embedding_with_hash_bucket(hashes, empty, weight, num_buckets, bounded=False):
+    """KPFusedEmbeddingWithHashBucket (fused_embedding_with_hash_bucket.cc:29-77); with
+    ``bounded`` the Dnn/Linear/RecEmbeddingV2 variant that leaves out-of-table buckets
+    zero (fused_dnn_embedding_with_hash_bucket.cc:32-47)."""
+    h = _c(hashes, np.uint64)
+    w = _c(weight, np.float32)
+    e = None if empty is None else _c(empty, np.uint8)
+    out = np.empty((h.shape[0], w.shape[1]), np.float32)
+    hp = h.ctypes.data_as(C.POINTER(C.c_uint64))
+    ep = _p(e, u8p) if e is not None else None
+    if bounded:
+        lib().oracle_dnn_embedding_with_hash_bucket(
+            hp, ep, C.c_int64(h.shape[0]), _p(w, f32p), C.c_int64(w.shape[0]),
+            C.c_int64(w.shape[1]), C.c_int64(num_buckets), _p(out, f32p))
+    else:
+        lib().oracle_embedding_with_hash_bucket(
+            hp, ep, C.c_int64(h.shape[0]), _p(w, f32p), C.c_int64(w.shape[1]),
+            C.c_int64(num_buckets), _p(out, f32p))
+    return out
+
+
+def sparse_embedding(hashes, empty, num_buckets):
+    """KPFusedSparseEmbedding / RecEmbeddingV1
+    (python/tensorflow/kernels/fused_sparse_embedding.cc:25-80)."""
+    h = _c(hashes, np.uint64)
+    e = _c(empty, np.uint8)
+    n = h.shape[0]
+    idx = np.zeros((n, 2), np.int64)
+    val = np.zeros(n, np.int64)
+    emp = np.zeros(n, np.uint8)
+    shp = np.zeros(2, np.int64)
+    ni, nv = C.c_int64(0), C.c_int64(0)
+    lib().oracle_sparse_embedding(h.ctypes.data_as(C.POINTER(C.c_uint64)), _p(e, u8p),
+                                  C.c_int64(n), C.c_int64(num_buckets), _p(idx, i64p),
+                                  _p(val, i64p), _p(emp, u8p), _p(shp, i64p),
+                                  C.byref(ni), C.byref(nv))
+    return idx[:ni.value], val[:nv.value], emp[:nv.value].astype(bool), shp
+
+
+def sparse_embedding2(ids, table, lo, hi, dflt) -> np.ndarray:
+    """sparse_embedding2 fusion (annc/service/cpu/graph_opt.cc:8-41)."""
+    ids = _c(ids, np.int64).reshape(-1)
+    t = _c(table, np.float32)
+    out = np.empty((ids.shape[0], t.shape[1]), np.float32)
+    lib().oracle_sparse_embedding2(_p(ids, i64p), C.c_int64(ids.shape[0]), _p(t, f32p),
+                                   C.c_int64(t.shape[1]), C.c_int64(lo), C.c_int64(hi),
+                                   C.c_int64(dflt), _p(out, f32p))
+    return out
+
+
+def pooling(arg, mul_out, slice_starts, slice_limits) -> np.ndarray:
+    """__pooling (annc/service/cpu/graph_opt.cc:131-176)."""
+    arg = _c(arg, np.int64)
+    mo = _c(mul_out, np.float32)
+    m, k = arg.shape
+    n = mo.shape[2]
+    out = np.empty((m, n), np.float32)
+    ss = _c(slice_starts, np.int64)
+    sl = _c(slice_limits, np.int64)
+    a_info = np.array([m, k, 1, 0], np.int64)
+    m_info = np.array([m, k, n, 2, 1, 0], np.int64)
+    lib().oracle_pooling(_p(out, f32p), _p(arg, i64p), _p(mo, f32p), _p(ss, i64p),
+                         _p(sl, i64p), _p(a_info, i64p), _p(m_info, i64p))
+    return out
+
+
+def softmax(x) -> np.ndarray:
+    """__xla_cpu_runtime_XnnPackSoftMaxND (annc/service/cpu/xla/xnnpack_ops.cc:30-74)."""
+    x = _c(x, np.float32)
+    ch = x.shape[-1]
+    out = np.empty_like(x)
+    lib().oracle_softmax(_p(x, f32p), _p(out, f32p), C.c_int64(x.size // ch), C.c_int64(ch))
+    return out
+
+
+def reduce_mean(value, m, n) -> np.ndarray:
+    """__reduce_mean (annc/service/cpu/reduce_rewriter.cc:31-46)."""
+    v = _c(value, np.float32)
+    out = np.empty(n, np.float32)
+    lib().oracle_reduce_mean(_p(out, f32p), _p(v, f32p), C.c_int64(m), C.c_int64(n))
+    return out
+
+
+def argmax3d(invals, inidxs, init_value, init_idx):
+    """ArgMax3D (annc/service/cpu/xla/kernel_selector.cc:317-394)."""
+    v = _c(invals, np.float32)
+    ix = _c(inidxs, np.int32)
+    n = v.shape[-1]
+    rows = v.size // n
+    ov = np.empty(v.shape[:-1], np.float32)
+    oi = np.empty(v.shape[:-1], np.int32)
+    lib().oracle_argmax3d(C.c_int64(rows), C.c_int64(n), _p(v, f32p), _p(ix, i32p),
+                          C.c_float(init_value), C.c_int32(init_idx), _p(ov, f32p), _p(oi, i32p))
+    return ov, oi
+
+
+# ---------------------------------------------------------------- GEMM family
+
+def sgemm(trA, trB, A, B, M, N, K, alpha=1.0, beta=0.0, Cin=None, blas=True) -> np.ndarray:
+    """Row-major sgemm with the leading dimensions of
+    annc/service/cpu/xla/kernel_selector.cc:31-43.  ``blas=True`` uses numpy's
+    OpenBLAS sgemm (the library family the reference calls), else the scalar C loop."""
+    A = _c(A, np.float32).reshape((M, K) if not trA else (K, M))
+    B = _c(B, np.float32).reshape((K, N) if not trB else (N, K))
+    if blas:
+        a = A.T if trA else A
+        b = B.T if trB else B
+        r = np.float32(alpha) * (a @ b)
+        if beta != 0.0:
+            r = r + np.float32(beta) * _c(Cin, np.float32).reshape(M, N)
+        return r.astype(np.float32)
+    out = np.zeros((M, N), np.float32) if Cin is None else _c(Cin, np.float32).reshape(M, N).copy()
+    lib().oracle_sgemm(C.c_int(int(trA)), C.c_int(int(trB)), C.c_int64(M), C.c_int64(N),
+                       C.c_int64(K), C.c_float(alpha), _p(A, f32p), _p(B, f32p),
+                       C.c_float(beta), _p(out, f32p))
+    return out
+
+
+def matmul(A, B):
+    """__matmul (annc/service/cpu/gemm_rewriter.cc:161-185)."""
+    return (_c(A, np.float32) @ _c(B, np.float32)).astype(np.float32)
+
+
+def batch_matmul(A, B):
+    """__batch_matmul (annc/service/cpu/gemm_rewriter.cc:187-216)."""
+    return np.matmul(_c(A, np.float32), _c(B, np.float32)).astype(np.float32)
+
+
+def matmul_add(addend, A, B):
+    """__matmul_add (annc/service/cpu/gemm_rewriter.cc:218-247): memcpy + sgemm(beta=1)."""
+    return (_c(addend, np.float32) + _c(A, np.float32) @ _c(B, np.float32)).astype(np.float32)
+
+
+def matmul_add_relu(addend, A, B):
+    """__matmul_add_relu (annc/service/cpu/gemm_rewriter.cc:249-281); the max operand is
+    ignored by the reference, a literal 0 is used (:279)."""
+    return np.maximum(matmul_add(addend, A, B), np.float32(0.0))
+
+
+def sgemv(trA, A, X, M, N, alpha=1.0, beta=0.0, Y=None):
+    """KernelSelectorGEMV (annc/service/cpu/xla/kernel_selector.cc:168-178)."""
+    A = _c(A, np.float32).reshape(M, N)
+    X = _c(X, np.float32)
+    out = np.zeros(N if trA else M, np.float32) if Y is None else _c(Y, np.float32).copy()
+    lib().oracle_sgemv(C.c_int(int(trA)), C.c_int64(M), C.c_int64(N), C.c_float(alpha),
+                       _p(A, f32p), _p(X, f32p), C.c_float(beta), _p(out, f32p))
+    return out
+
+
+def batch_matmul_add_sigmoid(lhs, rhs, bias) -> np.ndarray:
+    """KPFusedBatchMatMulAddSigmoid, generic path
+    (annc/tensorflow/kernels/fused_batchmatmul_add_sigmoid.cc:216-255)."""
+    lhs = _c(lhs, np.float32)
+    rhs = _c(rhs, np.float32)
+    bias = _c(bias, np.float32)
+    b, m, k = lhs.shape
+    n = rhs.shape[-1]
+    bd = np.ones(3, np.int64)
+    for i, d in enumerate(bias.shape):
+        bd[3 - bias.ndim + i] = d
+    out = np.empty((b, m, n), np.float32)
+    lib().oracle_batch_matmul_add_sigmoid(_p(lhs, f32p), _p(rhs, f32p), _p(bias, f32p),
+                                          _p(bd, i64p), C.c_int64(b), C.c_int64(m),
+                                          C.c_int64(k), C.c_int64(n), C.c_int(int(rhs.ndim == 3)),
+                                          _p(out, f32p))
+    return out
+
+
+# ---------------------------------------------------------------- kn4 prepacked layout
+
+def _split_axis(dim: int, tile: int, vec: int) -> List[Tuple[int, int]]:
+    """Chunk boundaries of one axis (python/annc/optimize/data_pack.py:43-92): chunks of
+    ``tile``; when ``dim`` is not a multiple the last two chunks share the remainder,
+    the first of them rounded to a multiple of ``vec``."""
+    if dim < tile:
+        return [(0, dim)]
+    num = dim // tile + (1 if dim % tile else 0)
+    out = []
+    for i in range(num):
+        start, end = i * tile, (i + 1) * tile
+        if dim % tile:
+            if i == num - 2 or i == num - 1:
+                res = dim - (num - 2) * tile
+                first = (res // 2) // vec * vec
+                if res - first > first + 1:
+                    first += vec
+                if i == num - 2:
+                    end = start + first
+                else:
+                    start, end = dim - res + first, dim
+        out.append((start, end))
+    return out
+
+
+def _panel_widths(n: int, vec: int) -> List[int]:
+    """Panel widths inside one block (data_pack.py:129-149)."""
+    w = [vec] * (n // vec)
+    rest = n % vec
+    small = 4 if vec == 12 else vec // 2
+    while small:
+        if vec == 12:
+            while rest >= small:
+                w.append(small)
+                rest -= small
+        elif rest >= small:
+            w.append(small)
+            rest -= small
+        small //= 2
+    return w
+
+
+def kn4_offsets(K: int, N: int, vec: int = 12, k_tile: int = 352, n_tile: int = 128) -> np.ndarray:
+    """int64[K,N] map: position of B[k,n] inside the kn4-packed buffer written by
+    ``FormageChange(12).run(B, kn, kn4, [(0,352),(1,128)])``
+    (python/annc/optimize/constant_folding.py:77-88, data_pack.py:36-41,118-127)."""
+    off = np.empty((K, N), np.int64)
+    pos = 0
+    for k0, k1 in _split_axis(K, k_tile, vec):
+        for n0, n1 in _split_axis(N, n_tile, vec):
+            nloc = n0
+            for w in _panel_widths(n1 - n0, vec):
+                cnt = (k1 - k0) * w
+                off[k0:k1, nloc:nloc + w] = pos + np.arange(cnt, dtype=np.int64).reshape(k1 - k0, w)
+                pos += cnt
+                nloc += w
+    assert pos == K * N
+    return off
+
+
+def kn4_pack(B: np.ndarray) -> np.ndarray:
+    B = _c(B, np.float32)
+    out = np.empty(B.size, np.float32)
+    out[kn4_offsets(*B.shape).reshape(-1)] = B.reshape(-1)
+    return out.reshape(B.shape)
+
+
+def kn4_unpack(packed: np.ndarray, K: int, N: int) -> np.ndarray:
+    return _c(packed, np.float32).reshape(-1)[kn4_offsets(K, N)]
+
+
+def layout_matmul(A, Bpacked):
+    """__layout_matmul (annc/service/cpu/gemm_rewriter.cc:136-159): C = A . unpack(Bpacked)."""
+    A = _c(A, np.float32)
+    K = A.shape[1]
+    N = Bpacked.size // K
+    return (A @ kn4_unpack(Bpacked, K, N)).astype(np.float32)
+
+
+# ---------------------------------------------------------------- ANNC_FLAGS (real reference)
+
+def flags_ref_available() -> bool:
+    return os.path.exists(_FLAGS_REF_PATH)
+
+
+def flag_enabled_ref(flags_env: str | None, name: str) -> bool:
+    """Runs the reference's own parser (annc/service/cpu/annc_flags.cc) compiled into
+    oracle/_ref/libannc_flags_ref.so."""
+    l = C.CDLL(_FLAGS_REF_PATH)
+    return bool(l.annc_ref_flag_enabled(None if flags_env is None else flags_env.encode(),
+                                        name.encode()))
