@@ -1,0 +1,94 @@
+// Shared host-side plumbing of libannc_b200: status + message, the calling
+// thread's stream, host/device pointer classification, the per-thread staging
+// arena and the registry of constants uploaded once.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <vector>
+
+#include "annc_b200.h"
+
+namespace annc {
+
+// Records `code` and a printf-style message for annc_last_error(); returns code.
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define ANNC_CUDA(call)                                        \
+  do {                                                         \
+    cudaError_t annc_e_ = (call);                              \
+    if (annc_e_ != cudaSuccess) return ::annc::cuda_fail(annc_e_, #call); \
+  } while (0)
+
+#define ANNC_TRY(call)                     \
+  do {                                     \
+    int annc_rc_ = (call);                 \
+    if (annc_rc_ != ANNC_OK) return annc_rc_; \
+  } while (0)
+
+// OP_REQUIRES counterpart: the message is the reference's text.
+#define ANNC_REQUIRE(cond, code, msg) \
+  do {                                \
+    if (!(cond)) return ::annc::fail(code, "%s", msg); \
+  } while (0)
+
+cudaStream_t current_stream();
+// Events set with annc_embed_bag_set_timing_events on this thread (may be null).
+void timing_events(cudaEvent_t* start, cudaEvent_t* stop);
+
+inline int64_t numel(const annc_tensor& t) {
+  int64_t n = 1;
+  for (int i = 0; i < t.rank; ++i) n *= t.dims[i];
+  return n;
+}
+size_t dtype_size(int32_t dtype);
+
+// One entry-point invocation.  in()/out() turn caller pointers (host or device)
+// into device pointers, staging host memory through the thread's arena;
+// finish() copies staged outputs back and, if anything was staged, waits.
+class Call {
+ public:
+  Call();
+  ~Call();
+  int status() const { return status_; }
+  cudaStream_t stream() const { return stream_; }
+
+  // Device view of `bytes` bytes at p (uploads when p is host memory and not a
+  // registered constant).  nullptr on failure (status() tells why) or when p is null.
+  const void* in(const void* p, size_t bytes);
+  template <typename T>
+  const T* in(const T* p, size_t count) {
+    return static_cast<const T*>(in(static_cast<const void*>(p), count * sizeof(T)));
+  }
+  // Device buffer standing for output p; host outputs are copied back in finish().
+  // `preload` uploads the current host contents first (for beta != 0).
+  void* out(void* p, size_t bytes, bool preload = false);
+  template <typename T>
+  T* out(T* p, size_t count, bool preload = false) {
+    return static_cast<T*>(out(static_cast<void*>(p), count * sizeof(T), preload));
+  }
+  // Device scratch valid until finish().
+  void* scratch(size_t bytes);
+  // Small host read of possibly-device memory (synchronous).
+  int read_host(const void* p, size_t bytes, void* dst);
+  // True when p is device (or managed) memory.
+  bool is_device(const void* p);
+
+  int finish();
+
+ private:
+  struct Pending {
+    void* host;
+    void* dev;
+    size_t bytes;
+  };
+  cudaStream_t stream_;
+  int status_ = ANNC_OK;
+  bool staged_ = false;
+  std::vector<Pending> pending_;
+};
+
+}  // namespace annc

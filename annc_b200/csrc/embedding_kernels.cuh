@@ -1,0 +1,576 @@
+// Device kernels of the embedding path: segment prepass, bag (gather + segment
+// reduce, with the fused uint64 hash-bucket modulo), the atomic route for
+// unsorted segment ids, single-row gathers, and the helpers of the
+// unique / non-zero ops.  HBM-bound: every table row is read once with 16-byte
+// loads, every output row is written once.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace annc {
+namespace emb {
+
+constexpr int kMaxTables = 64;          // tables per grouped launch
+constexpr int kErrRow = 1;              // row index outside its table
+constexpr int kErrSegment = 2;          // segment id outside [0, batch)
+
+// Head of the bag workspace (256 bytes), then int32 offsets[num_tables][batch + 1].
+struct BagHeader {
+  int err_bits;
+  int pad[3];
+  int unsorted[kMaxTables];  // per table: segment ids were seen to decrease
+};
+static_assert(sizeof(BagHeader) <= 512, "header layout");
+constexpr size_t kHeaderBytes = 512;
+
+struct BagTableDev {
+  const float* table;
+  const void* ids;
+  const int64_t* seg;  // slice_input
+  float* out;
+  long long rows;
+  unsigned long long num_buckets;
+  long long nnz;
+};
+
+struct BagParams {
+  BagTableDev t[kMaxTables];
+  int num_tables;
+  int id_kind;  // 0 i32 rows, 1 i64 rows, 2 u64 fingerprints
+  int combiner;
+  int col;
+  long long ncols;
+  long long batch;
+  long long dim;
+  long long out_stride;
+};
+
+// ---- prepass: CSR offsets from the (sorted) segment column --------------------
+// Thread i in [0, nnz] looks at the boundary between lookups i-1 and i and writes
+// offsets[s] = i for every segment s in (seg[i-1], seg[i]] (empty bags included),
+// with virtual seg[-1] = -1 and seg[nnz] = batch.  A decrease marks the table
+// unsorted; ids outside [0, batch) set kErrSegment.
+__global__ void bag_prepass_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int t = blockIdx.y;
+  const BagTableDev& T = p.t[t];
+  int* off = offsets + (long long)t * (p.batch + 1);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i <= T.nnz; i += stride) {
+    long long prev = (i == 0) ? -1 : T.seg[(i - 1) * p.ncols + p.col];
+    long long cur = (i == T.nnz) ? p.batch : T.seg[i * p.ncols + p.col];
+    if (i < T.nnz && (cur < 0 || cur >= p.batch)) {
+      atomicOr(&hdr->err_bits, kErrSegment);
+      cur = cur < 0 ? 0 : p.batch;
+    }
+    if (prev < -1) prev = -1;
+    if (prev > p.batch) prev = p.batch;
+    if (cur < prev) {
+      if (i < T.nnz) hdr->unsorted[t] = 1;
+      continue;
+    }
+    for (long long s = prev + 1; s <= cur; ++s) off[s] = (int)i;
+  }
+}
+
+__device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, long long i,
+                                                 unsigned long long num_buckets) {
+  if (id_kind == 0) return (long long)((const int*)ids)[i];
+  if (id_kind == 1) return ((const long long*)ids)[i];
+  return (long long)(((const unsigned long long*)ids)[i] % num_buckets);
+}
+
+__device__ __forceinline__ float4 ldg4(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ void add4(float4& a, const float4& b) {
+  a.x = __fadd_rn(a.x, b.x);
+  a.y = __fadd_rn(a.y, b.y);
+  a.z = __fadd_rn(a.z, b.z);
+  a.w = __fadd_rn(a.w, b.w);
+}
+
+// ---- bag kernel: LANES lanes own one bag; each lane owns VPL float4 columns -----
+// Rows are added in lookup order into a zero accumulator, the order of the
+// reference's scalar loop, so sums are bit-identical for sorted input.  Four
+// row loads are in flight per group.  For an unsorted table the group writes the
+// zero row and clears the bag's counter; the scatter kernels then do the work.
+template <int LANES, int VPL>
+__global__ void __launch_bounds__(256)
+bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  constexpr int GROUPS_PER_WARP = 32 / LANES;
+  const int lane_in_warp = threadIdx.x & 31;
+  const int lane = lane_in_warp % LANES;
+  const unsigned gmask =
+      (LANES == 32) ? 0xffffffffu : (((1u << LANES) - 1u) << ((lane_in_warp / LANES) * LANES));
+  const long long group =
+      ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GROUPS_PER_WARP +
+      lane_in_warp / LANES;
+  const long long total = (long long)p.num_tables * p.batch;
+  if (group >= total) return;
+  const int t = (int)(group / p.batch);
+  const long long s = group - (long long)t * p.batch;
+  const BagTableDev& T = p.t[t];
+  int* off = offsets + (long long)t * (p.batch + 1);
+  float* orow = T.out + s * p.out_stride;
+
+  float4 acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  if (hdr->unsorted[t]) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+      *reinterpret_cast<float4*>(orow + (v * LANES + lane) * 4) = acc[v];
+    __syncwarp(gmask);
+    if (lane == 0) off[s] = 0;  // becomes the bag's lookup counter
+    return;
+  }
+
+  const int start = off[s], end = off[s + 1];
+  for (int base = start; base < end; base += LANES) {
+    long long my = -1;
+    if (base + lane < end) {
+      my = load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets);
+      if (my < 0 || my >= T.rows) {
+        atomicOr(&hdr->err_bits, kErrRow);
+        my = -1;
+      }
+    }
+    const int n = min(LANES, end - base);
+    for (int j = 0; j < n; j += 4) {
+      long long r[4];
+      float4 v[4][VPL];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        r[q] = __shfl_sync(gmask, my, (j + q) % LANES, LANES);
+        if (j + q >= n) r[q] = -1;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (r[q] >= 0) {
+          const float* src = T.table + r[q] * p.dim;
+#pragma unroll
+          for (int w = 0; w < VPL; ++w) v[q][w] = ldg4(src + (w * LANES + lane) * 4);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (r[q] >= 0) {
+#pragma unroll
+          for (int w = 0; w < VPL; ++w) add4(acc[w], v[q][w]);
+        }
+      }
+    }
+  }
+  if (p.combiner == 1 && end > start) {
+    const float inv = __fdiv_rn(1.0f, (float)(end - start));
+#pragma unroll
+    for (int w = 0; w < VPL; ++w) {
+      acc[w].x = __fmul_rn(acc[w].x, inv);
+      acc[w].y = __fmul_rn(acc[w].y, inv);
+      acc[w].z = __fmul_rn(acc[w].z, inv);
+      acc[w].w = __fmul_rn(acc[w].w, inv);
+    }
+  }
+#pragma unroll
+  for (int w = 0; w < VPL; ++w)
+    *reinterpret_cast<float4*>(orow + (w * LANES + lane) * 4) = acc[w];
+}
+
+// Any dim (not a multiple of 4, or unaligned tables): one warp per bag, lanes
+// stride over the columns; same summation order.
+__global__ void __launch_bounds__(256)
+bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int lane = threadIdx.x & 31;
+  const long long group = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)p.num_tables * p.batch;
+  if (group >= total) return;
+  const int t = (int)(group / p.batch);
+  const long long s = group - (long long)t * p.batch;
+  const BagTableDev& T = p.t[t];
+  int* off = offsets + (long long)t * (p.batch + 1);
+  float* orow = T.out + s * p.out_stride;
+  if (hdr->unsorted[t]) {
+    for (long long c = lane; c < p.dim; c += 32) orow[c] = 0.f;
+    __syncwarp();
+    if (lane == 0) off[s] = 0;
+    return;
+  }
+  const int start = off[s], end = off[s + 1];
+  const float inv = (p.combiner == 1 && end > start) ? __fdiv_rn(1.0f, (float)(end - start)) : 1.0f;
+  for (long long c0 = 0; c0 < p.dim; c0 += 32) {
+    const long long c = c0 + lane;
+    float acc = 0.f;
+    for (int i = start; i < end; ++i) {
+      long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
+      if (r < 0 || r >= T.rows) {
+        if (lane == 0 && c0 == 0) atomicOr(&hdr->err_bits, kErrRow);
+        continue;
+      }
+      if (c < p.dim) acc = __fadd_rn(acc, __ldg(T.table + r * p.dim + c));
+    }
+    if (c < p.dim) orow[c] = (p.combiner == 1 && end > start) ? __fmul_rn(acc, inv) : acc;
+  }
+}
+
+// ---- unsorted route: atomic scatter (sum order not defined; within 1e-5 rel) ----
+__global__ void __launch_bounds__(256)
+bag_scatter_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int t = blockIdx.y;
+  if (!hdr->unsorted[t]) return;
+  const BagTableDev& T = p.t[t];
+  int* counts = offsets + (long long)t * (p.batch + 1);
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < T.nnz;
+       i += warps) {
+    long long seg = T.seg[i * p.ncols + p.col];
+    long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
+    if (seg < 0 || seg >= p.batch) continue;  // flagged by the prepass
+    if (r < 0 || r >= T.rows) {
+      if (lane == 0) atomicOr(&hdr->err_bits, kErrRow);
+      continue;
+    }
+    if (lane == 0) atomicAdd(&counts[seg], 1);
+    float* orow = T.out + seg * p.out_stride;
+    for (long long c = lane; c < p.dim; c += 32) atomicAdd(orow + c, __ldg(T.table + r * p.dim + c));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bag_scatter_mean_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int t = blockIdx.y;
+  if (!hdr->unsorted[t]) return;
+  const BagTableDev& T = p.t[t];
+  const int* counts = offsets + (long long)t * (p.batch + 1);
+  const long long total = p.batch * p.dim;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long s = e / p.dim, c = e - s * p.dim;
+    const int n = counts[s];
+    if (n > 0) {
+      float* q = T.out + s * p.out_stride + c;
+      *q = __fmul_rn(*q, __fdiv_rn(1.0f, (float)n));
+    }
+  }
+}
+
+// ---- max segment id (+1 = batch of the reference) ------------------------------
+__global__ void seg_max_kernel(const int64_t* seg, long long nnz, long long ncols, int col,
+                               long long* out_max) {
+  long long m = 0;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += stride) {
+    long long v = seg[i * ncols + col];
+    m = v > m ? v : m;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    long long w = __shfl_xor_sync(0xffffffffu, m, o);
+    m = w > m ? w : m;
+  }
+  if ((threadIdx.x & 31) == 0 && m > 0) atomicMax(out_max, m);
+}
+
+// ---- single-row gathers ---------------------------------------------------------
+// out[i,:] = skip(i) ? 0 : table[row(i),:]; one warp per output row.
+// mode 0: KPFusedEmbeddingWithHashBucket (row = fp % num_buckets, empty -> zeros)
+// mode 1: bounded variant (row outside [0, rows) -> zeros)
+// mode 2: sparse_embedding2 (valid = lo <= id < hi; out = m * table[valid ? id : dflt])
+struct GatherParams {
+  const float* table;
+  const void* ids;
+  const unsigned char* empty;
+  float* out;
+  long long n, rows, dim;
+  unsigned long long num_buckets;
+  long long lo, hi, dflt;
+  int mode;
+  int ids64;
+};
+
+__global__ void __launch_bounds__(256) row_gather_kernel(GatherParams g, int* err) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  const bool vec = (g.dim % 4 == 0) && ((((uintptr_t)g.table) | ((uintptr_t)g.out)) % 16 == 0);
+  for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < g.n;
+       i += warps) {
+    long long row = -1;
+    float scale = 1.0f;
+    bool use_scale = false;
+    if (g.mode == 2) {
+      long long id = g.ids64 ? ((const long long*)g.ids)[i] : (long long)((const int*)g.ids)[i];
+      const bool valid = id >= g.lo && id < g.hi;
+      row = valid ? id : g.dflt;
+      scale = valid ? 1.0f : 0.0f;
+      use_scale = true;
+      if (row < 0 || row >= g.rows) {
+        if (lane == 0) atomicOr(err, kErrRow);
+        row = -1;
+      }
+    } else if (!(g.empty && g.empty[i])) {
+      unsigned long long b = ((const unsigned long long*)g.ids)[i] % g.num_buckets;
+      row = (long long)b;
+      if (row < 0 || row >= g.rows) {
+        if (g.mode == 0 && lane == 0) atomicOr(err, kErrRow);
+        row = -1;
+      }
+    }
+    float* o = g.out + i * g.dim;
+    const float* src = row >= 0 ? g.table + row * g.dim : nullptr;
+    if (vec) {
+      for (long long c = lane * 4; c < g.dim; c += 128) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src) v = ldg4(src + c);
+        if (use_scale) {
+          v.x = __fmul_rn(scale, v.x);
+          v.y = __fmul_rn(scale, v.y);
+          v.z = __fmul_rn(scale, v.z);
+          v.w = __fmul_rn(scale, v.w);
+        }
+        *reinterpret_cast<float4*>(o + c) = v;
+      }
+    } else {
+      for (long long c = lane; c < g.dim; c += 32) {
+        float v = src ? __ldg(src + c) : 0.f;
+        o[c] = use_scale ? __fmul_rn(scale, v) : v;
+      }
+    }
+  }
+}
+
+// KPFusedSparseDynamicStitch: table = id % N, row = id / N.
+struct StitchParams {
+  const float* const* tables;  // device array [N]
+  const long long* table_rows; // device array [N]
+  const long long* x;
+  float* out;
+  long long n, dim;
+  int num_partitions;
+};
+
+__global__ void __launch_bounds__(256) stitch_kernel(StitchParams g, int* err) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < g.n;
+       i += warps) {
+    const long long id = g.x[i];
+    const long long t = id % g.num_partitions;
+    const long long r = id / g.num_partitions;
+    float* o = g.out + i * g.dim;
+    if (id < 0 || !(r < g.table_rows[t])) {
+      if (lane == 0) atomicOr(err, kErrRow);
+      for (long long c = lane; c < g.dim; c += 32) o[c] = 0.f;
+      continue;
+    }
+    const float* src = g.tables[t] + r * g.dim;
+    const bool vec = (g.dim % 4 == 0) && ((((uintptr_t)src) | ((uintptr_t)o)) % 16 == 0);
+    if (vec) {
+      for (long long c = lane * 4; c < g.dim; c += 128)
+        *reinterpret_cast<float4*>(o + c) = ldg4(src + c);
+    } else {
+      for (long long c = lane; c < g.dim; c += 32) o[c] = __ldg(src + c);
+    }
+  }
+}
+
+// ---- first-appearance unique (KPFusedGather, segment order of the Nonzero op) ---
+// Open-addressing table of int64 keys; the empty marker is INT64_MIN, a key equal
+// to the marker lives in the extra last slot.  first[slot] = smallest position
+// that holds the key.
+constexpr long long kEmptyKey = (long long)0x8000000000000000ull;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+  x ^= x >> 33;
+  x *= 0xff51afd7ed558ccdull;
+  x ^= x >> 33;
+  x *= 0xc4ceb9fe1a85ec53ull;
+  x ^= x >> 33;
+  return x;
+}
+
+__device__ __forceinline__ long long find_or_insert(long long* keys, long long cap, long long key) {
+  if (key == kEmptyKey) return cap;  // dedicated slot
+  unsigned long long h = mix64((unsigned long long)key) & (unsigned long long)(cap - 1);
+  for (long long probe = 0; probe < cap; ++probe) {
+    long long old = atomicCAS((unsigned long long*)&keys[h], (unsigned long long)kEmptyKey,
+                              (unsigned long long)key);
+    if (old == kEmptyKey || old == key) return (long long)h;
+    h = (h + 1) & (unsigned long long)(cap - 1);
+  }
+  return -1;  // table full: cannot happen with cap >= 2 * n
+}
+
+__global__ void unique_init_kernel(long long* keys, int* first, long long cap) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i <= cap; i += stride) {
+    keys[i] = kEmptyKey;
+    first[i] = 0x7fffffff;
+  }
+}
+
+__global__ void unique_insert_kernel(const int64_t* src, long long n, long long ncols, int col,
+                                     long long* keys, int* first, long long cap, int* slot_of) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    long long slot = find_or_insert(keys, cap, src[i * ncols + col]);
+    slot_of[i] = (int)slot;
+    if (slot >= 0) atomicMin(&first[slot], (int)i);
+  }
+}
+
+__global__ void unique_flag_kernel(const int* slot_of, const int* first, long long n, int* flag) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    flag[i] = (slot_of[i] >= 0 && first[slot_of[i]] == (int)i) ? 1 : 0;
+}
+
+// rank[] = exclusive scan of flag[].  Writes unique keys in first-appearance order and
+// turns first[slot] into the key's rank.
+__global__ void unique_emit_kernel(const int64_t* src, long long n, long long ncols, int col,
+                                   const int* slot_of, const int* flag, const int* rank,
+                                   int* first, long long* out_unique) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (flag[i]) {
+      if (out_unique) out_unique[rank[i]] = src[i * ncols + col];
+      first[slot_of[i]] = rank[i];
+    }
+  }
+}
+
+// inverse[i] = rank of key i; optionally as int64 (segment column for the bag kernels).
+__global__ void unique_inverse_kernel(const int* slot_of, const int* first, long long n,
+                                      int* inverse32, long long* inverse64) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int r = slot_of[i] >= 0 ? first[slot_of[i]] : 0;
+    if (inverse32) inverse32[i] = r;
+    if (inverse64) inverse64[i] = r;
+  }
+}
+
+// out[u,:] = table[unique[u],:] with the `idx < rows` check of the reference.
+__global__ void __launch_bounds__(256)
+unique_rows_kernel(const float* table, long long rows, long long dim, const long long* unique,
+                   long long nu, float* out, int* err) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu;
+       u += warps) {
+    const long long r = unique[u];
+    if (!(r < rows) || r < 0) {
+      if (lane == 0) atomicOr(err, kErrRow);
+      continue;
+    }
+    for (long long c = lane; c < dim; c += 32) out[u * dim + c] = __ldg(table + r * dim + c);
+  }
+}
+
+// ---- exclusive scan of int32 (three passes, 2048 items per block) ---------------
+constexpr int kScanThreads = 512;
+constexpr int kScanItems = 4;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total_out) {
+  __shared__ int warp_sums[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int x = v;
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) warp_sums[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0;
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += y;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  const int warp_off = warp == 0 ? 0 : warp_sums[warp - 1];
+  if (total_out) *total_out = warp_sums[(blockDim.x >> 5) - 1];
+  const int r = warp_off + x - v;
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+scan_tile_sums_kernel(const int* in, long long n, int* tile_sums) {
+  const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * kScanItems;
+  int s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k)
+    if (base + k < n) s += in[base + k];
+  int total;
+  block_exclusive_scan(s, &total);
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+// One block walks all tile sums with a running carry; tile_sums becomes exclusive
+// offsets and *grand_total the overall sum.
+__global__ void __launch_bounds__(kScanThreads)
+scan_tile_offsets_kernel(int* tile_sums, long long ntiles, int* grand_total) {
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (long long base = 0; base < ntiles; base += kScanThreads) {
+    const long long i = base + threadIdx.x;
+    const int v = i < ntiles ? tile_sums[i] : 0;
+    int total;
+    const int ex = block_exclusive_scan(v, &total);
+    const int c = carry;
+    if (i < ntiles) tile_sums[i] = c + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) carry = c + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *grand_total = carry;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+scan_apply_kernel(const int* in, long long n, const int* tile_offsets, int* out) {
+  const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * kScanItems;
+  int v[kScanItems];
+  int s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    v[k] = base + k < n ? in[base + k] : 0;
+    s += v[k];
+  }
+  int ex = block_exclusive_scan(s, nullptr) + tile_offsets[blockIdx.x];
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    if (base + k < n) out[base + k] = ex;
+    ex += v[k];
+  }
+}
+
+// ---- non-zero compaction of the Nonzero op --------------------------------------
+// dense f32[nseg, dim] (already scaled for mean); flag = value != 0.
+__global__ void nonzero_flag_kernel(const float* dense, long long total, int* flag) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride)
+    flag[e] = dense[e] != 0.0f ? 1 : 0;
+}
+
+__global__ void nonzero_emit_kernel(const float* dense, long long total, long long dim, int rank,
+                                    const long long* seg_order, const int* flag, const int* pos,
+                                    int* out_indices, float* out_values) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    if (!flag[e]) continue;
+    const long long u = e / dim, d = e - u * dim;
+    const int o = pos[e];
+    out_indices[(long long)o * rank] = (int)seg_order[u];
+    if (rank == 2) out_indices[(long long)o * 2 + 1] = (int)d;
+    out_values[o] = dense[e];
+  }
+}
+
+}  // namespace emb
+}  // namespace annc

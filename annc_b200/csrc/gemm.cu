@@ -1,0 +1,159 @@
+// GEMM dispatcher, the kn4 converters and the KPFusedBatchMatMulAddSigmoid twin.
+#include <cstring>
+
+#include "common.h"
+#include "gemm.h"
+#include "kn4.h"
+
+namespace annc {
+namespace gemm {
+
+static int validate(const annc_gemm_desc& d) {
+  ANNC_REQUIRE(d.a && d.b && d.c, ANNC_ERR_INVALID_ARGUMENT, "gemm: null operand");
+  ANNC_REQUIRE(d.m >= 0 && d.n >= 0 && d.k >= 0 && d.batch >= 1, ANNC_ERR_INVALID_ARGUMENT,
+               "gemm: bad extents");
+  ANNC_REQUIRE(d.activation >= ANNC_ACT_NONE && d.activation <= ANNC_ACT_SIGMOID,
+               ANNC_ERR_INVALID_ARGUMENT, "gemm: bad activation");
+  ANNC_REQUIRE(d.b_format == ANNC_B_PLAIN || d.b_format == ANNC_B_KN4, ANNC_ERR_INVALID_ARGUMENT,
+               "gemm: bad b_format");
+  ANNC_REQUIRE(d.b_format == ANNC_B_PLAIN || !d.trans_b, ANNC_ERR_INVALID_ARGUMENT,
+               "gemm: kn4 B cannot be transposed");
+  ANNC_REQUIRE(d.math >= ANNC_MATH_AUTO && d.math <= ANNC_MATH_BF16, ANNC_ERR_INVALID_ARGUMENT,
+               "gemm: bad math mode");
+  return ANNC_OK;
+}
+
+// AUTO: tensor cores (TF32) when the shape fits the tcgen05 kernel, else CUDA cores.
+static int pick_math(const annc_gemm_desc& d) {
+  if (d.math == ANNC_MATH_FP32) return ANNC_MATH_FP32;
+  const int want = d.math == ANNC_MATH_AUTO ? ANNC_MATH_TF32 : d.math;
+  return tc_supported(d, want) ? want : ANNC_MATH_FP32;
+}
+
+const char* route_name(const annc_gemm_desc& d) {
+  switch (pick_math(d)) {
+    case ANNC_MATH_TF32: return "tcgen05_tf32";
+    case ANNC_MATH_BF16: return "tcgen05_bf16";
+    default: return "simt_fp32";
+  }
+}
+
+namespace {
+
+__global__ void kn4_convert_kernel(const float* src, float* dst, long long K, long long N,
+                                   int to_packed) {
+  const long long total = K * N;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long k = e / N, n = e - k * N;
+    const long long o = kn4::offset(K, N, k, n);
+    if (to_packed) dst[o] = src[e];
+    else dst[e] = src[o];
+  }
+}
+
+}  // namespace
+}  // namespace gemm
+}  // namespace annc
+
+using namespace annc;
+
+extern "C" {
+
+int annc_gemm_run(const annc_gemm_desc* desc, void* stream) {
+  ANNC_REQUIRE(desc, ANNC_ERR_INVALID_ARGUMENT, "gemm: null descriptor");
+  ANNC_TRY(gemm::validate(*desc));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int math = gemm::pick_math(*desc);
+  if (desc->math != ANNC_MATH_AUTO && desc->math != math)
+    return fail(ANNC_ERR_UNSUPPORTED, "gemm: shape not supported by the requested math mode");
+  if (math == ANNC_MATH_FP32) return gemm::run_simt(*desc, s);
+  return gemm::run_tc(*desc, math, s);
+}
+
+const char* annc_gemm_kernel_name(const annc_gemm_desc* desc) {
+  if (!desc) return "";
+  return gemm::route_name(*desc);
+}
+
+int annc_kn4_pack_dev(const float* b_kn, float* b_packed, int64_t k, int64_t n, void* stream) {
+  ANNC_REQUIRE(b_kn && b_packed && b_kn != b_packed, ANNC_ERR_INVALID_ARGUMENT, "kn4: bad buffers");
+  if (k * n <= 0) return ANNC_OK;
+  long long g = (k * n + 255) / 256;
+  if (g > 148 * 32) g = 148 * 32;
+  gemm::kn4_convert_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      b_kn, b_packed, k, n, 1);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_kn4_unpack_dev(const float* b_packed, float* b_kn, int64_t k, int64_t n, void* stream) {
+  ANNC_REQUIRE(b_kn && b_packed && b_kn != b_packed, ANNC_ERR_INVALID_ARGUMENT, "kn4: bad buffers");
+  if (k * n <= 0) return ANNC_OK;
+  long long g = (k * n + 255) / 256;
+  if (g > 148 * 32) g = 148 * 32;
+  gemm::kn4_convert_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      b_packed, b_kn, k, n, 0);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int64_t annc_kn4_offset(int64_t K, int64_t N, int64_t k, int64_t n) {
+  if (k < 0 || n < 0 || k >= K || n >= N) return -1;
+  return kn4::offset(K, N, k, n);
+}
+
+int annc_KPFusedBatchMatMulAddSigmoid(const annc_tensor* lhs, const annc_tensor* rhs,
+                                      const annc_tensor* bias, annc_alloc_fn alloc, void* ctx) {
+  ANNC_REQUIRE(lhs && rhs && bias && alloc, ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  ANNC_REQUIRE(lhs->rank == 3, ANNC_ERR_INVALID_ARGUMENT, "lhs must be rank 3");
+  ANNC_REQUIRE(rhs->rank == 2 || rhs->rank == 3, ANNC_ERR_INVALID_ARGUMENT, "rhs must be rank 2 or 3");
+  ANNC_REQUIRE(bias->rank <= 3, ANNC_ERR_INVALID_ARGUMENT, "bias rank must be <= 3");
+  const int64_t batch = lhs->dims[0], m = lhs->dims[1], k = lhs->dims[2];
+  const bool rhs_batched = rhs->rank == 3;
+  ANNC_REQUIRE(!rhs_batched || rhs->dims[0] == batch, ANNC_ERR_INVALID_ARGUMENT,
+               "lhs/rhs batch mismatch");
+  ANNC_REQUIRE(rhs->dims[rhs_batched ? 1 : 0] == k, ANNC_ERR_INVALID_ARGUMENT,
+               "lhs/rhs contracting dim mismatch");
+  const int64_t n = rhs->dims[rhs_batched ? 2 : 1];
+  const int64_t out_dims[3] = {batch, m, n};
+  float* out = static_cast<float*>(alloc(ctx, 0, ANNC_F32, 3, out_dims));
+  // BuildBiasInfo (fused_batchmatmul_add_sigmoid.cc:197-214)
+  int64_t bd[3] = {1, 1, 1};
+  for (int i = 0; i < bias->rank; ++i) bd[3 - bias->rank + i] = bias->dims[i];
+  ANNC_REQUIRE((bd[0] == 1 || bd[0] == batch) && (bd[1] == 1 || bd[1] == m) &&
+                   (bd[2] == 1 || bd[2] == n),
+               ANNC_ERR_INVALID_ARGUMENT, "bias shape is not broadcast-compatible");
+  gemm::BiasBroadcast bb;
+  bb.s2 = bd[2] == 1 ? 0 : 1;
+  bb.s1 = bd[1] == 1 ? 0 : bd[2];
+  bb.s0 = bd[0] == 1 ? 0 : bd[1] * bd[2];
+  if (batch * m * n == 0) return ANNC_OK;
+  ANNC_REQUIRE(out, ANNC_ERR_INTERNAL, "output allocation failed");
+  Call call;
+  annc_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.m = m;
+  d.n = n;
+  d.k = k;
+  d.batch = batch;
+  d.lda = k;
+  d.ldb = n;
+  d.ldc = n;
+  d.stride_a = m * k;
+  d.stride_b = rhs_batched ? k * n : 0;
+  d.stride_c = m * n;
+  d.alpha = 1.0f;
+  d.beta = 0.0f;
+  d.a = call.in((const float*)lhs->data, (size_t)numel(*lhs));
+  d.b = call.in((const float*)rhs->data, (size_t)numel(*rhs));
+  d.bias = call.in((const float*)bias->data, (size_t)numel(*bias));
+  d.c = call.out(out, (size_t)(batch * m * n));
+  d.activation = ANNC_ACT_SIGMOID;
+  d.math = ANNC_MATH_FP32;  // the reference test asks for 1e-5
+  if (call.status() != ANNC_OK) return call.status();
+  ANNC_TRY(gemm::run_simt(d, call.stream(), &bb));
+  return call.finish();
+}
+
+}  // extern "C"

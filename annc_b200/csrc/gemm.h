@@ -1,0 +1,28 @@
+// Internal interface of the GEMM core.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "annc_b200.h"
+
+namespace annc {
+namespace gemm {
+
+// bias[b*s0 + i*s1 + j*s2]: the numpy-style broadcast of
+// KPFusedBatchMatMulAddSigmoid (fused_batchmatmul_add_sigmoid.cc:197-214).
+struct BiasBroadcast {
+  long long s0, s1, s2;
+};
+
+// CUDA-core fp32 route; takes every shape, both transposes and the kn4 B format.
+int run_simt(const annc_gemm_desc& d, cudaStream_t s, const BiasBroadcast* bb = nullptr);
+
+// tcgen05 route: whether the descriptor fits, and the launch.
+bool tc_supported(const annc_gemm_desc& d, int math);
+int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s);
+
+// Picks the route the way annc_gemm_run does; returns a static name.
+const char* route_name(const annc_gemm_desc& d);
+
+}  // namespace gemm
+}  // namespace annc

@@ -1,0 +1,126 @@
+"""Device-pointer entry points (`*_dev`, annc_gemm_run) on torch CUDA tensors.
+
+torch supplies device memory and the stream; every kernel that runs is from
+libannc_b200.so.  Nothing here allocates inside a call: outputs and workspaces are
+passed in, so the calls can sit in a timed loop or under stream capture."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from ._lib import (ACT_NONE, B_PLAIN, MATH_AUTO, BagTable, GemmDesc, check, lib)
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class BagPlan:
+    """Holds the host descriptor array and the device workspace of one grouped
+    embedding-bag call (tables, id buffers, segment matrices and outputs fixed)."""
+
+    def __init__(self, tables: Sequence[torch.Tensor], ids: Sequence[torch.Tensor],
+                 slice_inputs: Sequence[torch.Tensor], out: torch.Tensor, out_slot0: int,
+                 batch: int, id_kind: int = 2, col: int = 0, combiner: int = 0,
+                 num_buckets: Optional[Sequence[int]] = None):
+        self.n = len(tables)
+        self.dim = int(tables[0].shape[1])
+        self.batch = int(batch)
+        self.id_kind, self.col, self.combiner = id_kind, col, combiner
+        self.ncols = int(slice_inputs[0].shape[1])
+        self.out = out
+        # out is [batch, slots, dim]; table t writes slot out_slot0 + t
+        slots = int(out.shape[1]) if out.dim() == 3 else 1
+        self.out_stride = slots * self.dim
+        self.keep = (list(tables), list(ids), list(slice_inputs))
+        self.desc = (BagTable * self.n)()
+        esz = out.element_size()
+        for t in range(self.n):
+            d = self.desc[t]
+            d.table = tables[t].data_ptr()
+            d.rows = int(tables[t].shape[0])
+            d.num_buckets = int(num_buckets[t]) if num_buckets is not None else int(tables[t].shape[0])
+            d.ids = ids[t].data_ptr()
+            d.slice_input = slice_inputs[t].data_ptr()
+            d.nnz = int(ids[t].shape[0])
+            d.out = out.data_ptr() + (out_slot0 + t) * self.dim * esz
+        self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=out.device)
+
+    def run(self) -> None:
+        check(lib.annc_embed_bags_dev(self.desc, C.c_int(self.n), C.c_int64(self.dim),
+                                      C.c_int(self.id_kind), C.c_int64(self.ncols),
+                                      C.c_int32(self.col), C.c_int(self.combiner),
+                                      C.c_int64(self.batch), C.c_int64(self.out_stride),
+                                      C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws_bytes),
+                                      _stream()))
+
+    def error_bits(self) -> int:
+        bits = C.c_int(0)
+        check(lib.annc_embed_bag_check(C.c_void_p(self.ws.data_ptr()), _stream(), C.byref(bits)))
+        return bits.value
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, m: int, n: int, k: int,
+         trans_a: bool = False, trans_b: bool = False, batch: int = 1,
+         lda: Optional[int] = None, ldb: Optional[int] = None, ldc: Optional[int] = None,
+         stride_a: int = 0, stride_b: int = 0, stride_c: int = 0,
+         alpha: float = 1.0, beta: float = 0.0, addend: Optional[torch.Tensor] = None,
+         ld_addend: Optional[int] = None, stride_addend: int = 0,
+         bias: Optional[torch.Tensor] = None, activation: int = ACT_NONE,
+         b_format: int = B_PLAIN, math: int = MATH_AUTO) -> str:
+    """annc_gemm_run; returns the name of the kernel family that ran."""
+    d = GemmDesc()
+    d.trans_a, d.trans_b = int(trans_a), int(trans_b)
+    d.m, d.n, d.k, d.batch = m, n, k, batch
+    d.lda = lda if lda is not None else (m if trans_a else k)
+    d.ldb = ldb if ldb is not None else (k if trans_b else n)
+    d.ldc = ldc if ldc is not None else n
+    d.ld_addend = ld_addend if ld_addend is not None else n
+    d.stride_a, d.stride_b, d.stride_c, d.stride_addend = stride_a, stride_b, stride_c, stride_addend
+    d.alpha, d.beta = alpha, beta
+    d.a, d.b, d.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    d.addend = addend.data_ptr() if addend is not None else None
+    d.bias = bias.data_ptr() if bias is not None else None
+    d.activation, d.b_format, d.math = activation, b_format, math
+    name = lib.annc_gemm_kernel_name(C.byref(d)).decode()
+    check(lib.annc_gemm_run(C.byref(d), _stream()))
+    return name
+
+
+def softmax(x: torch.Tensor, out: torch.Tensor) -> None:
+    ch = x.shape[-1]
+    check(lib.annc_softmax_dev(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+                               C.c_int64(x.numel() // ch), C.c_int64(ch), _stream()))
+
+
+def gemv(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, m: int, n: int, trans_a=False,
+         alpha=1.0, beta=0.0) -> None:
+    check(lib.annc_gemv_dev(C.c_int(int(trans_a)), C.c_int64(m), C.c_int64(n), C.c_float(alpha),
+                            C.c_void_p(a.data_ptr()), C.c_void_p(x.data_ptr()), C.c_float(beta),
+                            C.c_void_p(y.data_ptr()), _stream()))
+
+
+def dot_interaction(z: torch.Tensor, out: torch.Tensor) -> None:
+    """z f32[batch, F, D] -> out f32[batch, out_stride] = [z[:,0,:] | tril(z z^T, -1) | 0 pad]."""
+    batch, F, D = z.shape
+    check(lib.annc_dot_interaction_dev(C.c_void_p(z.data_ptr()), C.c_int64(batch), C.c_int(F),
+                                       C.c_int(D), C.c_int64(F * D), C.c_void_p(out.data_ptr()),
+                                       C.c_int64(out.shape[1]), _stream()))
+
+
+def kn4_pack(b_kn: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(b_kn)
+    check(lib.annc_kn4_pack_dev(C.c_void_p(b_kn.data_ptr()), C.c_void_p(out.data_ptr()),
+                                C.c_int64(b_kn.shape[0]), C.c_int64(b_kn.shape[1]), _stream()))
+    return out
+
+
+def kn4_unpack(b_packed: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(b_packed)
+    check(lib.annc_kn4_unpack_dev(C.c_void_p(b_packed.data_ptr()), C.c_void_p(out.data_ptr()),
+                                  C.c_int64(b_packed.shape[0]), C.c_int64(b_packed.shape[1]),
+                                  _stream()))
+    return out

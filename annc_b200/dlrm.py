@@ -1,0 +1,122 @@
+"""DLRM-style inference step assembled from the library's operator entry points,
+the way an ANNC-rewritten graph would call them:
+
+  bottom MLP   3 x matmul + bias + ReLU            (annc_gemm_run, bias-row epilogue)
+  embeddings   hash-bucket + gather + segment sum  (annc_embed_bags_dev, all tables, one launch)
+  interaction  batch_matmul Z Z^T, lower triangle  (annc_dot_interaction_dev)
+  top MLP      2 x matmul + bias + ReLU, 1 x matmul + bias + sigmoid
+
+torch holds the device buffers and the stream; all kernels are from libannc_b200.so.
+Buffers are allocated once in __init__, a step allocates nothing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import device as dev
+from ._lib import ACT_RELU, ACT_SIGMOID, MATH_AUTO, lib
+from .synth import DlrmModel
+
+
+class DlrmPipeline:
+    def __init__(self, model: DlrmModel, device: torch.device, math: int = MATH_AUTO,
+                 keep_host_inputs: bool = False):
+        self.device = device
+        self.math = math
+        emb = model.emb
+        self.batch = B = emb.batch
+        self.dim = D = emb.dim
+        self.T = T = len(emb.tables)
+        self.F = F = T + 1
+        tri = F * (F - 1) // 2
+        self.inter = D + tri
+        self.inter_pad = (self.inter + 3) // 4 * 4  # 16-byte rows for the tensor-core loader
+
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        self.tables = [up(t) for t in emb.tables]
+        self.bottom = [(up(w), up(b)) for w, b in model.bottom]
+        top = []
+        for i, (w, b) in enumerate(model.top):
+            if i == 0 and w.shape[0] != self.inter_pad:
+                w = np.concatenate([w, np.zeros((self.inter_pad - w.shape[0], w.shape[1]), np.float32)])
+            top.append((up(w), up(b)))
+        self.top = top
+
+        # step inputs: one flat buffer per kind so that an end-to-end step is three copies
+        nnz = [b.raw_ids.shape[0] for b in emb.bags]
+        self.nnz = nnz
+        self.nnz_total = int(sum(nnz))
+        ids_host = np.concatenate([b.raw_ids for b in emb.bags])
+        seg_host = np.concatenate([b.slice_input for b in emb.bags])
+        self.ids_all = up(ids_host)
+        self.seg_all = up(seg_host)
+        self.dense = up(model.dense)
+        offs = np.concatenate([[0], np.cumsum(nnz)])
+        self.ids = [self.ids_all[offs[t]:offs[t + 1]] for t in range(T)]
+        self.segs = [self.seg_all[offs[t]:offs[t + 1]] for t in range(T)]
+        if keep_host_inputs:
+            self.h_ids = torch.from_numpy(ids_host).pin_memory()
+            self.h_seg = torch.from_numpy(seg_host).pin_memory()
+            self.h_dense = torch.from_numpy(np.ascontiguousarray(model.dense)).pin_memory()
+            self.h_out = torch.empty((B, 1), dtype=torch.float32).pin_memory()
+
+        f32 = dict(dtype=torch.float32, device=device)
+        self.acts_b = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.bottom[:-1]]
+        self.z = torch.empty((B, F, D), **f32)
+        self.inter_buf = torch.empty((B, self.inter_pad), **f32)
+        self.acts_t = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.top]
+        self.out = self.acts_t[-1]
+        self.plan = dev.BagPlan(self.tables, self.ids, self.segs, self.z, 1, B, id_kind=2, col=0,
+                                combiner=0)
+        self.kernel_names: List[str] = []
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ one step
+    def forward(self) -> torch.Tensor:
+        names = []
+        B, F, D = self.batch, self.F, self.dim
+        x = self.dense
+        nb = len(self.bottom)
+        for i, (w, b) in enumerate(self.bottom):
+            last = i == nb - 1
+            y = self.z if last else self.acts_b[i]
+            names.append(dev.gemm(x, w, y, m=B, n=w.shape[1], k=w.shape[0], bias=b,
+                                  activation=ACT_RELU, ldc=(F * D if last else None),
+                                  math=self.math))
+            x = y
+        self.plan.run()
+        dev.dot_interaction(self.z, self.inter_buf)
+        x = self.inter_buf
+        nt = len(self.top)
+        for i, (w, b) in enumerate(self.top):
+            y = self.acts_t[i]
+            act = ACT_SIGMOID if i == nt - 1 else ACT_RELU
+            names.append(dev.gemm(x, w, y, m=B, n=w.shape[1], k=w.shape[0], bias=b, activation=act,
+                                  math=self.math))
+            x = y
+        self.kernel_names = names
+        # prepass + bag + scatter route + interaction + one kernel per MLP layer
+        self.launches_per_step = 3 + 1 + len(names)
+        return self.out
+
+    def forward_e2e(self) -> torch.Tensor:
+        """Host buffers in, host result out: the three input copies from pinned memory, the
+        step, and the copy of the predictions back are all on the current stream."""
+        self.ids_all.copy_(self.h_ids, non_blocking=True)
+        self.seg_all.copy_(self.h_seg, non_blocking=True)
+        self.dense.copy_(self.h_dense, non_blocking=True)
+        out = self.forward()
+        self.h_out.copy_(out, non_blocking=True)
+        return self.h_out
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.ids_all.numel() * 8 + self.seg_all.numel() * 8 + self.dense.numel() * 4
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.out.numel() * 4

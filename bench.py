@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""DLRM-style inference benchmark of annc_b200 (one process per GPU).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU reference arm
+
+A step is one inference pass over one synthetic batch of the DLRM-style config
+(13 dense, bottom MLP 13-512-256-64, 26 tables with log-uniform rows 1e3..1e7,
+dim 64, Zipf 1.05 ids, bags 1..20, dot interaction, top MLP 415-512-256-1,
+batch 65536 per GPU, fp32 weights / TF32 tensor-core math).  Prints one JSON line.
+
+Timing: W >= 3 warm-up steps, then K steps bracketed by a barrier and a device
+synchronize, CUDA events on the launching stream, max over ranks.  Every step's
+inputs (6.6 GB of tables, 0.43 GB of ids) are far larger than the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "dlrm_inference_samples_per_s"
+UNIT = "samples/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="annc_b200", choices=["annc_b200", "reference"])
+    ap.add_argument("--batch", type=int, default=65536, help="samples per GPU per step")
+    ap.add_argument("--max-rows", type=float, default=1e7)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_config(args, world):
+    return {"workload": "dlrm_style_fp32w_tf32math_batch%d_26tables_dim64_zipf1.05" % args.batch,
+            "global_batch": args.batch * world, "per_gpu_batch": args.batch,
+            "tables": 26, "dim": 64, "rows": "log-uniform 1e3..%g" % args.max_rows,
+            "parallelism": "replicas" if world > 1 else "single",
+            "l2": "inputs larger than L2 (tables 6.6 GB, ids 0.43 GB per step)"}
+
+
+# ---------------------------------------------------------------- clocks
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only)."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ---------------------------------------------------------------- CPU arm
+
+def cpu_forward_timed(model, threads, reps, sample=None):
+    from oracle import oracle
+    oracle.dlrm_forward(model, sample=min(2048, model.emb.batch), threads=threads)  # page-in
+    t = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        oracle.dlrm_forward(model, sample=sample, threads=threads)
+        t.append(time.perf_counter() - t0)
+    return t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from annc_b200 import synth
+    from oracle import oracle
+    model = synth.dlrm_model(seed=args.seed, batch=args.batch, max_rows=args.max_rows)
+    threads = oracle.host_threads()
+    n = model.emb.batch
+    times = cpu_forward_timed(model, threads, args.warmup + args.steps)[args.warmup:]
+    ms = 1e3 * sum(times) / len(times)
+    value = n / (ms / 1e3)
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": workload_config(args, 1),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": "one full batch of %d samples per step; C restatement of the "
+                                       "reference kernels + OpenBLAS sgemm" % n},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- GPU arm
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (annc_b200 has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    devi = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=devi)
+
+    from annc_b200 import synth
+    from annc_b200._lib import lib
+    from annc_b200.dlrm import DlrmPipeline
+    import ctypes as C
+
+    model = synth.dlrm_model(seed=args.seed, batch=args.batch, max_rows=args.max_rows,
+                             input_seed=(1000 + rank) if world > 1 else None)
+    pipe = DlrmPipeline(model, devi, keep_host_inputs=True)
+    emb_bytes = model.emb.algorithmic_bytes()
+    nnz = model.emb.nnz
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=devi)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(3, args.warmup)):
+        pipe.forward()
+    torch.cuda.synchronize()
+    assert pipe.plan.error_bits() == 0, "embedding kernels flagged an index error"
+
+    # device-resident pass: the whole step, and the bag kernel alone through event hooks
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    pairs = [(C.c_void_p(lib.annc_timer_create()), C.c_void_p(lib.annc_timer_create()))
+             for _ in range(args.steps)]
+    it = iter(pairs)
+
+    def step_with_hooks():
+        a, b = next(it)
+        lib.annc_embed_bag_set_timing_events(a, b)
+        pipe.forward()
+
+    ms_total = timed(step_with_hooks, args.steps)
+    lib.annc_embed_bag_set_timing_events(None, None)
+    bag_ms = []
+    for a, b in pairs:
+        v = C.c_float(0)
+        lib.annc_timer_elapsed_ms(a, b, C.byref(v))
+        bag_ms.append(v.value)
+        lib.annc_timer_destroy(a)
+        lib.annc_timer_destroy(b)
+    ms_step = ms_total / args.steps
+
+    # end-to-end pass: host buffers in, host result out
+    for _ in range(2):
+        pipe.forward_e2e()
+    ms_e2e = timed(pipe.forward_e2e, args.steps) / args.steps
+    sampler.stop()
+    sampler.join(timeout=2)
+
+    value = args.batch * world / (ms_step / 1e3)
+    e2e_value = args.batch * world / (ms_e2e / 1e3)
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    bag_avg_ms = sum(bag_ms) / len(bag_ms)
+    achieved = emb_bytes / (bag_avg_ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "bag_reduce_kernel<16,1> (hash-bucket + gather + segment sum, "
+                                          "26 tables in one launch)",
+                "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
+                "algorithmic_bytes_per_launch": emb_bytes, "lookups_per_launch": nnz,
+                "kernel_ms": bag_avg_ms, "traffic": None}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+                "impl": "annc_b200", "config": workload_config(args, world),
+                "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
+                        "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes},
+                "gpu_launches": pipe.launches_per_step * args.steps,
+                "gemm_kernels": sorted(set(pipe.kernel_names)),
+                "roofline": roofline, "clocks": sampler.summary()}
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle
+            threads = oracle.host_threads()
+            t = cpu_forward_timed(model, threads, 3)
+            cpu_ms = 1e3 * sum(t) / len(t)
+            line["cpu_baseline"] = {"value": args.batch / (cpu_ms / 1e3), "unit": UNIT, "cores": threads,
+                                    "kind": "port", "ms_per_step": cpu_ms,
+                                    "sample": "3 full batches of %d samples (C restatement of the "
+                                              "reference kernels, one table per thread, + OpenBLAS sgemm)"
+                                              % args.batch}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

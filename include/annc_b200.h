@@ -1,0 +1,332 @@
+/*
+ * annc_b200 -- C ABI of the B200 (sm_100a) implementation of the custom operators
+ * that ANNC's XLA and TF-Grappler passes route to.
+ *
+ * Three groups of entry points:
+ *
+ *  (1) The reference's own symbols, same names and signatures, so that graphs
+ *      rewritten by annc-opt / the ANNC passes dispatch here unchanged:
+ *      the XLA custom-call targets (`void f(void* out, const void** in)`), the
+ *      XLA:CPU runtime symbols of the kernel selector and the softmax.  They
+ *      are declared at the end of this file; the C++-mangled aliases that the
+ *      reference's MLIR lowering calls are defined in the library as well.
+ *  (2) Plain-C twins of the TensorFlow fused ops (`annc_KPFused...`): inputs as
+ *      `annc_tensor` views, outputs obtained through an allocation callback that
+ *      plays the role of OpKernelContext::allocate_output, status + message in
+ *      place of OP_REQUIRES.
+ *  (3) Device-pointer entry points (`*_dev`, `annc_gemm_run`): no staging, no
+ *      allocation, explicit stream.  The roofline figures are measured on these.
+ *
+ * Pointer rule for groups (1) and (2): every data pointer may be host memory or
+ * device memory.  Host buffers are staged through a per-thread device arena and
+ * results are copied back before the call returns; device buffers are used in
+ * place on the calling thread's stream (annc_set_stream).  Constant operands
+ * (weights, tables) can be registered once with annc_register_constant so that
+ * they are uploaded a single time.  There is no CPU fallback anywhere: without a
+ * CUDA device every compute entry point fails with ANNC_ERR_CUDA.
+ *
+ * Reference citations are paths inside the ANNC project.
+ */
+#ifndef ANNC_B200_H_
+#define ANNC_B200_H_
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status */
+
+enum {
+  ANNC_OK = 0,
+  ANNC_ERR_INVALID_ARGUMENT = 3, /* tensorflow errors::InvalidArgument */
+  ANNC_ERR_INTERNAL = 13,        /* tensorflow errors::Internal        */
+  ANNC_ERR_CUDA = 100,           /* CUDA runtime/driver failure        */
+  ANNC_ERR_TIMEOUT = 101,        /* a bounded device-side wait ran out */
+  ANNC_ERR_UNSUPPORTED = 102
+};
+
+/* Message of the last failing call on this thread (the reference's OP_REQUIRES
+ * text where there is one).  Valid until the next call on the same thread. */
+const char* annc_last_error(void);
+
+/* Version string "annc_b200 <semver> sm_100a". */
+const char* annc_version(void);
+
+/* Stream used by the calling thread for groups (1) and (2); NULL = default stream. */
+void annc_set_stream(void* cuda_stream);
+void* annc_get_stream(void);
+
+/* Uploads `bytes` at host pointer `ptr` once; later calls that receive `ptr` use
+ * the device copy (XLA constants / parameters and TF variables keep their address
+ * for the lifetime of the executable).  annc_unregister_constant drops it. */
+int annc_register_constant(const void* ptr, size_t bytes);
+int annc_unregister_constant(const void* ptr);
+
+/* Frees the calling thread's staging arena and every registered constant. */
+void annc_release_device_memory(void);
+
+/* ---------------------------------------------------------------- gating
+ * ANNC_FLAGS parser, same grammar, defaults and group expansion as
+ * annc/service/cpu/annc_flags.cc:10-131. */
+
+/* Parsed once from the environment, like annc::get_annc_flags(). */
+int annc_flags_is_enabled(const char* name);
+/* Parses `flags` (may be NULL = unset) afresh and answers for `name`. */
+int annc_flags_is_enabled_in(const char* flags, const char* name);
+
+/* Custom-call registry, the counterpart of REGISTER_ALL_GEMM_KERNELS
+ * (annc/service/cpu/kdnn_rewriter.h:148-155, install/tensorflow.patch:187-198):
+ * all seven targets are registered when flag `annc-pass` is on.  Returns the
+ * function address or NULL. */
+void* annc_lookup_custom_call(const char* target_name);
+/* Which target a `dot` (optionally followed by add, add+maximum) is rewritten to
+ * under the current flags, following the benefit order of
+ * annc/service/cpu/gemm_rewriter.cc:116-134; NULL when none applies.
+ * pattern: 0 = dot, 1 = dot+add, 2 = dot+add+maximum, 3 = batch dot;
+ * rhs_is_parameter selects the layout_matmul matcher (gemm_rewriter.cc:13-56). */
+const char* annc_select_gemm_target(int pattern, int rhs_is_parameter);
+
+/* ---------------------------------------------------------------- tensors */
+
+enum { ANNC_F32 = 1, ANNC_I32 = 3, ANNC_I64 = 9, ANNC_BOOL = 10, ANNC_U64 = 23 };
+
+typedef struct annc_tensor {
+  void* data;      /* host or device */
+  int32_t dtype;   /* ANNC_F32 ... */
+  int32_t rank;    /* 0..4 */
+  int64_t dims[4];
+} annc_tensor;
+
+/* Output allocation callback (OpKernelContext::allocate_output): must return a
+ * buffer of prod(dims) elements of `dtype`, host or device, or NULL to fail. */
+typedef void* (*annc_alloc_fn)(void* ctx, int output_index, int32_t dtype,
+                               int32_t rank, const int64_t* dims);
+
+/* ---------------------------------------------------------------- TF fused-op twins */
+
+/* KPFusedSparseSegmentReduce<Tidx>
+ * (annc/tensorflow/kernels/embedding_fused_sparse_segment_reduce.cc:38-152).
+ * data f32[rows,D]; indices i32|i64[nnz]; slice_input i64[nnz,ncols];
+ * begin i32[2]; begin_1 i32[1]; combiner 0 sum / 1 mean.
+ * Output 0: f32[max(seg)+1, D]; output 1: i32 scalar. */
+int annc_KPFusedSparseSegmentReduce(const annc_tensor* data, const annc_tensor* indices,
+                                    const annc_tensor* slice_input, const annc_tensor* begin,
+                                    const annc_tensor* begin_1, int combiner,
+                                    annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedSparseSegmentReduceNonzero<Tidx>
+ * (annc/tensorflow/kernels/embedding_fused_sparse_segment_reduce_nonzero.cc:39-374).
+ * data f32[rows] or f32[rows,D].  Outputs: 0 i32[r] shape, 1 i32[nz,r] indices,
+ * 2 f32[nz] values; segments in first-appearance order. */
+int annc_KPFusedSparseSegmentReduceNonzero(const annc_tensor* data, const annc_tensor* indices,
+                                           const annc_tensor* slice_input,
+                                           const annc_tensor* begin, int combiner,
+                                           annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedGather (annc/tensorflow/kernels/embedding_fused_gather.cc:26-86).
+ * Outputs: 0 i64[U] unique keys (first appearance), 1 i32[nnz] inverse map,
+ * 2 f32[U,D] rows. */
+int annc_KPFusedGather(const annc_tensor* data, const annc_tensor* keys,
+                       const annc_tensor* begin, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedSparseDynamicStitch
+ * (annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:31-83).
+ * x i64[...]; `num_tables` partition tables f32[rows_p, D].  Output 0: f32[numel(x), D]. */
+int annc_KPFusedSparseDynamicStitch(const annc_tensor* x, const annc_tensor* tables,
+                                    int num_tables, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedEmbeddingWithHashBucket
+ * (python/tensorflow/kernels/fused_embedding_with_hash_bucket.cc:29-77).
+ * The string input is replaced by its 64-bit fingerprints (`fingerprints` u64[batch])
+ * and an optional `empty` bool[batch] mask (NULL = no empty strings): the
+ * string -> Fingerprint64 step (FarmHash) is outside this library.
+ * `bounded` != 0 selects the KPFusedDnn/KPFusedLinear...WithHashBucket and
+ * RecEmbeddingV2 behaviour (fused_dnn_embedding_with_hash_bucket.cc:32-47): buckets
+ * outside the table leave zeros.  Output 0: f32[batch, D]. */
+int annc_KPFusedEmbeddingWithHashBucket(const annc_tensor* fingerprints, const annc_tensor* empty,
+                                        const annc_tensor* variable, int64_t num_buckets,
+                                        int bounded, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedSparseEmbedding / RecEmbeddingV1
+ * (python/tensorflow/kernels/fused_sparse_embedding.cc:25-80).  Outputs: 0 i64[n,2]
+ * indices, 1 i64[nv] values, 2 bool[nv] empty_row_indicator, 3 i64[2] dense_shape.
+ * As in the reference, a non-empty input whose bucket is 0 contributes an index row
+ * but no value, so nv can be smaller than n. */
+int annc_KPFusedSparseEmbedding(const annc_tensor* fingerprints, const annc_tensor* empty,
+                                int64_t num_buckets, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedBatchMatMulAddSigmoid
+ * (annc/tensorflow/kernels/fused_batchmatmul_add_sigmoid.cc:393-433).
+ * lhs f32[B,m,k]; rhs f32[k,n] or f32[B,k,n]; bias rank <= 3, numpy broadcast.
+ * Output 0: f32[B,m,n].  Computed in fp32 (tolerance of the reference test: 1e-5). */
+int annc_KPFusedBatchMatMulAddSigmoid(const annc_tensor* lhs, const annc_tensor* rhs,
+                                      const annc_tensor* bias, annc_alloc_fn alloc, void* ctx);
+
+/* sparse_embedding2 fusion (annc/service/cpu/graph_opt.cc:8-41): the reference only
+ * wraps the subgraph in a loop fusion; this is that loop.
+ * out[i,:] = (lo <= ids[i] < hi) ? table[ids[i],:] * 1.0f : table[dflt,:] * 0.0f.
+ * ids i32|i64[n]; table f32[rows,D]; out f32[n,D] (caller-owned, host or device). */
+int annc_sparse_embedding2(const annc_tensor* ids, const annc_tensor* table, int64_t lo,
+                           int64_t hi, int64_t dflt, float* out);
+
+/* ---------------------------------------------------------------- device entry points */
+
+/* Embedding bag: hash-bucket mapping + row gather + segment sum/mean in one pass.
+ *   id_kind 0: ids are i32 row numbers, 1: i64 row numbers,
+ *           2: u64 fingerprints, row = id % num_buckets (uint64 arithmetic,
+ *              fused_embedding_with_hash_bucket.cc:63-64).
+ * slice_input i64[nnz, ncols], column `col` = segment id of each lookup
+ * (embedding_fused_sparse_segment_reduce.cc:59-72); batch must be > max segment id.
+ * Sorted segment ids (the order of a canonical SparseTensor) run bit-exactly in the
+ * reference's summation order; unsorted ids are accepted and reduced with atomics.
+ * out f32[batch, ...]: row s is written at out + s*out_stride (out_stride >= D floats).
+ * workspace: annc_embed_bag_workspace_bytes(batch) bytes of device memory. */
+typedef struct annc_bag_table {
+  const float* table;          /* f32[rows, D]                         */
+  int64_t rows;                /* table rows (bounds check)            */
+  int64_t num_buckets;         /* modulus for id_kind 2                */
+  const void* ids;             /* [nnz]                                */
+  const int64_t* slice_input;  /* i64[nnz, ncols]                      */
+  int64_t nnz;
+  float* out;                  /* first output row of this table       */
+} annc_bag_table;
+
+size_t annc_embed_bag_workspace_bytes(int num_tables, int64_t batch);
+
+int annc_embed_bags_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                        int64_t dim, int id_kind, int64_t ncols, int32_t col, int combiner,
+                        int64_t batch, int64_t out_stride, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Reads the device-side error word the embedding kernels set (0 = clean,
+ * bit 0 = row index outside its table, bit 1 = segment id outside [0,batch)).
+ * Synchronises `stream`. */
+int annc_embed_bag_check(void* workspace, void* stream, int* error_bits);
+
+/* Measurement hooks: CUDA events made by annc_timer_create.  While a pair is set on
+ * the calling thread, annc_embed_bags_dev records `start` right before and `stop`
+ * right after its bag-reduce kernel (the prepass and the atomic route stay outside),
+ * so a benchmark can time that kernel alone inside a longer step.  NULL, NULL clears. */
+void* annc_timer_create(void);
+void annc_timer_destroy(void* event);
+int annc_timer_elapsed_ms(void* start, void* stop, float* ms);
+void annc_embed_bag_set_timing_events(void* start, void* stop);
+
+/* GEMM core: C = act(alpha * op(A) * op(B) + beta * C + addend + bias), row-major. */
+enum { ANNC_ACT_NONE = 0, ANNC_ACT_RELU = 1, ANNC_ACT_SIGMOID = 2 };
+enum { ANNC_B_PLAIN = 0, ANNC_B_KN4 = 1 };
+enum { ANNC_MATH_AUTO = 0, ANNC_MATH_FP32 = 1, ANNC_MATH_TF32 = 2, ANNC_MATH_BF16 = 3 };
+
+typedef struct annc_gemm_desc {
+  int32_t trans_a, trans_b;
+  int64_t m, n, k;
+  int64_t batch;                 /* >= 1 */
+  int64_t lda, ldb, ldc, ld_addend;
+  int64_t stride_a, stride_b, stride_c, stride_addend; /* per batch, in floats; 0 = shared */
+  float alpha, beta;
+  const float* a;
+  const float* b;
+  float* c;
+  const float* addend;           /* [m,n] or NULL */
+  const float* bias;             /* [n] or NULL   */
+  int32_t activation;            /* ANNC_ACT_*    */
+  int32_t b_format;              /* ANNC_B_*; KN4 = python/annc/optimize/data_pack.py layout */
+  int32_t math;                  /* ANNC_MATH_*   */
+  int32_t reserved;
+} annc_gemm_desc;
+
+int annc_gemm_run(const annc_gemm_desc* desc, void* stream);
+/* Name of the kernel family annc_gemm_run would pick ("tcgen05_tf32", "simt_fp32", ...). */
+const char* annc_gemm_kernel_name(const annc_gemm_desc* desc);
+
+/* kn4 <-> [K,N] conversion on the device (layout of python/annc/optimize/data_pack.py,
+ * vector 12, tiles 352 x 128, python/annc/optimize/constant_folding.py:77-88). */
+int annc_kn4_pack_dev(const float* b_kn, float* b_packed, int64_t k, int64_t n, void* stream);
+int annc_kn4_unpack_dev(const float* b_packed, float* b_kn, int64_t k, int64_t n, void* stream);
+/* Host: offset of element (k, n) inside the packed buffer. */
+int64_t annc_kn4_offset(int64_t K, int64_t N, int64_t k, int64_t n);
+
+/* Row softmax, fp32 (annc/service/cpu/xla/xnnpack_ops.cc:30-74). */
+int annc_softmax_dev(const float* in, float* out, int64_t batch, int64_t channels, void* stream);
+/* __pooling (annc/service/cpu/graph_opt.cc:131-176). */
+int annc_pooling_dev(float* out, const int64_t* arg, const float* mul_out, int64_t m, int64_t k,
+                     int64_t n, const int64_t slice_starts[3], const int64_t slice_limits[3],
+                     void* stream);
+/* __reduce_mean (annc/service/cpu/reduce_rewriter.cc:31-46): out[i] = sum_j |value[i*m+j]| / m. */
+int annc_reduce_mean_dev(float* out, const float* value, int64_t m, int64_t n, void* stream);
+/* ArgMax over the last dim, ties -> last (annc/service/cpu/xla/kernel_selector.cc:317-340). */
+int annc_argmax_dev(int64_t rows, int64_t n, const float* invals, const int32_t* inidxs,
+                    float init_value, int32_t init_idx, float* outvals, int32_t* outidxs,
+                    void* stream);
+/* y = alpha*op(A)x + beta*y (annc/service/cpu/xla/kernel_selector.cc:168-178). */
+int annc_gemv_dev(int trans_a, int64_t m, int64_t n, float alpha, const float* a, const float* x,
+                  float beta, float* y, void* stream);
+
+/* DLRM dot interaction on the device: Z f32[batch, F, D] (row stride z_stride floats per
+ * sample) -> out[b, :] = [ Z[b,0,:] (D values) | strict lower triangle of Z[b] Z[b]^T in
+ * row-major (i,j<i) order | zero padding up to out_stride ].  This is the
+ * `__batch_matmul` of Z by its transpose (annc/service/cpu/gemm_rewriter.cc:187-216)
+ * followed by the triangle gather and concat that XLA fuses around it. */
+int annc_dot_interaction_dev(const float* z, int64_t batch, int features, int dim,
+                             int64_t z_stride, float* out, int64_t out_stride, void* stream);
+
+/* ---------------------------------------------------------------- reference symbols
+ * XLA custom-call targets (annc/service/cpu/kdnn_rewriter.h:140-155).  `in` holds the
+ * fusion operands followed by one s64 vector [dims..., minor_to_major...] per operand
+ * (annc/service/hlo_util.h:14-33). */
+void __matmul(void* out, const void** in);          /* gemm_rewriter.cc:161-185 */
+void __layout_matmul(void* out, const void** in);   /* gemm_rewriter.cc:136-159 */
+void __batch_matmul(void* out, const void** in);    /* gemm_rewriter.cc:187-216 */
+void __matmul_add(void* out, const void** in);      /* gemm_rewriter.cc:218-247 */
+void __matmul_add_relu(void* out, const void** in); /* gemm_rewriter.cc:249-281 */
+void __reduce_mean(void* out, const void** in);     /* reduce_rewriter.cc:31-46 */
+void __pooling(void* out, void** in);               /* graph_opt.cc:131-176     */
+
+/* XLA:CPU runtime symbols (annc/service/cpu/xla/xnnpack_ops.h:26-29,
+ * annc/service/cpu/xla/kernel_selector.h:94-183).  The reference declares the
+ * kernel-selector functions with C++ linkage in xla::cpu; the library exports them
+ * under both the plain and the mangled names. */
+void __xla_cpu_runtime_XnnPackSoftMaxND(const void* run_options_ptr, void* in, void* out,
+                                        int64_t batch_size, int64_t channels);
+#define ANNC_DECL_GEMM(name)                                                              \
+  void __xla_cpu_runtime_KernelSelectorGEMM##name(const void* run_options_ptr, bool trA,  \
+                                                  bool trB, const float* A, const float* B,\
+                                                  int M, int N, int K, float alpha,        \
+                                                  float beta, float* C);
+#define ANNC_DECL_B3D(name)                                                                \
+  void __xla_cpu_runtime_KernelSelectorBatch3D##name(const void* run_options_ptr, bool trA,\
+                                                     bool trB, const float* A,             \
+                                                     const float* B, int P, int M, int N,  \
+                                                     int K, float* C);
+#define ANNC_DECL_B4D(name)                                                                \
+  void __xla_cpu_runtime_KernelSelectorBatch4D##name(const void* run_options_ptr, bool trA,\
+                                                     bool trB, const float* A,             \
+                                                     const float* B, int Q, int P, int M,  \
+                                                     int N, int K, float* C);
+#define ANNC_DECL_GEMV(name)                                                              \
+  void __xla_cpu_runtime_KernelSelectorGEMV##name(const void* run_options_ptr, bool trA,  \
+                                                  const float* A, const float* X, int M,  \
+                                                  int N, float alpha, float beta, float* Y);
+#define ANNC_DECL_ARGMAX(name)                                                            \
+  void __xla_cpu_runtime_ArgMax3D##name(const void* run_options_ptr, int B, int M, int N, \
+                                        float* invals, int32_t* inidxs, float init_value, \
+                                        int32_t init_idx, float* outvals, int32_t* outidxs);
+ANNC_DECL_GEMM(Sequential) ANNC_DECL_GEMM(Parallel) ANNC_DECL_GEMM(MLIR) ANNC_DECL_GEMM(Empty)
+ANNC_DECL_B3D(Sequential) ANNC_DECL_B3D(Parallel) ANNC_DECL_B3D(MLIR) ANNC_DECL_B3D(Empty)
+ANNC_DECL_B4D(Sequential) ANNC_DECL_B4D(Parallel) ANNC_DECL_B4D(MLIR) ANNC_DECL_B4D(Empty)
+ANNC_DECL_GEMV() ANNC_DECL_GEMV(MLIR) ANNC_DECL_GEMV(Empty)
+ANNC_DECL_ARGMAX(Parallel) ANNC_DECL_ARGMAX(Sequential) ANNC_DECL_ARGMAX(Empty)
+#undef ANNC_DECL_GEMM
+#undef ANNC_DECL_B3D
+#undef ANNC_DECL_B4D
+#undef ANNC_DECL_GEMV
+#undef ANNC_DECL_ARGMAX
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* ANNC_B200_H_ */

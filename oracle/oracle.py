@@ -419,3 +419,61 @@ def flag_enabled_ref(flags_env: str | None, name: str) -> bool:
     l = C.CDLL(_FLAGS_REF_PATH)
     return bool(l.annc_ref_flag_enabled(None if flags_env is None else flags_env.encode(),
                                         name.encode()))
+
+
+# ---------------------------------------------------------------- DLRM-style model on the CPU
+
+def embed_bags_tables(tables, table_rows, raw_ids, slice_inputs, batch, dim, out, out_slots,
+                      out_first, combiner=0, col=0, threads=1) -> None:
+    """Hash-bucket mapping (E1) + segment reduce (E3) of every table into
+    out[batch, out_slots, dim] starting at slot out_first; one table per thread."""
+    n = len(tables)
+    tabs = [_c(t, np.float32) for t in tables]
+    ids = [_c(i, np.int64) for i in raw_ids]
+    segs = [_c(s, np.int64) for s in slice_inputs]
+    tp = (f32p * n)(*[_p(t, f32p) for t in tabs])
+    ip = (i64p * n)(*[_p(i, i64p) for i in ids])
+    sp = (i64p * n)(*[_p(s, i64p) for s in segs])
+    rows = np.asarray(table_rows, np.int64)
+    nnz = np.array([i.shape[0] for i in ids], np.int64)
+    assert out.dtype == np.float32 and out.flags.c_contiguous
+    lib().oracle_embed_bags_tables(C.c_int(n), tp, _p(rows, i64p), C.c_int64(dim), ip, sp,
+                                   _p(nnz, i64p), C.c_int64(segs[0].shape[1]), C.c_int32(col),
+                                   C.c_int(combiner), C.c_int64(batch), _p(out, f32p),
+                                   C.c_int64(out_slots), C.c_int64(out_first), C.c_int(threads))
+
+
+def host_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+def dlrm_forward(model, sample: int | None = None, threads: int = 1) -> np.ndarray:
+    """CPU forward of the DLRM-style model the way the reference's operators would run it:
+    bottom MLP as __matmul_add_relu calls (OpenBLAS sgemm + bias add + max, gemm_rewriter.cc
+    :249-281), per-table hash-bucket + KPFusedSparseSegmentReduce sum pooling, dot interaction
+    as __batch_matmul of Z by its transpose and the strict lower triangle, top MLP with a final
+    sigmoid.  ``sample`` limits the pass to the first `sample` samples of the batch."""
+    emb = model.emb
+    B = emb.batch if sample is None else min(sample, emb.batch)
+    x = _c(model.dense[:B], np.float32)
+    for w, b in model.bottom:
+        x = np.maximum(x @ w + b, np.float32(0))
+    T = len(emb.tables)
+    F = T + 1
+    z = np.empty((B, F, emb.dim), np.float32)
+    z[:, 0, :] = x
+    ids, segs = [], []
+    for bag in emb.bags:
+        n = int(np.searchsorted(bag.slice_input[:, 0], B, side="left"))
+        ids.append(bag.raw_ids[:n])
+        segs.append(bag.slice_input[:n])
+    embed_bags_tables(emb.tables, [t.shape[0] for t in emb.tables], ids, segs, B, emb.dim, z, F, 1,
+                      threads=threads)
+    g = np.matmul(z, np.swapaxes(z, 1, 2))
+    li, lj = np.tril_indices(F, -1)
+    h = np.concatenate([z[:, 0, :], g[:, li, lj]], axis=1)
+    for i, (w, b) in enumerate(model.top):
+        h = h @ w + b
+        if i + 1 < len(model.top):
+            h = np.maximum(h, np.float32(0))
+    return (np.float32(1) / (np.float32(1) + np.exp(-h, dtype=np.float32))).astype(np.float32)

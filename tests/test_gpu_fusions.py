@@ -1,0 +1,85 @@
+"""Parity of the softmax, pooling, reduce-mean, arg-max and dot-interaction kernels
+with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+ops = pytest.importorskip("annc_b200.ops")
+from annc_b200 import device, synth  # noqa: E402
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("shape", [(1, 2), (7, 33), (64, 128), (16384, 256), (100, 1000), (5, 1024), (3, 4100)])
+def test_softmax(shape):
+    rng = np.random.default_rng(shape[1])
+    x = (rng.standard_normal(shape) * 3).astype(np.float32)
+    want = oracle.softmax(x)
+    got = ops.xla_softmax(_dev(x)).cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-5  # absolute, on probabilities
+    np.testing.assert_allclose(got.sum(-1), 1.0, atol=1e-5)
+    if x.size < 100000:
+        assert np.abs(ops.xla_softmax(x) - want).max() <= 1e-5
+
+
+def test_bmm_then_softmax_config():
+    """batch_matmul Q[64,256,64] . K^T[64,64,256] then row softmax over the [16384,256] view."""
+    q, kt = synth.batch_matmul_softmax_case(0)
+    s = ops.xla_batch_matmul(_dev(q), _dev(kt))
+    p = ops.xla_softmax(s.view(64 * 256, 256))
+    want = oracle.softmax(oracle.batch_matmul(q, kt).reshape(-1, 256))
+    assert np.abs(p.cpu().numpy() - want).max() <= 2e-3  # scores may come from the TF32 route
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 30, 16), (5, 6, 4), (1, 1, 1), (33, 7, 50)])
+def test_pooling(m, k, n):
+    rng = np.random.default_rng(m)
+    arg = rng.integers(-1, 3, (m, k)).astype(np.int64)
+    arg[0] = 0  # a row with no positive entry -> zeros
+    mo = rng.standard_normal((m, k, n)).astype(np.float32)
+    for ss, sl in [([0, 0, 0], [m, k, n]), ([0, 1, 0], [m, k, max(1, n - 1)])]:
+        want = oracle.pooling(arg, mo, ss, sl)
+        np.testing.assert_array_equal(ops.xla_pooling(arg, mo, ss, sl), want)
+        np.testing.assert_array_equal(ops.xla_pooling(_dev(arg), _dev(mo), ss, sl).cpu().numpy(), want)
+
+
+def test_reduce_mean():
+    rng = np.random.default_rng(0)
+    m, n = 37, 19
+    v = rng.standard_normal(m * n).astype(np.float32)
+    want = oracle.reduce_mean(v, m, n)
+    np.testing.assert_allclose(ops.xla_reduce_mean(v, m, n), want, rtol=1e-5)
+
+
+@pytest.mark.parametrize("variant", ["Sequential", "Parallel"])
+def test_argmax_last_wins(variant):
+    rng = np.random.default_rng(1)
+    vals = rng.integers(0, 5, (3, 7, 100)).astype(np.float32)  # many ties
+    vals[0, 0, :] = -5.0  # all below init -> init pair survives
+    idxs = rng.integers(0, 1000, vals.shape).astype(np.int32)
+    wv, wi = oracle.argmax3d(vals, idxs, -1.0, 77)
+    gv, gi = ops.selector_argmax3d(variant, vals, idxs, -1.0, 77)
+    np.testing.assert_array_equal(gv, wv)
+    np.testing.assert_array_equal(gi, wi)
+
+
+@pytest.mark.parametrize("F,D", [(27, 64), (4, 16), (32, 32), (9, 128)])
+def test_dot_interaction(F, D):
+    rng = np.random.default_rng(F)
+    batch = 333
+    z = rng.standard_normal((batch, F, D)).astype(np.float32)
+    tri = F * (F - 1) // 2
+    width = (D + tri + 3) // 4 * 4
+    out = torch.full((batch, width), 9.0, device="cuda")
+    device.dot_interaction(_dev(z), out)
+    g = oracle.batch_matmul(z, np.swapaxes(z, 1, 2))
+    li, lj = np.tril_indices(F, -1)
+    want = np.concatenate([z[:, 0, :], g[:, li, lj], np.zeros((batch, width - D - tri), np.float32)], 1)
+    got = out.cpu().numpy()
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
