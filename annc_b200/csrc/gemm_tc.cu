@@ -1,6 +1,493 @@
+// TF32 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   C[M,N] = act(alpha * A[M,K] * B + beta * C + addend + bias)
+//
+// One CTA computes a 128 x 128 tile of C with UMMA 128x128x8 (kind::tf32), fp32
+// accumulators in 128 TMEM columns.  Shared memory holds a ring of stages, each one
+// 128 x 32 floats of A and 32 x 128 floats of B, both in the 128-byte-swizzle
+// layout the UMMA shared-memory descriptors name.
+//
+//   warp 0      A tiles (and B when it is stored [N,K]) by TMA, cp.async.bulk.tensor
+//               without multicast, completion counted on the stage's "full" mbarrier
+//   warp 1      TMEM allocation, tcgen05.mma issue by one thread, tcgen05.commit on
+//               the stage's "empty" mbarrier and, after the last k-step, on "done"
+//   warps 2-5   B loader when B is stored [K,N] or in the kn4 prepacked layout:
+//               16-byte cp.async from global straight into the N-major swizzled
+//               stage (the packed layout is consumed as it lies in memory, no
+//               unpacked copy is made); then the epilogue: tcgen05.ld of the
+//               accumulator rows, alpha/beta/addend/bias/activation in registers,
+//               16-byte stores.
+//
+// fp32 operands are fed unchanged to kind::tf32, which reads the upper 19 bits.
+// Two CTAs fit one SM (3 stages = 96 KB each), so one CTA's epilogue overlaps the
+// other's main loop.  Every mbarrier wait is bounded: when a wait runs out the CTA
+// raises a device flag (read by annc_gemm_check), leaves its loops, frees its TMEM
+// and returns.
+#include <cuda.h>
+
+#include <cstdint>
+#include <cstring>
+
 #include "common.h"
 #include "gemm.h"
-namespace annc { namespace gemm {
-bool tc_supported(const annc_gemm_desc&, int) { return false; }
-int run_tc(const annc_gemm_desc&, int, cudaStream_t) { return fail(ANNC_ERR_UNSUPPORTED, "tc gemm not built"); }
-}}
+#include "kn4.h"
+
+namespace annc {
+namespace gemm {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32;
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * BK * 4;  // 16 KB
+constexpr int B_BYTES = BN * BK * 4;  // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;      // 6 warps
+constexpr int LOADER_THREADS = 128;   // warps 2..5
+constexpr int TMEM_COLS = 128;
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+
+enum BMode { B_TMA_NK = 0, B_PLAIN_KN = 1, B_KN4 = 2 };
+
+struct TcParams {
+  int M, N, K;
+  int b_mode;
+  const float* B;
+  long long ldb;
+  float* C;
+  long long ldc;
+  const float* addend;
+  long long ld_addend;
+  const float* bias;
+  float alpha, beta;
+  int act;
+};
+
+__device__ int g_gemm_error = 0;  // 1: an mbarrier wait ran out
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after about one second, or as soon as another role of the
+// CTA has given up (abort word in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_flag = 1;
+        atomicExch(&g_gemm_error, 1);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier when every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and
+// stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  if (act == ANNC_ACT_RELU) return fmaxf(v, 0.0f);
+  if (act == ANNC_ACT_SIGMOID) return __fdiv_rn(1.0f, 1.0f + expf(-v));
+  return v;
+}
+
+// ---------------------------------------------------------------- kernel
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // stages need 1024-byte alignment
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  // barrier block: full[STAGES], empty[STAGES], done, then tmem base word and abort word
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES, bar_done = bars + 16 * STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + 16 * STAGES + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  // A CTA of an earlier wave (or launch) gave up on a wait: do not start, fail fast.
+  if (*reinterpret_cast<volatile int*>(&g_gemm_error) != 0) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int KT = (p.K + BK - 1) / BK;
+  const bool b_by_loader = p.b_mode != B_TMA_NK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1 + (b_by_loader ? LOADER_THREADS : 0));
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      for (int it = 0; it < KT; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) break;
+        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+        mbar_expect_tx(bar_full + 8 * s, b_by_loader ? A_BYTES : STAGE_BYTES);
+        tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
+        if (!b_by_loader) tma_load_2d(sb, &tmap_b, it * BK, n0, bar_full + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A/B tf32, A K-major, B K- or N-major, N, M
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((b_by_loader ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      bool ok = true;
+      for (int it = 0; it < KT && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+        if (!ok) break;
+        fence_proxy_async();
+        tc_fence_after();
+        const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          // A, K-major: rows of 128 bytes, 8-row groups 1024 bytes apart; a k-step of 8
+          // tf32 is 32 bytes along the row.
+          const uint64_t ad = smem_desc(sa + kk * 32, 16, 1024);
+          // B, K-major ([N,K] source): same shape as A.  B, N-major ([K,N] / kn4 source):
+          // 32-column blocks of BK rows x 128 bytes, blocks 4096 bytes apart (leading
+          // offset), 8-row k groups 1024 bytes apart; a k-step of 8 is one k group.
+          const uint64_t bd = b_by_loader ? smem_desc(sb + kk * 1024, BK * 128, 1024)
+                                          : smem_desc(sb + kk * 32, 16, 1024);
+          umma_tf32(tmem_base, ad, bd, idesc, (it | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_empty + 8 * s);
+      }
+      if (ok) umma_commit(bar_done);
+    }
+  } else {
+    // ---------------- B loader (warps 2..5), then epilogue
+    const int lt = threadIdx.x - 64;  // 0..127
+    if (b_by_loader) {
+      // chunk column c (16 bytes = 4 floats of n) is fixed per thread; rows k = kr + 4 i
+      const int c = lt & 31, kr = lt >> 5;
+      const int n = n0 + c * 4;
+      const bool n_ok = n < p.N;
+      // kn4: position of this 4-column chunk inside its panel, fixed per thread
+      kn4::Chunk nc = {0, 0};
+      kn4::Panel pn = {0, 0};
+      if (p.b_mode == B_KN4 && n_ok) {
+        nc = kn4::axis_chunk(p.N, kn4::kTileN, n);
+        pn = kn4::panel_of(nc.len, n - nc.start);
+      }
+      const uint32_t dst_col = (uint32_t)(c >> 3) * (BK * 128);
+      const int cc = c & 7;
+      for (int it = 0; it < KT; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) break;
+        const uint32_t sb = base + s * STAGE_BYTES + A_BYTES;
+#pragma unroll
+        for (int i = 0; i < BK / 4; ++i) {
+          const int kl = kr + 4 * i;  // row inside the stage
+          const long long k = (long long)it * BK + kl;
+          const bool ok = n_ok && k < p.K;
+          const float* src = p.B;
+          if (ok) {
+            if (p.b_mode == B_KN4) {
+              const kn4::Chunk kc = kn4::axis_chunk(p.K, kn4::kTileK, k);
+              src = p.B + kc.start * p.N + kc.len * (nc.start + pn.start) +
+                    (k - kc.start) * pn.width + (n - nc.start - pn.start);
+            } else {
+              src = p.B + k * p.ldb + n;
+            }
+          }
+          const uint32_t dst = sb + dst_col + (uint32_t)kl * 128u + (uint32_t)((cc ^ (kl & 7)) << 4);
+          cp_async16(dst, src, ok ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(bar_full + 8 * s);
+      }
+      cp_async_wait_all();
+    }
+    // epilogue: warp w may touch TMEM lanes 32 (w % 4) .. 32 (w % 4) + 31
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    const bool done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag)) != 0;
+    tc_fence_after();
+    if (done) {
+      const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                       ((p.N & 3) == 0);
+      const bool add_vec = p.addend && ((p.ld_addend & 3) == 0) &&
+                           ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (row < p.M && n0 + c0 < p.N) {
+          float* crow = p.C + (long long)row * p.ldc + n0 + c0;
+          const float* arow = p.addend ? p.addend + (long long)row * p.ld_addend + n0 + c0 : nullptr;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int col = n0 + c0 + j;
+            if (col >= p.N) break;
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = p.alpha * __uint_as_float(r[j + e]);
+            if (vec) {
+              if (p.beta != 0.f) {
+                const float4 o = *reinterpret_cast<const float4*>(crow + j);
+                v[0] += p.beta * o.x; v[1] += p.beta * o.y; v[2] += p.beta * o.z; v[3] += p.beta * o.w;
+              }
+              if (arow) {
+                if (add_vec) {
+                  const float4 a = __ldg(reinterpret_cast<const float4*>(arow + j));
+                  v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) v[e] += __ldg(arow + j + e);
+                }
+              }
+              if (p.bias) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] += __ldg(p.bias + col + e);
+              }
+              float4 o;
+              o.x = act_apply(v[0], p.act); o.y = act_apply(v[1], p.act);
+              o.z = act_apply(v[2], p.act); o.w = act_apply(v[3], p.act);
+              *reinterpret_cast<float4*>(crow + j) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (col + e < p.N) {
+                  float x = v[e];
+                  if (p.beta != 0.f) x += p.beta * crow[j + e];
+                  if (arow) x += __ldg(arow + j + e);
+                  if (p.bias) x += __ldg(p.bias + col + e);
+                  crow[j + e] = act_apply(x, p.act);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D fp32 tensor [rows, cols] with row pitch ld floats; box = 32 columns x 128 rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+int make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return ANNC_OK;
+}
+
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool tc_supported(const annc_gemm_desc& d, int math) {
+  if (math != ANNC_MATH_TF32) return false;
+  if (d.batch != 1 || d.trans_a) return false;
+  if (d.m < 64 || d.n < 16 || d.k < 32) return false;
+  if (d.m > 128LL * 65535 || d.n > (1LL << 30) || d.k > (1LL << 30)) return false;
+  if (!al16(d.a) || (d.lda & 3) || (d.k & 3)) return false;  // TMA: 16-byte base and pitch
+  if (d.b_format == ANNC_B_KN4) return (d.n & 3) == 0 && al16(d.b);
+  if (d.trans_b) return al16(d.b) && (d.ldb & 3) == 0;       // [N,K] by TMA
+  return al16(d.b) && (d.ldb & 3) == 0 && (d.n & 3) == 0;    // [K,N] by 16-byte cp.async
+}
+
+int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
+  if (!tc_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 gemm: unsupported shape");
+  static bool attr_set = false;
+  if (!attr_set) {
+    ANNC_CUDA(cudaFuncSetAttribute(gemm_tf32_tcgen05_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set = true;
+  }
+  CUtensorMap ta, tb;
+  ANNC_TRY(make_map(&ta, d.a, d.m, d.k, d.lda));
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)d.m;
+  p.N = (int)d.n;
+  p.K = (int)d.k;
+  if (d.b_format == ANNC_B_KN4) {
+    p.b_mode = B_KN4;
+    tb = ta;
+  } else if (d.trans_b) {
+    p.b_mode = B_TMA_NK;
+    ANNC_TRY(make_map(&tb, d.b, d.n, d.k, d.ldb));
+  } else {
+    p.b_mode = B_PLAIN_KN;
+    tb = ta;
+  }
+  p.B = d.b;
+  p.ldb = d.ldb;
+  p.C = d.c;
+  p.ldc = d.ldc;
+  p.addend = d.addend;
+  p.ld_addend = d.ld_addend;
+  p.bias = d.bias;
+  p.alpha = d.alpha;
+  p.beta = d.beta;
+  p.act = d.activation;
+  dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM));
+  gemm_tf32_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, p);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int read_error_flag(int* flag) {
+  ANNC_CUDA(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
+  return ANNC_OK;
+}
+
+}  // namespace gemm
+}  // namespace annc
+
+extern "C" int annc_gemm_check(void* stream, int* timed_out) {
+  if (!timed_out) return annc::fail(ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  ANNC_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return annc::gemm::read_error_flag(timed_out);
+}

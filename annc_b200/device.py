@@ -124,3 +124,11 @@ def kn4_unpack(b_packed: torch.Tensor) -> torch.Tensor:
                                   C.c_int64(b_packed.shape[0]), C.c_int64(b_packed.shape[1]),
                                   _stream()))
     return out
+
+
+def gemm_timed_out() -> bool:
+    """True when a tensor-core GEMM CTA gave up on a bounded wait since the library was
+    loaded (annc_gemm_check; synchronises the current stream)."""
+    flag = C.c_int(0)
+    check(lib.annc_gemm_check(_stream(), C.byref(flag)))
+    return flag.value != 0

@@ -240,6 +240,9 @@ typedef struct annc_gemm_desc {
 } annc_gemm_desc;
 
 int annc_gemm_run(const annc_gemm_desc* desc, void* stream);
+/* Synchronises `stream` and reports whether a tensor-core GEMM CTA has given up on one of
+ * its bounded mbarrier waits since the library was loaded (its output is then invalid). */
+int annc_gemm_check(void* stream, int* timed_out);
 /* Name of the kernel family annc_gemm_run would pick ("tcgen05_tf32", "simt_fp32", ...). */
 const char* annc_gemm_kernel_name(const annc_gemm_desc* desc);
 
