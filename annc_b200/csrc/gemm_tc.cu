@@ -5,7 +5,8 @@
 // One CTA computes a 128 x 128 tile of C with UMMA 128x128x8 (kind::tf32), fp32
 // accumulators in 128 TMEM columns.  Shared memory holds a ring of stages, each one
 // 128 x 32 floats of A and 32 x 128 floats of B, both in the 128-byte-swizzle
-// layout the UMMA shared-memory descriptors name.
+// layout the UMMA shared-memory descriptors name (A and a K-major B: SWIZZLE_128B;
+// an N-major B: SWIZZLE_128B_BASE32B).
 //
 //   warp 0      A tiles (and B when it is stored [N,K]) by TMA, cp.async.bulk.tensor
 //               without multicast, completion counted on the stage's "full" mbarrier
@@ -167,13 +168,17 @@ __device__ __forceinline__ void tmem_ld_wait() {
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading and
 // stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   layout 2 = SWIZZLE_128B          (16-byte units XOR row % 8, 8-row atoms)
+//   layout 1 = SWIZZLE_128B_BASE32B  (32-byte units XOR row % 4, 4-row atoms): the one
+//              layout the tensor core accepts for an N-major (or M-major) tf32 operand.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;  // version
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  d |= (uint64_t)layout << 61;
   return d;
 }
 
@@ -258,12 +263,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int kk = 0; kk < BK / 8; ++kk) {
           // A, K-major: rows of 128 bytes, 8-row groups 1024 bytes apart; a k-step of 8
           // tf32 is 32 bytes along the row.
-          const uint64_t ad = smem_desc(sa + kk * 32, 16, 1024);
+          const uint64_t ad = smem_desc(sa + kk * 32, 16, 1024, 2);
           // B, K-major ([N,K] source): same shape as A.  B, N-major ([K,N] / kn4 source):
           // 32-column blocks of BK rows x 128 bytes, blocks 4096 bytes apart (leading
-          // offset), 8-row k groups 1024 bytes apart; a k-step of 8 is one k group.
-          const uint64_t bd = b_by_loader ? smem_desc(sb + kk * 1024, BK * 128, 1024)
-                                          : smem_desc(sb + kk * 32, 16, 1024);
+          // offset), 4-row k groups 512 bytes apart (stride offset); a k-step of 8 rows
+          // starts 1024 bytes after the previous one.
+          const uint64_t bd = b_by_loader ? smem_desc(sb + kk * 1024, BK * 128, 512, 1)
+                                          : smem_desc(sb + kk * 32, 16, 1024, 2);
           umma_tf32(tmem_base, ad, bd, idesc, (it | kk) != 0 ? 1u : 0u);
         }
         umma_commit(bar_empty + 8 * s);
@@ -307,7 +313,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               src = p.B + k * p.ldb + n;
             }
           }
-          const uint32_t dst = sb + dst_col + (uint32_t)kl * 128u + (uint32_t)((cc ^ (kl & 7)) << 4);
+          // 32-byte unit (cc >> 1) XOR (row % 4); the 16-byte half keeps its place
+          const uint32_t dst = sb + dst_col + (uint32_t)kl * 128u +
+                               (uint32_t)((((cc >> 1) ^ (kl & 3)) << 5) | ((cc & 1) << 4));
           cp_async16(dst, src, ok ? 16u : 0u);
         }
         cp_async_arrive_noinc(bar_full + 8 * s);
