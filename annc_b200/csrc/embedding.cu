@@ -85,10 +85,10 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
   if (ev1) cudaEventRecord(ev1, s);
   // Atomic route for tables whose segment ids were not sorted; the blocks return
   // at once for sorted tables.
-  dim3 sc_grid(grid_for(max_nnz, 8, 148 * 8), num_tables);
+  dim3 sc_grid(grid_for(max_nnz, 8, 148), num_tables);
   bag_scatter_kernel<<<sc_grid, 256, 0, s>>>(p, hdr, offsets);
   if (combiner == 1) {
-    dim3 mean_grid(grid_for(batch * dim, 256, 148 * 8), num_tables);
+    dim3 mean_grid(grid_for(batch * dim, 256, 148), num_tables);
     bag_scatter_mean_kernel<<<mean_grid, 256, 0, s>>>(p, hdr, offsets);
   }
   cudaError_t e = cudaGetLastError();
