@@ -3,6 +3,7 @@
 // follow the reference kernels so that its unit tests translate one to one.
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.h"
@@ -195,6 +196,67 @@ int annc_embed_bag_check(void* workspace, void* stream, int* error_bits) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   ANNC_CUDA(cudaMemcpyAsync(error_bits, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
   ANNC_CUDA(cudaStreamSynchronize(s));
+  return ANNC_OK;
+}
+
+// ---------------------------------------------------------------- bags without a workspace
+// Scratch of annc_embed_bags_static_dev: lives in the library image, so every GPU
+// that loads the library holds these 8 MiB + 512 B until the process exits.
+constexpr size_t kStaticBagInts = size_t(2) << 20;  // offsets: num_tables * (batch + 1) ints
+static __device__ __align__(256) unsigned char g_bag_scratch[kHeaderBytes + kStaticBagInts * sizeof(int)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+// In host code `g_bag_scratch` is only a handle for the runtime, never a device
+// address: the address is asked for once per device, with that device current.
+int static_scratch(void** out) {
+  int dev = -1;
+  ANNC_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ANNC_ERR_UNSUPPORTED, "device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    ANNC_CUDA(cudaGetSymbolAddress(&p, g_bag_scratch));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return ANNC_OK;
+}
+}  // namespace
+
+int annc_embed_bags_static_dev(const annc_bag_table* tables, int num_tables, int64_t dim,
+                               int id_kind, int64_t ncols, int32_t col, int combiner,
+                               int64_t batch, int64_t out_stride, int* error_bits_dev,
+                               void* stream) {
+  ANNC_REQUIRE(tables && num_tables >= 1, ANNC_ERR_INVALID_ARGUMENT, "no tables");
+  ANNC_REQUIRE(combiner == 0 || combiner == 1, ANNC_ERR_INVALID_ARGUMENT, "combiner must be 0 or 1");
+  ANNC_REQUIRE(id_kind >= 0 && id_kind <= 2, ANNC_ERR_INVALID_ARGUMENT, "id_kind must be 0, 1 or 2");
+  ANNC_REQUIRE(col >= 0 && col < ncols, ANNC_ERR_INVALID_ARGUMENT, "Column index out of range");
+  ANNC_REQUIRE(dim >= 1 && out_stride >= dim && batch >= 0, ANNC_ERR_INVALID_ARGUMENT,
+               "bad dim / out_stride / batch");
+  if ((size_t)num_tables * (size_t)(batch + 1) > kStaticBagInts)
+    return fail(ANNC_ERR_UNSUPPORTED,
+                "annc_embed_bags_static_dev: num_tables * (batch + 1) = %lld exceeds the built-in "
+                "scratch of %lld entries; use annc_embed_bags_dev with a caller workspace",
+                (long long)num_tables * (long long)(batch + 1), (long long)kStaticBagInts);
+  void* ws = nullptr;
+  ANNC_TRY(static_scratch(&ws));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto* hdr = static_cast<BagHeader*>(ws);
+  int* offsets = reinterpret_cast<int*>(static_cast<char*>(ws) + kHeaderBytes);
+  // The array keeps the previous call's contents: the header (error word, unsorted
+  // marks) must start at zero; the offsets are fully rewritten by the prepass.
+  ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
+  for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
+    const int nt = std::min(kMaxTables, num_tables - t0);
+    ANNC_TRY(run_bags(tables + t0, nt, dim, id_kind, ncols, col, combiner, batch, out_stride, hdr,
+                      offsets + (size_t)t0 * (size_t)(batch + 1), s));
+  }
+  if (error_bits_dev)
+    ANNC_CUDA(cudaMemcpyAsync(error_bits_dev, &hdr->err_bits, sizeof(int), cudaMemcpyDeviceToDevice, s));
   return ANNC_OK;
 }
 

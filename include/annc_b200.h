@@ -202,6 +202,28 @@ int annc_embed_bags_dev(const annc_bag_table* tables /* host array */, int num_t
                         int64_t batch, int64_t out_stride, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Same operation as annc_embed_bags_dev for callers that must not allocate device
+ * memory and have none to lend: code running inside a framework callback where
+ * cudaMalloc is forbidden or would deadlock (an allocator hook, a stream-ordered
+ * region owned by somebody else), or a host that fixed its memory budget at start-up.
+ * No counterpart in the reference: its CPU kernels take their scratch from the heap.
+ * The bag offsets live in an 8 MiB + 512 B array inside the library image, which every
+ * GPU that loads the library keeps until the process exits.
+ *   - Limit: num_tables * (batch + 1) <= 2,097,152; larger requests fail with
+ *     ANNC_ERR_UNSUPPORTED and a message naming the limit.  Nothing is allocated or
+ *     freed, here or in any routine it calls.
+ *   - The first call on each device looks the array's address up (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the array and it keeps the last call's contents
+ *     (the part that must start at zero is cleared on `stream` by each call): two calls
+ *     that can overlap on the GPU (different streams, no ordering) race on it.
+ *   - error_bits_dev (device int, may be NULL) receives the error word that
+ *     annc_embed_bag_check would report, by an asynchronous copy on `stream`. */
+int annc_embed_bags_static_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                               int64_t dim, int id_kind, int64_t ncols, int32_t col, int combiner,
+                               int64_t batch, int64_t out_stride, int* error_bits_dev,
+                               void* stream);
+
 /* Reads the device-side error word the embedding kernels set (0 = clean,
  * bit 0 = row index outside its table, bit 1 = segment id outside [0,batch)).
  * Synchronises `stream`. */
