@@ -32,9 +32,12 @@ static void launch_bag(const BagParams& p, BagHeader* hdr, int* offsets, cudaStr
 // Launches prepass + bag kernels (+ the atomic route) for up to kMaxTables tables.
 static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, int id_kind,
                     int64_t ncols, int32_t col, int combiner, int64_t batch, int64_t out_stride,
-                    BagHeader* hdr, int* offsets, cudaStream_t s) {
+                    BagHeader* hdr, int* offsets, cudaStream_t s, int shard_count = 1,
+                    int shard_rank = 0) {
   BagParams p;
   memset(&p, 0, sizeof(p));
+  p.shard_count = shard_count;
+  p.shard_rank = shard_rank;
   p.num_tables = num_tables;
   p.id_kind = id_kind;
   p.combiner = combiner;
@@ -185,8 +188,36 @@ int annc_embed_bags_dev(const annc_bag_table* tables, int num_tables, int64_t di
   ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
   for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
     const int nt = std::min(kMaxTables, num_tables - t0);
+    if (t0 > 0) ANNC_CUDA(cudaMemsetAsync(hdr->unsorted, 0, sizeof(hdr->unsorted), s));
     ANNC_TRY(run_bags(tables + t0, nt, dim, id_kind, ncols, col, combiner, batch, out_stride, hdr,
                       offsets + (size_t)t0 * (size_t)(batch + 1), s));
+  }
+  return ANNC_OK;
+}
+
+int annc_embed_bags_sharded_dev(const annc_bag_table* tables, int num_tables, int64_t dim,
+                                int id_kind, int64_t ncols, int32_t col, int combiner,
+                                int64_t batch, int64_t out_stride, int shard_count,
+                                int shard_rank, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  ANNC_REQUIRE(tables && num_tables >= 1, ANNC_ERR_INVALID_ARGUMENT, "no tables");
+  ANNC_REQUIRE(combiner == 0 || combiner == 1, ANNC_ERR_INVALID_ARGUMENT, "combiner must be 0 or 1");
+  ANNC_REQUIRE(id_kind >= 0 && id_kind <= 2, ANNC_ERR_INVALID_ARGUMENT, "id_kind must be 0, 1 or 2");
+  ANNC_REQUIRE(col >= 0 && col < ncols, ANNC_ERR_INVALID_ARGUMENT, "Column index out of range");
+  ANNC_REQUIRE(dim >= 1 && out_stride >= dim, ANNC_ERR_INVALID_ARGUMENT, "bad dim / out_stride");
+  ANNC_REQUIRE(shard_count >= 1 && shard_rank >= 0 && shard_rank < shard_count,
+               ANNC_ERR_INVALID_ARGUMENT, "bad shard_count / shard_rank");
+  ANNC_REQUIRE(workspace && workspace_bytes >= annc_embed_bag_workspace_bytes(num_tables, batch),
+               ANNC_ERR_INVALID_ARGUMENT, "workspace too small");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto* hdr = static_cast<BagHeader*>(workspace);
+  int* offsets = reinterpret_cast<int*>(static_cast<char*>(workspace) + kHeaderBytes);
+  ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
+  for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
+    const int nt = std::min(kMaxTables, num_tables - t0);
+    if (t0 > 0) ANNC_CUDA(cudaMemsetAsync(hdr->unsorted, 0, sizeof(hdr->unsorted), s));
+    ANNC_TRY(run_bags(tables + t0, nt, dim, id_kind, ncols, col, combiner, batch, out_stride, hdr,
+                      offsets + (size_t)t0 * (size_t)(batch + 1), s, shard_count, shard_rank));
   }
   return ANNC_OK;
 }
@@ -252,6 +283,7 @@ int annc_embed_bags_static_dev(const annc_bag_table* tables, int num_tables, int
   ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
   for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
     const int nt = std::min(kMaxTables, num_tables - t0);
+    if (t0 > 0) ANNC_CUDA(cudaMemsetAsync(hdr->unsorted, 0, sizeof(hdr->unsorted), s));
     ANNC_TRY(run_bags(tables + t0, nt, dim, id_kind, ncols, col, combiner, batch, out_stride, hdr,
                       offsets + (size_t)t0 * (size_t)(batch + 1), s));
   }

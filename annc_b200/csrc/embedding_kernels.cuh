@@ -45,6 +45,8 @@ struct BagParams {
   long long batch;
   long long dim;
   long long out_stride;
+  int shard_count;  // row sharding: this rank owns rows r with r % shard_count == shard_rank,
+  int shard_rank;   // stored at local row r / shard_count (the reference's mod-partition rule)
 };
 
 // ---- prepass: CSR offsets from the (sorted) segment column --------------------
@@ -79,6 +81,14 @@ __device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, l
   if (id_kind == 0) return (long long)((const int*)ids)[i];
   if (id_kind == 1) return ((const long long*)ids)[i];
   return (long long)(((const unsigned long long*)ids)[i] % num_buckets);
+}
+
+// Row sharding.  Returns the local row, or -2 when another rank owns the row.
+constexpr long long kNotMine = -2;
+__device__ __forceinline__ long long shard_row(long long r, int shard_count, int shard_rank) {
+  if (shard_count <= 1 || r < 0) return r;
+  if ((int)(r % shard_count) != shard_rank) return kNotMine;
+  return r / shard_count;
 }
 
 __device__ __forceinline__ float4 ldg4(const float* p) {
@@ -132,8 +142,9 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   for (int base = start; base < end; base += LANES) {
     long long my = -1;
     if (base + lane < end) {
-      my = load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets);
-      if (my < 0 || my >= T.rows) {
+      my = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets), p.shard_count,
+                     p.shard_rank);
+      if (my != kNotMine && (my < 0 || my >= T.rows)) {
         atomicOr(&hdr->err_bits, kErrRow);
         my = -1;
       }
@@ -204,7 +215,9 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
     const long long c = c0 + lane;
     float acc = 0.f;
     for (int i = start; i < end; ++i) {
-      long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
+      long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+                              p.shard_rank);
+      if (r == kNotMine) continue;
       if (r < 0 || r >= T.rows) {
         if (lane == 0 && c0 == 0) atomicOr(&hdr->err_bits, kErrRow);
         continue;
@@ -227,13 +240,15 @@ bag_scatter_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < T.nnz;
        i += warps) {
     long long seg = T.seg[i * p.ncols + p.col];
-    long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
+    long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+                            p.shard_rank);
     if (seg < 0 || seg >= p.batch) continue;  // flagged by the prepass
+    if (lane == 0) atomicAdd(&counts[seg], 1);  // bag length counts every rank's lookups
+    if (r == kNotMine) continue;
     if (r < 0 || r >= T.rows) {
       if (lane == 0) atomicOr(&hdr->err_bits, kErrRow);
       continue;
     }
-    if (lane == 0) atomicAdd(&counts[seg], 1);
     float* orow = T.out + seg * p.out_stride;
     for (long long c = lane; c < p.dim; c += 32) atomicAdd(orow + c, __ldg(T.table + r * p.dim + c));
   }

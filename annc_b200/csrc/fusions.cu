@@ -227,6 +227,28 @@ dot_interaction_kernel(const float* __restrict__ z, long long batch, int F, long
   for (long long e = D + tri + lane; e < out_stride; e += 32) ob[e] = 0.f;
 }
 
+// ---- sum of partial pooled vectors, ascending part order (deterministic).
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const float* __restrict__ src, int parts, long long part_stride, long long rows,
+                    long long width4, long long src_stride, float* __restrict__ out,
+                    long long out_stride) {
+  const long long total = rows * width4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long r = e / width4, c = (e - r * width4) * 4;
+    const float* s0 = src + r * src_stride + c;
+    float4 acc = __ldg(reinterpret_cast<const float4*>(s0));
+    for (int p = 1; p < parts; ++p) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(s0 + p * part_stride));
+      acc.x = __fadd_rn(acc.x, v.x);
+      acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z);
+      acc.w = __fadd_rn(acc.w, v.w);
+    }
+    *reinterpret_cast<float4*>(out + r * out_stride + c) = acc;
+  }
+}
+
 }  // namespace
 }  // namespace annc
 
@@ -301,6 +323,23 @@ int annc_gemv_dev(int trans_a, int64_t m, int64_t n, float alpha, const float* a
   } else {
     gemv_t_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(m, n, alpha, a, x, beta, y);
   }
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int64_t rows,
+                          int64_t width, int64_t src_stride, float* out, int64_t out_stride,
+                          void* stream) {
+  ANNC_REQUIRE(src && out && parts >= 1, ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  ANNC_REQUIRE((width & 3) == 0 && (src_stride & 3) == 0 && (out_stride & 3) == 0 &&
+                   (part_stride & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+               ANNC_ERR_INVALID_ARGUMENT, "sum_partials needs 16-byte aligned rows");
+  if (rows * width <= 0) return ANNC_OK;
+  long long g = (rows * (width / 4) + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  sum_partials_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, parts, part_stride, rows, width / 4, src_stride, out, out_stride);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

@@ -125,6 +125,60 @@ __global__ void __launch_bounds__(256) sgemm_n1_kernel(annc_gemm_desc d) {
   }
 }
 
+// k <= 16 with row-major A and B (the first DLRM layer, 13 dense features): the work is
+// writing C.  A thread keeps its four columns of B in registers, 64 rows of A sit in
+// shared memory, every output row is written with coalesced 16-byte stores.
+constexpr int SK_ROWS = 64, SK_MAXK = 16;
+__global__ void __launch_bounds__(128) sgemm_smallk_kernel(annc_gemm_desc d) {
+  __shared__ float As[SK_ROWS][SK_MAXK];
+  const long long m0 = (long long)blockIdx.y * SK_ROWS;
+  const long long col = ((long long)blockIdx.x * 128 + threadIdx.x) * 4;
+  for (int e = threadIdx.x; e < SK_ROWS * SK_MAXK; e += 128) {
+    const int r = e / SK_MAXK, k = e % SK_MAXK;
+    As[r][k] = (m0 + r < d.m && k < d.k) ? d.a[(m0 + r) * d.lda + k] : 0.f;
+  }
+  float4 w[SK_MAXK];
+#pragma unroll
+  for (int k = 0; k < SK_MAXK; ++k) {
+    w[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < d.k && col < d.n) w[k] = __ldg(reinterpret_cast<const float4*>(d.b + k * d.ldb + col));
+  }
+  float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (d.bias && col < d.n) bias = __ldg(reinterpret_cast<const float4*>(d.bias + col));
+  __syncthreads();
+  if (col >= d.n) return;
+  const int rows = (int)(d.m - m0 < SK_ROWS ? d.m - m0 : SK_ROWS);
+  for (int r = 0; r < rows; ++r) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < SK_MAXK; ++k) {
+      const float a = As[r][k];
+      acc.x = fmaf(a, w[k].x, acc.x);
+      acc.y = fmaf(a, w[k].y, acc.y);
+      acc.z = fmaf(a, w[k].z, acc.z);
+      acc.w = fmaf(a, w[k].w, acc.w);
+    }
+    float* crow = d.c + (m0 + r) * d.ldc + col;
+    float v[4] = {d.alpha * acc.x, d.alpha * acc.y, d.alpha * acc.z, d.alpha * acc.w};
+    if (d.beta != 0.f) {
+      const float4 o = *reinterpret_cast<const float4*>(crow);
+      v[0] += d.beta * o.x; v[1] += d.beta * o.y; v[2] += d.beta * o.z; v[3] += d.beta * o.w;
+    }
+    if (d.addend) {
+      const float4 a4 = __ldg(reinterpret_cast<const float4*>(d.addend + (m0 + r) * d.ld_addend + col));
+      v[0] += a4.x; v[1] += a4.y; v[2] += a4.z; v[3] += a4.w;
+    }
+    float4 o;
+    o.x = apply_act(v[0] + bias.x, d.activation);
+    o.y = apply_act(v[1] + bias.y, d.activation);
+    o.z = apply_act(v[2] + bias.z, d.activation);
+    o.w = apply_act(v[3] + bias.w, d.activation);
+    *reinterpret_cast<float4*>(crow) = o;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 }  // namespace
 
 int run_simt(const annc_gemm_desc& d, cudaStream_t s, const BiasBroadcast* bb) {
@@ -132,6 +186,16 @@ int run_simt(const annc_gemm_desc& d, cudaStream_t s, const BiasBroadcast* bb) {
   if (d.n == 1 && d.batch == 1 && !d.trans_a && !bb && d.b_format == ANNC_B_PLAIN &&
       (d.trans_b || d.ldb == 1)) {
     sgemm_n1_kernel<<<(unsigned)((d.m + 7) / 8), 256, 0, s>>>(d);
+    ANNC_CUDA(cudaGetLastError());
+    return ANNC_OK;
+  }
+  if (d.k <= SK_MAXK && d.k >= 1 && d.m >= 1024 && d.batch == 1 && !d.trans_a && !d.trans_b && !bb &&
+      d.b_format == ANNC_B_PLAIN && (d.n & 3) == 0 && (d.ldb & 3) == 0 && (d.ldc & 3) == 0 &&
+      aligned16(d.b) && aligned16(d.c) && (!d.bias || aligned16(d.bias)) &&
+      (!d.addend || (aligned16(d.addend) && (d.ld_addend & 3) == 0)) &&
+      (d.m + SK_ROWS - 1) / SK_ROWS <= 65535) {
+    dim3 grid((unsigned)((d.n / 4 + 127) / 128), (unsigned)((d.m + SK_ROWS - 1) / SK_ROWS));
+    sgemm_smallk_kernel<<<grid, 128, 0, s>>>(d);
     ANNC_CUDA(cudaGetLastError());
     return ANNC_OK;
   }

@@ -8,11 +8,11 @@
 // layout the UMMA shared-memory descriptors name (A and a K-major B: SWIZZLE_128B;
 // an N-major B: SWIZZLE_128B_BASE32B).
 //
-//   warp 0      A tiles (and B when it is stored [N,K]) by TMA, cp.async.bulk.tensor
+//   warp 0      A tiles (and B when it is stored [N,K] or [K,N]) by TMA, cp.async.bulk.tensor
 //               without multicast, completion counted on the stage's "full" mbarrier
 //   warp 1      TMEM allocation, tcgen05.mma issue by one thread, tcgen05.commit on
 //               the stage's "empty" mbarrier and, after the last k-step, on "done"
-//   warps 2-5   B loader when B is stored [K,N] or in the kn4 prepacked layout:
+//   warps 2-5   B loader when B is stored in the kn4 prepacked layout:
 //               16-byte cp.async from global straight into the N-major swizzled
 //               stage (the packed layout is consumed as it lies in memory, no
 //               unpacked copy is made); then the epilogue: tcgen05.ld of the
@@ -20,8 +20,8 @@
 //               16-byte stores.
 //
 // fp32 operands are fed unchanged to kind::tf32, which reads the upper 19 bits.
-// Two CTAs fit one SM (3 stages = 96 KB each), so one CTA's epilogue overlaps the
-// other's main loop.  Every mbarrier wait is bounded: when a wait runs out the CTA
+// With 3 stages (96 KB) two CTAs fit one SM, so one CTA's epilogue overlaps the other's
+// main loop; small grids run 6 stages with one CTA per SM.  Every mbarrier wait is bounded: when a wait runs out the CTA
 // raises a device flag (read by annc_gemm_check), leaves its loops, frees its TMEM
 // and returns.
 #include <cuda.h>
@@ -38,16 +38,20 @@ namespace gemm {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 3;
+// 3 stages (96 KB): two CTAs share an SM and hide each other's prologue and epilogue;
+// 6 stages (192 KB): one CTA per SM with a deeper ring, for grids that cannot fill the
+// SMs twice and would otherwise wait on memory latency.
 constexpr int A_BYTES = BM * BK * 4;  // 16 KB
 constexpr int B_BYTES = BN * BK * 4;  // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;      // 6 warps
 constexpr int LOADER_THREADS = 128;   // warps 2..5
 constexpr int TMEM_COLS = 128;
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+constexpr size_t smem_bytes(int stages) { return 1024 + (size_t)stages * STAGE_BYTES + 256; }
 
-enum BMode { B_TMA_NK = 0, B_PLAIN_KN = 1, B_KN4 = 2 };
+// B sources: [N,K] by TMA (K-major operand), [K,N] by TMA (N-major operand, four
+// 32-column boxes per stage), kn4-packed by the cp.async loader (N-major operand).
+enum BMode { B_TMA_NK = 0, B_TMA_KN = 1, B_KN4 = 2 };
 
 struct TcParams {
   int M, N, K;
@@ -189,7 +193,8 @@ __device__ __forceinline__ float act_apply(float v, int act) {
 }
 
 // ---------------------------------------------------------------- kernel
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+template <int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, STAGES <= 3 ? 2 : 1)
 gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -208,7 +213,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int KT = (p.K + BK - 1) / BK;
-  const bool b_by_loader = p.b_mode != B_TMA_NK;
+  const bool b_by_loader = p.b_mode == B_KN4;
+  const bool b_n_major = p.b_mode != B_TMA_NK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -241,14 +247,20 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
         mbar_expect_tx(bar_full + 8 * s, b_by_loader ? A_BYTES : STAGE_BYTES);
         tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
-        if (!b_by_loader) tma_load_2d(sb, &tmap_b, it * BK, n0, bar_full + 8 * s);
+        if (p.b_mode == B_TMA_NK) {
+          tma_load_2d(sb, &tmap_b, it * BK, n0, bar_full + 8 * s);
+        } else if (p.b_mode == B_TMA_KN) {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j)  // one 32-column x BK-row box per block
+            tma_load_2d(sb + j * (BK * 128), &tmap_b, n0 + 32 * j, it * BK, bar_full + 8 * s);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
       // instruction descriptor: D fp32, A/B tf32, A K-major, B K- or N-major, N, M
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((b_by_loader ? 1u : 0u) << 16) |
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((b_n_major ? 1u : 0u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       bool ok = true;
       for (int it = 0; it < KT && ok; ++it) {
@@ -268,7 +280,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // 32-column blocks of BK rows x 128 bytes, blocks 4096 bytes apart (leading
           // offset), 4-row k groups 512 bytes apart (stride offset); a k-step of 8 rows
           // starts 1024 bytes after the previous one.
-          const uint64_t bd = b_by_loader ? smem_desc(sb + kk * 1024, BK * 128, 512, 1)
+          const uint64_t bd = b_n_major ? smem_desc(sb + kk * 1024, BK * 128, 512, 1)
                                           : smem_desc(sb + kk * 32, 16, 1024, 2);
           umma_tf32(tmem_base, ad, bd, idesc, (it | kk) != 0 ? 1u : 0u);
         }
@@ -284,12 +296,25 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int c = lt & 31, kr = lt >> 5;
       const int n = n0 + c * 4;
       const bool n_ok = n < p.N;
-      // kn4: position of this 4-column chunk inside its panel, fixed per thread
-      kn4::Chunk nc = {0, 0};
-      kn4::Panel pn = {0, 0};
-      if (p.b_mode == B_KN4 && n_ok) {
-        nc = kn4::axis_chunk(p.N, kn4::kTileN, n);
-        pn = kn4::panel_of(nc.len, n - nc.start);
+      // Position of this 4-column chunk inside its panel: fixed per thread.
+      int col_term = 0, width = 0, col_in = 0;
+      if (n_ok) {
+        const kn4::Chunk nc = kn4::axis_chunk(p.N, kn4::kTileN, n);
+        const kn4::Panel pn = kn4::panel_of(nc.len, n - nc.start);
+        col_term = (int)(nc.start + pn.start);
+        width = (int)pn.width;
+        col_in = (int)(n - nc.start - pn.start);
+      }
+      // K chunks: 352 rows each up to `k_uniform`, then the two chunks that share the
+      // remainder (kn4.h); all in 32-bit arithmetic, the element offset in 64-bit.
+      constexpr int TK = (int)kn4::kTileK;
+      int k_uniform = p.K, k_split = p.K, len0 = p.K < TK ? p.K : TK;
+      if (p.K >= TK && p.K % TK != 0) {
+        k_uniform = (p.K / TK - 1) * TK;
+        const int res = p.K - k_uniform;
+        int first = (res / 2) / 12 * 12;
+        if (res - first > first + 1) first += 12;
+        k_split = k_uniform + first;
       }
       const uint32_t dst_col = (uint32_t)(c >> 3) * (BK * 128);
       const int cc = c & 7;
@@ -301,17 +326,23 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int i = 0; i < BK / 4; ++i) {
           const int kl = kr + 4 * i;  // row inside the stage
-          const long long k = (long long)it * BK + kl;
+          const int k = it * BK + kl;
           const bool ok = n_ok && k < p.K;
           const float* src = p.B;
           if (ok) {
-            if (p.b_mode == B_KN4) {
-              const kn4::Chunk kc = kn4::axis_chunk(p.K, kn4::kTileK, k);
-              src = p.B + kc.start * p.N + kc.len * (nc.start + pn.start) +
-                    (k - kc.start) * pn.width + (n - nc.start - pn.start);
+            int start, len;
+            if (k < k_uniform) {
+              start = k / TK * TK;
+              len = len0;
+            } else if (k < k_split) {
+              start = k_uniform;
+              len = k_split - k_uniform;
             } else {
-              src = p.B + k * p.ldb + n;
+              start = k_split;
+              len = p.K - k_split;
             }
+            src = p.B + ((long long)start * p.N + (long long)len * col_term +
+                         (long long)((k - start) * width + col_in));
           }
           // 32-byte unit (cc >> 1) XOR (row % 4); the 16-byte half keeps its place
           const uint32_t dst = sb + dst_col + (uint32_t)kl * 128u +
@@ -328,58 +359,74 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag)) != 0;
     tc_fence_after();
     if (done) {
-      const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                       ((p.N & 3) == 0);
-      const bool add_vec = p.addend && ((p.ld_addend & 3) == 0) &&
-                           ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+      // Phase 1: this warp's 32 x 128 accumulator slab, scaled by alpha, goes to shared
+      // memory (the stage ring is idle once `done` has fired), rows padded to 132 floats.
+      constexpr int LD = BN + 4;
+      float* slab = reinterpret_cast<float*>(gen_base) + (size_t)q * 32 * LD;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (row < p.M && n0 + c0 < p.N) {
-          float* crow = p.C + (long long)row * p.ldc + n0 + c0;
-          const float* arow = p.addend ? p.addend + (long long)row * p.ld_addend + n0 + c0 : nullptr;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int col = n0 + c0 + j;
-            if (col >= p.N) break;
-            float v[4];
+        for (int j = 0; j < 32; j += 4) {
+          float4 v;
+          v.x = p.alpha * __uint_as_float(r[j]);
+          v.y = p.alpha * __uint_as_float(r[j + 1]);
+          v.z = p.alpha * __uint_as_float(r[j + 2]);
+          v.w = p.alpha * __uint_as_float(r[j + 3]);
+          *reinterpret_cast<float4*>(slab + lane * LD + c0 + j) = v;
+        }
+      }
+      __syncwarp();
+      // Phase 2: one output row per step, the 32 lanes cover its 128 columns with
+      // 16-byte accesses, so C, the addend and the bias are read and written coalesced.
+      const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+      const bool add_vec = p.addend && ((p.ld_addend & 3) == 0) &&
+                           ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+      const int col = n0 + lane * 4;
+      float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] = p.alpha * __uint_as_float(r[j + e]);
-            if (vec) {
-              if (p.beta != 0.f) {
-                const float4 o = *reinterpret_cast<const float4*>(crow + j);
-                v[0] += p.beta * o.x; v[1] += p.beta * o.y; v[2] += p.beta * o.z; v[3] += p.beta * o.w;
-              }
-              if (arow) {
-                if (add_vec) {
-                  const float4 a = __ldg(reinterpret_cast<const float4*>(arow + j));
-                  v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-                } else {
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) v[e] += __ldg(arow + j + e);
-                }
-              }
-              if (p.bias) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) v[e] += __ldg(p.bias + col + e);
-              }
-              float4 o;
-              o.x = act_apply(v[0], p.act); o.y = act_apply(v[1], p.act);
-              o.z = act_apply(v[2], p.act); o.w = act_apply(v[3], p.act);
-              *reinterpret_cast<float4*>(crow + j) = o;
+        for (int e = 0; e < 4; ++e)
+          if (col + e < p.N) bias4[e] = __ldg(p.bias + col + e);
+      }
+      const int rows_here = min(32, p.M - (m0 + q * 32));
+      for (int rr = 0; rr < rows_here; ++rr) {
+        if (col >= p.N) break;
+        const long long grow = (long long)(m0 + q * 32 + rr);
+        const float4 a4 = *reinterpret_cast<const float4*>(slab + rr * LD + lane * 4);
+        float v[4] = {a4.x, a4.y, a4.z, a4.w};
+        float* crow = p.C + grow * p.ldc + col;
+        const float* arow = p.addend ? p.addend + grow * p.ld_addend + col : nullptr;
+        if (vec && col + 3 < p.N) {
+          if (p.beta != 0.f) {
+            const float4 o = *reinterpret_cast<const float4*>(crow);
+            v[0] += p.beta * o.x; v[1] += p.beta * o.y; v[2] += p.beta * o.z; v[3] += p.beta * o.w;
+          }
+          if (arow) {
+            if (add_vec) {
+              const float4 a = __ldg(reinterpret_cast<const float4*>(arow));
+              v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
             } else {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                if (col + e < p.N) {
-                  float x = v[e];
-                  if (p.beta != 0.f) x += p.beta * crow[j + e];
-                  if (arow) x += __ldg(arow + j + e);
-                  if (p.bias) x += __ldg(p.bias + col + e);
-                  crow[j + e] = act_apply(x, p.act);
-                }
-              }
+              for (int e = 0; e < 4; ++e) v[e] += __ldg(arow + e);
+            }
+          }
+          float4 o;
+          o.x = act_apply(v[0] + bias4[0], p.act);
+          o.y = act_apply(v[1] + bias4[1], p.act);
+          o.z = act_apply(v[2] + bias4[2], p.act);
+          o.w = act_apply(v[3] + bias4[3], p.act);
+          *reinterpret_cast<float4*>(crow) = o;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (col + e < p.N) {
+              float x = v[e];
+              if (p.beta != 0.f) x += p.beta * crow[e];
+              if (arow) x += __ldg(arow + e);
+              crow[e] = act_apply(x + bias4[e], p.act);
             }
           }
         }
@@ -414,17 +461,20 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D fp32 tensor [rows, cols] with row pitch ld floats; box = 32 columns x 128 rows,
-// 128-byte swizzle, out-of-range elements read as zero.
-int make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld) {
+// 2-D fp32 tensor [rows, cols] with row pitch ld floats; box = 32 columns x box_rows rows;
+// out-of-range elements read as zero.  `n_major` picks the 128-byte swizzle with 32-byte
+// atoms that an N-major tf32 operand needs, else the plain 128-byte swizzle.
+int make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld,
+             int box_rows, bool n_major) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  const cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  n_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
   return ANNC_OK;
@@ -449,12 +499,14 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   if (!tc_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 gemm: unsupported shape");
   static bool attr_set = false;
   if (!attr_set) {
-    ANNC_CUDA(cudaFuncSetAttribute(gemm_tf32_tcgen05_kernel,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    ANNC_CUDA(cudaFuncSetAttribute(gemm_tf32_tcgen05_kernel<3>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(3)));
+    ANNC_CUDA(cudaFuncSetAttribute(gemm_tf32_tcgen05_kernel<6>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(6)));
     attr_set = true;
   }
   CUtensorMap ta, tb;
-  ANNC_TRY(make_map(&ta, d.a, d.m, d.k, d.lda));
+  ANNC_TRY(make_map(&ta, d.a, d.m, d.k, d.lda, BM, false));
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.M = (int)d.m;
@@ -465,10 +517,10 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
     tb = ta;
   } else if (d.trans_b) {
     p.b_mode = B_TMA_NK;
-    ANNC_TRY(make_map(&tb, d.b, d.n, d.k, d.ldb));
+    ANNC_TRY(make_map(&tb, d.b, d.n, d.k, d.ldb, BN, false));
   } else {
-    p.b_mode = B_PLAIN_KN;
-    tb = ta;
+    p.b_mode = B_TMA_KN;
+    ANNC_TRY(make_map(&tb, d.b, d.k, d.n, d.ldb, BK, true));
   }
   p.B = d.b;
   p.ldb = d.ldb;
@@ -481,7 +533,12 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   p.beta = d.beta;
   p.act = d.activation;
   dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM));
-  gemm_tf32_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, p);
+  const long long ctas = (long long)grid.x * grid.y;
+  if (ctas <= 148 * 3 / 2) {
+    gemm_tf32_tcgen05_kernel<6><<<grid, NUM_THREADS, smem_bytes(6), s>>>(ta, tb, p);
+  } else {
+    gemm_tf32_tcgen05_kernel<3><<<grid, NUM_THREADS, smem_bytes(3), s>>>(ta, tb, p);
+  }
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

@@ -1,0 +1,137 @@
+"""Per-operator timing on one GPU: GEMM TFLOP/s against the tensor peak and bandwidth
+kernels against the HBM peak, for the benchmark configurations and the DLRM layers.
+
+    python -m annc_b200.opbench [--only gemm|embed|misc] [--reps 20]
+
+CUDA events on the launching stream, 3 warm-ups, a 256 MB L2 flush between repetitions
+for working sets smaller than L2.  Prints one JSON line per case."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import device as dev
+from . import synth
+from ._lib import ACT_NONE, ACT_RELU, B_KN4, B_PLAIN, MATH_AUTO
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]) / 2, "measured"
+    except Exception:
+        return 6650.0, 1590.0 / 2, "fallback"
+
+
+_flush = None
+
+
+def time_ms(fn, reps, flush):
+    global _flush
+    if flush and _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        if flush:
+            _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return float(np.median(ts))
+
+
+def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False):
+    hbm, tf32, src = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((m, k), device="cuda", generator=g)
+    w = torch.randn((k, n), device="cuda", generator=g)
+    c = torch.empty((m, n), device="cuda")
+    bv = torch.randn(n, device="cuda", generator=g) if bias else None
+    ad = torch.randn((m, n), device="cuda", generator=g) if addend else None
+    kw = dict(m=m, n=n, k=k, bias=bv, addend=ad, activation=act, math=MATH_AUTO)
+    if bsrc == "nk":
+        b = w.t().contiguous()
+        kw["trans_b"] = True
+    elif bsrc == "kn4":
+        b = dev.kn4_pack(w)
+        kw["b_format"] = B_KN4
+    else:
+        b = w
+    names = []
+    fn = lambda: names.append(dev.gemm(a, b, c, **kw))
+    byt = 4 * (m * k + k * n + m * n * (2 if addend else 1))
+    ms = time_ms(fn, reps, flush=byt < (200 << 20))
+    fl = 2.0 * m * n * k
+    print(json.dumps({"op": name, "kernel": names[-1], "b": bsrc, "m": m, "n": n, "k": k,
+                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                      "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
+                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
+                      "peak": src}), flush=True)
+
+
+def run_gemm(reps):
+    gemm_case("matmul_add_relu C1", 512, 1024, 1024, reps, addend=True, act=ACT_RELU)
+    for bsrc in ("kn4", "kn", "nk"):
+        gemm_case("layout_matmul C2", 8192, 4096, 2048, reps, bsrc=bsrc)
+    for m in (128, 256, 512):
+        gemm_case("small-M sweep", m, 1024, 1024, reps)
+    for (k, n) in ((512, 256), (256, 64), (416, 512), (512, 256)):
+        for bsrc in ("kn", "nk"):
+            gemm_case("dlrm layer", 65536, n, k, reps, bsrc=bsrc, bias=True, act=ACT_RELU)
+    gemm_case("dlrm layer0 (K=13)", 65536, 512, 13, reps, bias=True, act=ACT_RELU)
+
+
+def run_embed(reps):
+    hbm, _, src = peaks()
+    w = synth.hash_bucket_bag_case(0)
+    up = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    out = torch.empty((w.batch, len(w.tables), w.dim), device="cuda")
+    plan = dev.BagPlan([up(t) for t in w.tables], [up(b.raw_ids) for b in w.bags],
+                       [up(b.slice_input) for b in w.bags], out, 0, w.batch)
+    ms = time_ms(plan.run, reps, flush=False)
+    byt = w.algorithmic_bytes()
+    print(json.dumps({"op": "embed_hash_bucket + segment sum C3 (prepass + bags)", "ms": round(ms, 4),
+                      "lookups": w.nnz, "gbs": round(byt / ms / 1e6, 1),
+                      "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
+                      "samples_per_s": round(w.batch / ms * 1e3), "peak": src}), flush=True)
+
+
+def run_misc(reps):
+    hbm, _, src = peaks()
+    x = torch.randn((16384, 256), device="cuda")
+    y = torch.empty_like(x)
+    ms = time_ms(lambda: dev.softmax(x, y), reps, flush=True)
+    print(json.dumps({"op": "softmax 16384x256", "ms": round(ms, 4),
+                      "gbs": round(2 * x.numel() * 4 / ms / 1e6, 1)}), flush=True)
+    z = torch.randn((65536, 27, 64), device="cuda")
+    o = torch.empty((65536, 416), device="cuda")
+    ms = time_ms(lambda: dev.dot_interaction(z, o), reps, flush=False)
+    byt = (z.numel() + o.numel()) * 4
+    print(json.dumps({"op": "dot interaction 65536x27x64", "ms": round(ms, 4),
+                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3)}),
+          flush=True)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="all")
+    ap.add_argument("--reps", type=int, default=20)
+    a = ap.parse_args()
+    if a.only in ("all", "gemm"):
+        run_gemm(a.reps)
+    if a.only in ("all", "embed"):
+        run_embed(a.reps)
+    if a.only in ("all", "misc"):
+        run_misc(a.reps)

@@ -202,6 +202,26 @@ int annc_embed_bags_dev(const annc_bag_table* tables /* host array */, int num_t
                         int64_t batch, int64_t out_stride, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Row-sharded variant for multi-GPU runs: the rank holds, for every table, the rows r
+ * with r % shard_count == shard_rank at local row r / shard_count (the mod-partition rule
+ * of annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71); `rows` in
+ * annc_bag_table is the local row count, num_buckets stays the global modulus.  Lookups
+ * owned by other ranks are skipped, so `out` receives this rank's partial sums; with
+ * combiner 1 the partial is scaled by 1/len(bag) (the full bag length), so the partials of
+ * all ranks add up to the mean.  The marks of unsorted tables are kept per launch of up to
+ * 64 tables. */
+int annc_embed_bags_sharded_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                                int64_t dim, int id_kind, int64_t ncols, int32_t col, int combiner,
+                                int64_t batch, int64_t out_stride, int shard_count,
+                                int shard_rank, void* workspace, size_t workspace_bytes,
+                                void* stream);
+/* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
+ * reduce step after the all-to-all of partial sums).  src part p starts at
+ * src + p * part_stride floats, rows are src_stride / out_stride floats apart. */
+int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int64_t rows,
+                          int64_t width, int64_t src_stride, float* out, int64_t out_stride,
+                          void* stream);
+
 /* Same operation as annc_embed_bags_dev for callers that must not allocate device
  * memory and have none to lend: code running inside a framework callback where
  * cudaMalloc is forbidden or would deadlock (an allocator hook, a stream-ordered

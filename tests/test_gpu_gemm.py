@@ -161,3 +161,17 @@ def test_bmm_add_sigmoid_errors(err):
         ops.kp_fused_batch_matmul_add_sigmoid(np.zeros(ls, np.float32), np.zeros(rs, np.float32),
                                               np.zeros(bs, np.float32))
     assert msg in e.value.message
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 512, 13), (1500, 64, 16), (1024, 8, 1)])
+def test_small_k_route(m, n, k):
+    """First DLRM layer shape class: k <= 16, bias + ReLU, fp32 exact route."""
+    rng = np.random.default_rng(k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    c = torch.empty((m, n), device="cuda")
+    name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, bias=_dev(bias), activation=1)
+    want = np.maximum(a @ b + bias, 0)
+    assert name == "simt_fp32"
+    assert nerr(c, want) <= 2e-5
