@@ -344,6 +344,16 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
   return ANNC_OK;
 }
 
+int annc_copy_rows_dev(float* dst, int64_t dst_stride, const float* src, int64_t src_stride,
+                       int64_t width, int64_t rows, void* stream) {
+  ANNC_REQUIRE(dst && src, ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  if (rows <= 0 || width <= 0) return ANNC_OK;
+  ANNC_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_stride * 4, src, (size_t)src_stride * 4,
+                              (size_t)width * 4, (size_t)rows, cudaMemcpyDeviceToDevice,
+                              static_cast<cudaStream_t>(stream)));
+  return ANNC_OK;
+}
+
 int annc_dot_interaction_dev(const float* z, int64_t batch, int features, int dim,
                              int64_t z_stride, float* out, int64_t out_stride, void* stream) {
   ANNC_REQUIRE(z && out, ANNC_ERR_INVALID_ARGUMENT, "null argument");

@@ -132,3 +132,51 @@ def gemm_timed_out() -> bool:
     flag = C.c_int(0)
     check(lib.annc_gemm_check(_stream(), C.byref(flag)))
     return flag.value != 0
+
+
+class BagLaunch:
+    """Grouped embedding-bag launch over explicit (table, ids, segments, output) entries,
+    optionally row-sharded (annc_embed_bags_sharded_dev).  Each entry is a tuple
+    (table_ptr, local_rows, num_buckets, ids_ptr, seg_ptr, nnz, out_ptr)."""
+
+    def __init__(self, entries, dim: int, batch: int, ncols: int, out_stride: int,
+                 device: torch.device, id_kind: int = 2, col: int = 0, combiner: int = 0,
+                 shard_count: int = 1, shard_rank: int = 0):
+        self.n = len(entries)
+        self.dim, self.batch, self.ncols, self.out_stride = dim, batch, ncols, out_stride
+        self.id_kind, self.col, self.combiner = id_kind, col, combiner
+        self.shard_count, self.shard_rank = shard_count, shard_rank
+        self.desc = (BagTable * self.n)()
+        for i, (tp, rows, nb, ip, sp, nnz, op) in enumerate(entries):
+            d = self.desc[i]
+            d.table, d.rows, d.num_buckets, d.ids, d.slice_input, d.nnz, d.out = \
+                tp, int(rows), int(nb), ip, sp, int(nnz), op
+        self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
+
+    def run(self) -> None:
+        check(lib.annc_embed_bags_sharded_dev(
+            self.desc, C.c_int(self.n), C.c_int64(self.dim), C.c_int(self.id_kind),
+            C.c_int64(self.ncols), C.c_int32(self.col), C.c_int(self.combiner),
+            C.c_int64(self.batch), C.c_int64(self.out_stride), C.c_int(self.shard_count),
+            C.c_int(self.shard_rank), C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws_bytes),
+            _stream()))
+
+    def error_bits(self) -> int:
+        bits = C.c_int(0)
+        check(lib.annc_embed_bag_check(C.c_void_p(self.ws.data_ptr()), _stream(), C.byref(bits)))
+        return bits.value
+
+
+def sum_partials(src: torch.Tensor, parts: int, part_stride: int, rows: int, width: int,
+                 src_stride: int, out_ptr: int, out_stride: int) -> None:
+    check(lib.annc_sum_partials_dev(C.c_void_p(src.data_ptr()), C.c_int(parts), C.c_int64(part_stride),
+                                    C.c_int64(rows), C.c_int64(width), C.c_int64(src_stride),
+                                    C.c_void_p(out_ptr), C.c_int64(out_stride), _stream()))
+
+
+def copy_rows(dst_ptr: int, dst_stride: int, src_ptr: int, src_stride: int, width: int,
+              rows: int) -> None:
+    """2-D device copy of `rows` rows of `width` floats between pitched buffers."""
+    check(lib.annc_copy_rows_dev(C.c_void_p(dst_ptr), C.c_int64(dst_stride), C.c_void_p(src_ptr),
+                                 C.c_int64(src_stride), C.c_int64(width), C.c_int64(rows), _stream()))

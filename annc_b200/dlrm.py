@@ -37,7 +37,7 @@ class DlrmPipeline:
         self.inter_pad = (self.inter + 3) // 4 * 4  # 16-byte rows for the tensor-core loader
 
         up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
-        self.tables = [up(t) for t in emb.tables]
+        self._up = up
         self.bottom = [(up(w), up(b)) for w, b in model.bottom]
         top = []
         for i, (w, b) in enumerate(model.top):
@@ -70,10 +70,22 @@ class DlrmPipeline:
         self.inter_buf = torch.empty((B, self.inter_pad), **f32)
         self.acts_t = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.top]
         self.out = self.acts_t[-1]
-        self.plan = dev.BagPlan(self.tables, self.ids, self.segs, self.z, 1, B, id_kind=2, col=0,
-                                combiner=0)
         self.kernel_names: List[str] = []
         self.launches_per_step = 0
+        self.embed_launches = 3  # prepass + bag + atomic route
+        self._setup_embedding(model)
+
+    def _setup_embedding(self, model: DlrmModel) -> None:
+        """Single GPU: every table resident, one grouped bag launch writes slots 1.. of z."""
+        self.tables = [self._up(t) for t in model.emb.tables]
+        self.plan = dev.BagPlan(self.tables, self.ids, self.segs, self.z, 1, self.batch, id_kind=2,
+                                col=0, combiner=0)
+
+    def embed(self) -> None:
+        self.plan.run()
+
+    def embed_error_bits(self) -> int:
+        return self.plan.error_bits()
 
     # ------------------------------------------------------------------ one step
     def forward(self) -> torch.Tensor:
@@ -88,7 +100,7 @@ class DlrmPipeline:
                                   activation=ACT_RELU, ldc=(F * D if last else None),
                                   math=self.math))
             x = y
-        self.plan.run()
+        self.embed()
         dev.dot_interaction(self.z, self.inter_buf)
         x = self.inter_buf
         nt = len(self.top)
@@ -100,7 +112,7 @@ class DlrmPipeline:
             x = y
         self.kernel_names = names
         # prepass + bag + scatter route + interaction + one kernel per MLP layer
-        self.launches_per_step = 3 + 1 + len(names)
+        self.launches_per_step = self.embed_launches + 1 + len(names)
         return self.out
 
     def forward_e2e(self) -> torch.Tensor:

@@ -1,0 +1,192 @@
+"""Multi-GPU embedding step of the DLRM-style pipeline: one process per GPU.
+
+Three partitionings of the tables, the MLPs always run on the rank's own batch slice
+(no collective in the MLP):
+
+  row      every table row-sharded with the reference's mod rule
+           (owner = bucket % G, local row = bucket / G,
+           annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71).
+           Ids are all-gathered, every rank pools the lookups it owns for the global
+           batch, partial sums go through an NCCL all-to-all and are added in rank order.
+  table    whole tables per rank (contiguous blocks); ids travel to the owners by
+           all-to-all, finished pooled vectors come back by all-to-all, no add.
+  replica  every rank holds every table; no exchange (scaling ceiling when tables fit).
+
+ShardPlan is pure numpy so that the partitioning logic is testable on CPU ranks.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import numpy as np
+
+
+class ShardPlan:
+    """Sizes and offsets of the exchange.  nnz[s][t] = lookups of rank s in table t."""
+
+    def __init__(self, mode: str, world: int, rank: int, table_rows: List[int], nnz: np.ndarray):
+        assert mode in ("row", "table", "replica")
+        self.mode, self.world, self.rank = mode, world, rank
+        self.table_rows = list(table_rows)
+        self.T = len(table_rows)
+        self.nnz = np.asarray(nnz, np.int64).reshape(world, self.T)
+        # table mode: contiguous blocks of tables per owner
+        blocks = np.array_split(np.arange(self.T), world)
+        self.owned = [list(map(int, b)) for b in blocks]
+        self.owner_of = np.zeros(self.T, np.int64)
+        for p, b in enumerate(self.owned):
+            self.owner_of[b] = p
+
+    # ---- row mode
+    def local_rows(self, t: int) -> int:
+        """Rows of table t stored on this rank: r with r % world == rank."""
+        rows, g, r = self.table_rows[t], self.world, self.rank
+        return (rows - r + g - 1) // g if rows > r else 0
+
+    def local_shard(self, table: np.ndarray) -> np.ndarray:
+        return np.ascontiguousarray(table[self.rank::self.world])
+
+    def gathered_len(self) -> int:
+        """Per-rank length of the padded id buffer that is all-gathered."""
+        return int(self.nnz.sum(axis=1).max())
+
+    def gathered_offset(self, s: int, t: int) -> int:
+        """Offset of rank s' lookups of table t inside its (table-ordered) flat buffer."""
+        return int(self.nnz[s, :t].sum())
+
+    # ---- table mode
+    def send_counts(self) -> List[int]:
+        """Lookups this rank sends to each owner (its buffer is table-ordered, and tables
+        are owned in contiguous blocks, so each destination's part is contiguous)."""
+        return [int(self.nnz[self.rank, self.owned[p]].sum()) for p in range(self.world)]
+
+    def recv_counts(self) -> List[int]:
+        """Lookups this rank receives from each source for the tables it owns."""
+        return [int(self.nnz[s, self.owned[self.rank]].sum()) for s in range(self.world)]
+
+    def recv_offset(self, s: int, j: int) -> int:
+        """Offset, inside the receive buffer, of source s' lookups of my j-th owned table."""
+        rc = self.recv_counts()
+        mine = self.owned[self.rank]
+        return int(sum(rc[:s]) + self.nnz[s, mine[:j]].sum())
+
+
+class ShardedDlrmPipeline:
+    """Built lazily to keep torch out of ShardPlan's import path."""
+
+    def __new__(cls, *args, **kwargs):
+        return _make_pipeline(*args, **kwargs)
+
+
+def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool = False):
+    import torch
+    import torch.distributed as dist
+
+    from . import device as dev
+    from ._lib import MATH_AUTO
+    from .dlrm import DlrmPipeline
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+
+    class _Pipe(DlrmPipeline):
+        def _setup_embedding(self, m) -> None:
+            emb = m.emb
+            T, B, D = self.T, self.batch, self.dim
+            nnz_all = [None] * world
+            dist.all_gather_object(nnz_all, [int(x) for x in self.nnz])
+            self.shard = plan = ShardPlan(mode, world, rank, [t.shape[0] for t in emb.tables],
+                                          np.array(nnz_all))
+            f32 = dict(dtype=torch.float32, device=self.device)
+            i64 = dict(dtype=torch.int64, device=self.device)
+            if mode == "replica":
+                DlrmPipeline._setup_embedding(self, m)
+                self.exchange_bytes = 0
+                return
+            if mode == "row":
+                self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
+                L = plan.gathered_len()
+                self.ids_pad = torch.zeros(L, **i64)
+                self.seg_pad = torch.zeros((L, 2), **i64)
+                self.ids_g = torch.zeros((world, L), **i64)
+                self.seg_g = torch.zeros((world, L, 2), **i64)
+                self.partial = torch.empty((world, B, T, D), **f32)
+                self.recv = torch.empty((world, B, T, D), **f32)
+                entries = []
+                for s in range(world):
+                    for t in range(T):
+                        off = plan.gathered_offset(s, t)
+                        entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
+                                        plan.table_rows[t],
+                                        self.ids_g.data_ptr() + (s * L + off) * 8,
+                                        self.seg_g.data_ptr() + (s * L + off) * 16,
+                                        int(plan.nnz[s, t]),
+                                        self.partial.data_ptr() + ((s * B) * T + t) * D * 4))
+                self.launch = dev.BagLaunch(entries, D, B, 2, T * D, self.device, shard_count=world,
+                                            shard_rank=rank)
+                self.embed_launches = 3 * ((len(entries) + 63) // 64) + 1
+                self.exchange_bytes = (world - 1) * B * T * D * 4 + (world - 1) * L * 24
+                return
+            # table mode
+            mine = plan.owned[rank]
+            self.tables = [self._up(emb.tables[t]) for t in mine]
+            sc, rc = plan.send_counts(), plan.recv_counts()
+            self.sc, self.rc = sc, rc
+            self.ids_r = torch.zeros(max(1, sum(rc)), **i64)
+            self.seg_r = torch.zeros((max(1, sum(rc)), 2), **i64)
+            To = len(mine)
+            self.pooled = torch.empty((world, B, max(To, 1), D), **f32)
+            counts_back = [len(plan.owned[p]) * B * D for p in range(world)]
+            self.back = torch.empty(sum(counts_back), **f32)
+            self.back_counts = counts_back
+            entries = []
+            for s in range(world):
+                for j, t in enumerate(mine):
+                    off = plan.recv_offset(s, j)
+                    entries.append((self.tables[j].data_ptr(), plan.table_rows[t], plan.table_rows[t],
+                                    self.ids_r.data_ptr() + off * 8, self.seg_r.data_ptr() + off * 16,
+                                    int(plan.nnz[s, t]),
+                                    self.pooled.data_ptr() + ((s * B) * To + j) * D * 4))
+            self.launch = dev.BagLaunch(entries, D, B, 2, max(To, 1) * D, self.device) if entries else None
+            self.embed_launches = 3 * ((len(entries) + 63) // 64) + world
+            self.exchange_bytes = (sum(sc) - sc[rank]) * 24 + (T - To) * B * D * 4
+
+        def embed(self) -> None:
+            plan = self.shard
+            T, B, D, F = self.T, self.batch, self.dim, self.F
+            if mode == "replica":
+                return DlrmPipeline.embed(self)
+            if mode == "row":
+                n = self.nnz_total
+                self.ids_pad[:n].copy_(self.ids_all)
+                self.seg_pad[:n].copy_(self.seg_all)
+                dist.all_gather_into_tensor(self.ids_g, self.ids_pad)
+                dist.all_gather_into_tensor(self.seg_g, self.seg_pad)
+                self.launch.run()
+                dist.all_to_all_single(self.recv, self.partial)
+                dev.sum_partials(self.recv, world, B * T * D, B, T * D, T * D,
+                                 self.z.data_ptr() + D * 4, F * D)
+                return
+            # table mode: ids to the owners, pooled vectors back
+            dist.all_to_all_single(self.ids_r[:sum(self.rc)], self.ids_all, self.rc, self.sc)
+            dist.all_to_all_single(self.seg_r[:sum(self.rc)], self.seg_all, self.rc, self.sc)
+            To = len(plan.owned[rank])
+            if self.launch is not None:
+                self.launch.run()
+            send = self.pooled.view(-1)[:world * B * To * D]
+            dist.all_to_all_single(self.back, send, self.back_counts, [B * To * D] * world)
+            off = 0
+            for p in range(world):
+                tp = len(plan.owned[p])
+                if tp:
+                    first = plan.owned[p][0]
+                    dev.copy_rows(self.z.data_ptr() + (1 + first) * D * 4, F * D,
+                                  self.back.data_ptr() + off * 4, tp * D, tp * D, B)
+                off += self.back_counts[p]
+
+        def embed_error_bits(self) -> int:
+            if mode == "replica":
+                return DlrmPipeline.embed_error_bits(self)
+            return self.launch.error_bits() if self.launch is not None else 0
+
+    return _Pipe(model, device, math=MATH_AUTO if math is None else math,
+                 keep_host_inputs=keep_host_inputs)

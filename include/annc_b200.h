@@ -222,6 +222,11 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
                           int64_t width, int64_t src_stride, float* out, int64_t out_stride,
                           void* stream);
 
+/* Pitched device-to-device copy of `rows` rows of `width` floats (strides in floats); places
+ * the pooled vectors received from another rank into their slots of the interaction input. */
+int annc_copy_rows_dev(float* dst, int64_t dst_stride, const float* src, int64_t src_stride,
+                       int64_t width, int64_t rows, void* stream);
+
 /* Same operation as annc_embed_bags_dev for callers that must not allocate device
  * memory and have none to lend: code running inside a framework callback where
  * cudaMalloc is forbidden or would deadlock (an allocator hook, a stream-ordered

@@ -1,0 +1,47 @@
+"""Worker run under torchrun by test_gpu_sharded.py: builds the sharded DLRM pipeline in the
+given mode on this rank's GPU and checks its predictions and pooled vectors against the CPU
+oracle evaluated on this rank's own batch.  Exit code 0 = parity."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from annc_b200 import synth  # noqa: E402
+from annc_b200.sharded import ShardedDlrmPipeline  # noqa: E402
+from oracle import oracle  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1]
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    model = synth.dlrm_model(seed=5, batch=2048, tables=7, max_rows=2e5, input_seed=100 + rank)
+    pipe = ShardedDlrmPipeline(model, dev, mode)
+    got = pipe.forward().cpu().numpy()
+    assert pipe.embed_error_bits() == 0
+    want = oracle.dlrm_forward(model, threads=4)
+    z = pipe.z.cpu().numpy()
+    emb = model.emb
+    zw = np.zeros_like(z)
+    oracle.embed_bags_tables(emb.tables, [t.shape[0] for t in emb.tables], [b.raw_ids for b in emb.bags],
+                             [b.slice_input for b in emb.bags], emb.batch, emb.dim, zw, z.shape[1], 1)
+    scale = np.abs(zw[:, 1:]).max()
+    perr = float(np.abs(z[:, 1:] - zw[:, 1:]).max() / scale)
+    if mode in ("table", "replica"):
+        assert np.array_equal(z[:, 1:], zw[:, 1:]), "pooled vectors must be bit-exact"
+    assert perr <= 1e-5, perr          # fp32 pooling tolerance under row sharding
+    assert np.abs(got - want).max() <= 2e-3  # TF32 MLP
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank} mode {mode} ok pooled_err {perr:.2e}")
+
+
+if __name__ == "__main__":
+    main()

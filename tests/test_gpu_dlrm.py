@@ -18,7 +18,7 @@ def test_dlrm_step_matches_oracle(math, tol):
     model = synth.dlrm_model(seed=3, batch=4096, max_rows=3e5)
     pipe = DlrmPipeline(model, torch.device("cuda:0"), math=math, keep_host_inputs=True)
     got = pipe.forward().cpu().numpy()
-    assert pipe.plan.error_bits() == 0
+    assert pipe.embed_error_bits() == 0
     want = oracle.dlrm_forward(model, threads=oracle.host_threads())
     assert np.abs(got - want).max() <= tol  # sigmoid outputs in (0,1): absolute == normwise
     # the end-to-end entry (host buffers in, host result out) gives the same answer
