@@ -5,6 +5,8 @@
 #include "common.h"
 
 namespace annc {
+int dot_interaction_tc(const float* z, int64_t batch, int F, int dim, int64_t z_stride, float* out,
+                       int64_t out_stride, cudaStream_t s);  // interaction_tc.cu
 namespace {
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -355,8 +357,17 @@ int annc_copy_rows_dev(float* dst, int64_t dst_stride, const float* src, int64_t
 }
 
 int annc_dot_interaction_dev(const float* z, int64_t batch, int features, int dim,
-                             int64_t z_stride, float* out, int64_t out_stride, void* stream) {
+                             int64_t z_stride, float* out, int64_t out_stride, int math,
+                             void* stream) {
   ANNC_REQUIRE(z && out, ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  if (math != ANNC_MATH_FP32 && batch > 0 && features >= 2 &&
+      out_stride >= dim + features * (features - 1) / 2) {
+    const int rc = dot_interaction_tc(z, batch, features, dim, z_stride, out, out_stride,
+                                      static_cast<cudaStream_t>(stream));
+    if (rc != ANNC_ERR_UNSUPPORTED) return rc;
+    if (math == ANNC_MATH_TF32)
+      return fail(ANNC_ERR_UNSUPPORTED, "dot interaction: shape not supported by the tensor-core kernel");
+  }
   ANNC_REQUIRE(features >= 1 && features <= 32, ANNC_ERR_UNSUPPORTED,
                "dot interaction supports up to 32 feature vectors");
   ANNC_REQUIRE(dim == 64 || dim == 128 || dim == 32 || dim == 16, ANNC_ERR_UNSUPPORTED,

@@ -32,6 +32,8 @@
 #include "common.h"
 #include "gemm.h"
 #include "kn4.h"
+#include "tc_host.h"
+#include "tc_ptx.cuh"
 
 namespace annc {
 namespace gemm {
@@ -69,122 +71,7 @@ struct TcParams {
 
 __device__ int g_gemm_error = 0;  // 1: an mbarrier wait ran out
 
-// ---------------------------------------------------------------- PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after about one second, or as soon as another role of the
-// CTA has given up (abort word in shared memory).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > 1000000000ull) {
-        *abort_flag = 1;
-        atomicExch(&g_gemm_error, 1);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.wait_all;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrives on the mbarrier when every tcgen05.mma issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor (sm_100 format): start address, leading and
-// stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
-//   layout 2 = SWIZZLE_128B          (16-byte units XOR row % 8, 8-row atoms)
-//   layout 1 = SWIZZLE_128B_BASE32B  (32-byte units XOR row % 4, 4-row atoms): the one
-//              layout the tensor core accepts for an N-major (or M-major) tf32 operand.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                              uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // version
-  d |= (uint64_t)layout << 61;
-  return d;
-}
+using namespace annc::tc;
 
 __device__ __forceinline__ float act_apply(float v, int act) {
   if (act == ANNC_ACT_RELU) return fmaxf(v, 0.0f);
@@ -243,7 +130,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int it = 0; it < KT; ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) break;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, &g_gemm_error)) break;
         const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
         mbar_expect_tx(bar_full + 8 * s, b_by_loader ? A_BYTES : STAGE_BYTES);
         tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
@@ -266,7 +153,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int it = 0; it < KT && ok; ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+        ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, &g_gemm_error);
         if (!ok) break;
         fence_proxy_async();
         tc_fence_after();
@@ -292,18 +179,52 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ---------------- B loader (warps 2..5), then epilogue
     const int lt = threadIdx.x - 64;  // 0..127
     if (b_by_loader) {
-      // chunk column c (16 bytes = 4 floats of n) is fixed per thread; rows k = kr + 4 i
-      const int c = lt & 31, kr = lt >> 5;
-      const int n = n0 + c * 4;
-      const bool n_ok = n < p.N;
-      // Position of this 4-column chunk inside its panel: fixed per thread.
-      int col_term = 0, width = 0, col_in = 0;
-      if (n_ok) {
-        const kn4::Chunk nc = kn4::axis_chunk(p.N, kn4::kTileN, n);
-        const kn4::Panel pn = kn4::panel_of(nc.len, n - nc.start);
-        col_term = (int)(nc.start + pn.start);
-        width = (int)pn.width;
-        col_in = (int)(n - nc.start - pn.start);
+      // The stage's 1024 16-byte chunks are numbered panel piece by panel piece (a piece =
+      // the part of a kn4 panel inside this tile's 128 columns), row-major inside a piece,
+      // which is the order the packed buffer stores them: chunk e = i * 128 + lt, so every
+      // warp-wide cp.async reads 512 contiguous bytes.  The mapping e -> (row, column,
+      // panel terms) does not depend on the k-step and is worked out once per thread.
+      int a_kl[BK / 4], a_term[BK / 4], a_w[BK / 4], a_in[BK / 4];
+      uint32_t a_dst[BK / 4];
+#pragma unroll
+      for (int i = 0; i < BK / 4; ++i) { a_kl[i] = 0; a_term[i] = 0; a_w[i] = -1; a_in[i] = 0; a_dst[i] = 0; }
+      {
+        const int tile_end = n0 + BN;
+        const int n_end = p.N < tile_end ? p.N : tile_end;
+        int cum = 0, col = n0;
+        while (col < tile_end) {
+          int wc, term = 0, w = -1, in0 = 0;  // wc: chunks of this piece per k-row
+          if (col < n_end) {
+            const kn4::Chunk nc = kn4::axis_chunk(p.N, kn4::kTileN, col);
+            const kn4::Panel pn = kn4::panel_of(nc.len, col - nc.start);
+            const int pend = (int)(nc.start + pn.start + pn.width);
+            const int piece_end = pend < n_end ? pend : n_end;
+            wc = (piece_end - col) / 4;
+            term = (int)(nc.start + pn.start);
+            w = (int)pn.width;
+            in0 = (int)(col - nc.start - pn.start);
+          } else {
+            wc = (tile_end - col) / 4;  // columns past N: zero-filled
+          }
+          if (wc <= 0) break;  // cannot happen for N % 4 == 0; never spin
+#pragma unroll
+          for (int i = 0; i < BK / 4; ++i) {
+            const int e = i * LOADER_THREADS + lt - cum;
+            if (e >= 0 && e < BK * wc) {
+              const int kl = e / wc, ci = e - kl * wc;
+              const int c = (col - n0) / 4 + ci;
+              a_kl[i] = kl;
+              a_term[i] = term;
+              a_w[i] = w;
+              a_in[i] = in0 + 4 * ci;
+              // 32-column block, row, then the 32-byte unit XOR (row % 4) and the 16-byte half
+              a_dst[i] = (uint32_t)(c >> 3) * (BK * 128) + (uint32_t)kl * 128u +
+                         (uint32_t)(((((c & 7) >> 1) ^ (kl & 3)) << 5) | ((c & 1) << 4));
+            }
+          }
+          cum += BK * wc;
+          col += 4 * wc;
+        }
       }
       // K chunks: 352 rows each up to `k_uniform`, then the two chunks that share the
       // remainder (kn4.h); all in 32-bit arithmetic, the element offset in 64-bit.
@@ -316,18 +237,15 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (res - first > first + 1) first += 12;
         k_split = k_uniform + first;
       }
-      const uint32_t dst_col = (uint32_t)(c >> 3) * (BK * 128);
-      const int cc = c & 7;
       for (int it = 0; it < KT; ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) break;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, &g_gemm_error)) break;
         const uint32_t sb = base + s * STAGE_BYTES + A_BYTES;
 #pragma unroll
         for (int i = 0; i < BK / 4; ++i) {
-          const int kl = kr + 4 * i;  // row inside the stage
-          const int k = it * BK + kl;
-          const bool ok = n_ok && k < p.K;
+          const int k = it * BK + a_kl[i];
+          const bool ok = a_w[i] > 0 && k < p.K;
           const float* src = p.B;
           if (ok) {
             int start, len;
@@ -341,13 +259,10 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               start = k_split;
               len = p.K - k_split;
             }
-            src = p.B + ((long long)start * p.N + (long long)len * col_term +
-                         (long long)((k - start) * width + col_in));
+            src = p.B + ((long long)start * p.N + (long long)len * a_term[i] +
+                         (long long)((k - start) * a_w[i] + a_in[i]));
           }
-          // 32-byte unit (cc >> 1) XOR (row % 4); the 16-byte half keeps its place
-          const uint32_t dst = sb + dst_col + (uint32_t)kl * 128u +
-                               (uint32_t)((((cc >> 1) ^ (kl & 3)) << 5) | ((cc & 1) << 4));
-          cp_async16(dst, src, ok ? 16u : 0u);
+          cp_async16(sb + a_dst[i], src, ok ? 16u : 0u);
         }
         cp_async_arrive_noinc(bar_full + 8 * s);
       }
@@ -356,7 +271,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // epilogue: warp w may touch TMEM lanes 32 (w % 4) .. 32 (w % 4) + 31
     const int q = warp & 3;
     const int row = m0 + q * 32 + lane;
-    const bool done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag)) != 0;
+    const bool done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag, &g_gemm_error)) != 0;
     tc_fence_after();
     if (done) {
       // Phase 1: this warp's 32 x 128 accumulator slab, scaled by alpha, goes to shared
@@ -444,42 +359,6 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// 2-D fp32 tensor [rows, cols] with row pitch ld floats; box = 32 columns x box_rows rows;
-// out-of-range elements read as zero.  `n_major` picks the 128-byte swizzle with 32-byte
-// atoms that an N-major tf32 operand needs, else the plain 128-byte swizzle.
-int make_map(CUtensorMap* map, const float* ptr, long long rows, long long cols, long long ld,
-             int box_rows, bool n_major) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-  const cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  n_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-  return ANNC_OK;
-}
-
 bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -551,8 +430,14 @@ int read_error_flag(int* flag) {
 }  // namespace gemm
 }  // namespace annc
 
+namespace annc { int dot_interaction_error_flag(int* flag); }
+
 extern "C" int annc_gemm_check(void* stream, int* timed_out) {
   if (!timed_out) return annc::fail(ANNC_ERR_INVALID_ARGUMENT, "null argument");
   ANNC_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  return annc::gemm::read_error_flag(timed_out);
+  int a = 0, b = 0;
+  ANNC_TRY(annc::gemm::read_error_flag(&a));
+  ANNC_TRY(annc::dot_interaction_error_flag(&b));
+  *timed_out = (a | b) ? 1 : 0;
+  return ANNC_OK;
 }

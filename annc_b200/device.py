@@ -103,12 +103,12 @@ def gemv(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, m: int, n: int, tran
                             C.c_void_p(y.data_ptr()), _stream()))
 
 
-def dot_interaction(z: torch.Tensor, out: torch.Tensor) -> None:
+def dot_interaction(z: torch.Tensor, out: torch.Tensor, math: int = MATH_AUTO) -> None:
     """z f32[batch, F, D] -> out f32[batch, out_stride] = [z[:,0,:] | tril(z z^T, -1) | 0 pad]."""
     batch, F, D = z.shape
     check(lib.annc_dot_interaction_dev(C.c_void_p(z.data_ptr()), C.c_int64(batch), C.c_int(F),
                                        C.c_int(D), C.c_int64(F * D), C.c_void_p(out.data_ptr()),
-                                       C.c_int64(out.shape[1]), _stream()))
+                                       C.c_int64(out.shape[1]), C.c_int(math), _stream()))
 
 
 def kn4_pack(b_kn: torch.Tensor) -> torch.Tensor:

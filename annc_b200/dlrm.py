@@ -46,23 +46,32 @@ class DlrmPipeline:
             top.append((up(w), up(b)))
         self.top = top
 
-        # step inputs: one flat buffer per kind so that an end-to-end step is three copies
+        # step inputs: one flat buffer per kind so that an end-to-end step is three copies.
+        # With host inputs kept there are two device input sets, so the copies of the next
+        # step overlap the kernels of the current one.
         nnz = [b.raw_ids.shape[0] for b in emb.bags]
         self.nnz = nnz
         self.nnz_total = int(sum(nnz))
         ids_host = np.concatenate([b.raw_ids for b in emb.bags])
         seg_host = np.concatenate([b.slice_input for b in emb.bags])
-        self.ids_all = up(ids_host)
-        self.seg_all = up(seg_host)
-        self.dense = up(model.dense)
         offs = np.concatenate([[0], np.cumsum(nnz)])
-        self.ids = [self.ids_all[offs[t]:offs[t + 1]] for t in range(T)]
-        self.segs = [self.seg_all[offs[t]:offs[t + 1]] for t in range(T)]
+        self.sets = []
+        for _ in range(2 if keep_host_inputs else 1):
+            st = {"ids_all": up(ids_host), "seg_all": up(seg_host), "dense": up(model.dense)}
+            st["ids"] = [st["ids_all"][offs[t]:offs[t + 1]] for t in range(T)]
+            st["segs"] = [st["seg_all"][offs[t]:offs[t + 1]] for t in range(T)]
+            self.sets.append(st)
+        self._use(0)
+        self._step = 0
         if keep_host_inputs:
             self.h_ids = torch.from_numpy(ids_host).pin_memory()
             self.h_seg = torch.from_numpy(seg_host).pin_memory()
             self.h_dense = torch.from_numpy(np.ascontiguousarray(model.dense)).pin_memory()
             self.h_out = torch.empty((B, 1), dtype=torch.float32).pin_memory()
+            self.copy_stream = torch.cuda.Stream(device=device)
+            self.ready = [torch.cuda.Event() for _ in self.sets]
+            self.done = [torch.cuda.Event() for _ in self.sets]
+            self._prefetched = [False, False]
 
         f32 = dict(dtype=torch.float32, device=device)
         self.acts_b = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.bottom[:-1]]
@@ -75,11 +84,22 @@ class DlrmPipeline:
         self.embed_launches = 3  # prepass + bag + atomic route
         self._setup_embedding(model)
 
+    def _use(self, i: int) -> None:
+        """Makes input set i the one the next forward() reads."""
+        st = self.sets[i]
+        self.cur = i
+        self.ids_all, self.seg_all, self.dense = st["ids_all"], st["seg_all"], st["dense"]
+        self.ids, self.segs = st["ids"], st["segs"]
+        if "plan" in st:
+            self.plan = st["plan"]
+
     def _setup_embedding(self, model: DlrmModel) -> None:
         """Single GPU: every table resident, one grouped bag launch writes slots 1.. of z."""
         self.tables = [self._up(t) for t in model.emb.tables]
-        self.plan = dev.BagPlan(self.tables, self.ids, self.segs, self.z, 1, self.batch, id_kind=2,
-                                col=0, combiner=0)
+        for st in self.sets:
+            st["plan"] = dev.BagPlan(self.tables, st["ids"], st["segs"], self.z, 1, self.batch,
+                                     id_kind=2, col=0, combiner=0)
+        self._use(self.cur)
 
     def embed(self) -> None:
         self.plan.run()
@@ -101,7 +121,7 @@ class DlrmPipeline:
                                   math=self.math))
             x = y
         self.embed()
-        dev.dot_interaction(self.z, self.inter_buf)
+        dev.dot_interaction(self.z, self.inter_buf, self.math)
         x = self.inter_buf
         nt = len(self.top)
         for i, (w, b) in enumerate(self.top):
@@ -115,14 +135,31 @@ class DlrmPipeline:
         self.launches_per_step = self.embed_launches + 1 + len(names)
         return self.out
 
+    def _issue_copy(self, i: int) -> None:
+        st = self.sets[i]
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.done[i])  # the step that last read set i is over
+            st["ids_all"].copy_(self.h_ids, non_blocking=True)
+            st["seg_all"].copy_(self.h_seg, non_blocking=True)
+            st["dense"].copy_(self.h_dense, non_blocking=True)
+            self.ready[i].record(self.copy_stream)
+        self._prefetched[i] = True
+
     def forward_e2e(self) -> torch.Tensor:
-        """Host buffers in, host result out: the three input copies from pinned memory, the
-        step, and the copy of the predictions back are all on the current stream."""
-        self.ids_all.copy_(self.h_ids, non_blocking=True)
-        self.seg_all.copy_(self.h_seg, non_blocking=True)
-        self.dense.copy_(self.h_dense, non_blocking=True)
+        """Host buffers in, host result out.  Every step copies its three input buffers from
+        pinned host memory and its predictions back; the copy of the following step's
+        inputs is issued on a second stream first, so it overlaps this step's kernels."""
+        cur = self._step % 2
+        if not self._prefetched[cur]:
+            self._issue_copy(cur)
+        self._issue_copy(1 - cur)
+        torch.cuda.current_stream().wait_event(self.ready[cur])
+        self._use(cur)
         out = self.forward()
         self.h_out.copy_(out, non_blocking=True)
+        self.done[cur].record()
+        self._prefetched[cur] = False
+        self._step += 1
         return self.h_out
 
     @property

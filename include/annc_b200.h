@@ -320,9 +320,12 @@ int annc_gemv_dev(int trans_a, int64_t m, int64_t n, float alpha, const float* a
  * sample) -> out[b, :] = [ Z[b,0,:] (D values) | strict lower triangle of Z[b] Z[b]^T in
  * row-major (i,j<i) order | zero padding up to out_stride ].  This is the
  * `__batch_matmul` of Z by its transpose (annc/service/cpu/gemm_rewriter.cc:187-216)
- * followed by the triangle gather and concat that XLA fuses around it. */
+ * followed by the triangle gather and concat that XLA fuses around it.
+ * math: ANNC_MATH_FP32 = CUDA cores, exact fp32; ANNC_MATH_AUTO / TF32 = tcgen05 kernel
+ * (dim 64, z_stride == features*dim), products in TF32, sums in fp32. */
 int annc_dot_interaction_dev(const float* z, int64_t batch, int features, int dim,
-                             int64_t z_stride, float* out, int64_t out_stride, void* stream);
+                             int64_t z_stride, float* out, int64_t out_stride, int math,
+                             void* stream);
 
 /* ---------------------------------------------------------------- reference symbols
  * XLA custom-call targets (annc/service/cpu/kdnn_rewriter.h:140-155).  `in` holds the
