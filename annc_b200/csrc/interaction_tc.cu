@@ -33,6 +33,8 @@ constexpr int I_BOX = 128 * 128;    // bytes reserved per 32-float half (128 row
 constexpr int I_STAGE = 2 * I_BOX;
 constexpr int I_LD = 132;           // padded accumulator row in shared memory (floats)
 constexpr int I_THREADS = 192;
+// Row-0 floats each epilogue thread carries per tile: samples_per_tile * 64 / 128, rounded up
+// to the template instance (2 covers F >= 26, the DLRM case; 32 covers F = 2).
 constexpr size_t I_SMEM = 1024 + (size_t)I_STAGES * I_STAGE + 128 * I_LD * 4 + 1024 + 256;
 
 __device__ int g_inter_error = 0;
@@ -52,6 +54,7 @@ __device__ __forceinline__ void epi_sync() {  // the 128 epilogue threads only
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
+template <int ROW0_PER_THREAD>
 __global__ void __launch_bounds__(I_THREADS, 1)
 dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -150,6 +153,14 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
     for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++li) {
       const int buf = (int)(li & 1);
       const uint32_t tph = (uint32_t)(li >> 1) & 1u;
+      const long long b0 = t * p.spt;
+      float row0[ROW0_PER_THREAD];
+#pragma unroll
+      for (int r = 0; r < ROW0_PER_THREAD; ++r) {  // unrounded copy of Z[b, 0, :]
+        const int idx = te + 128 * r;
+        const int s = idx / ID, col = idx - s * ID;
+        row0[r] = (s < p.spt && b0 + s < p.batch) ? __ldg(p.z + (b0 + s) * p.F * ID + col) : 0.f;
+      }
       // All four warps leave together: a warp that gave up still joins the barrier.
       const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * buf, tph, abort_flag,
                                                         &g_inter_error)) != 0;
@@ -174,20 +185,27 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);  // accumulator may be overwritten
       epi_sync();
-      const long long b0 = t * p.spt;
-      const int total = p.spt * (int)p.out_stride;
-      for (int e = te; e < total; e += 128) {
-        const int s = e / (int)p.out_stride, col = e - s * (int)p.out_stride;
-        const long long b = b0 + s;
-        if (b >= p.batch) break;
-        float v = 0.f;
-        if (col < ID) {
-          v = __ldg(p.z + b * p.F * ID + col);
-        } else if (col < ID + p.tri) {
-          const int pe = col - ID;
-          v = dsm[(s * p.F + pair_i[pe]) * I_LD + s * p.F + pair_j[pe]];
+      // Output rows of the tile's samples.  Triangle: pair index outer (its (i, j) is read
+      // once), sample inner; for one sample consecutive threads write consecutive floats.
+      for (int pe = te; pe < p.tri; pe += 128) {
+        const int pi = pair_i[pe], pj = pair_j[pe];
+        for (int s = 0; s < p.spt; ++s) {
+          const long long b = b0 + s;
+          if (b >= p.batch) break;
+          p.out[b * p.out_stride + ID + pe] = dsm[(s * p.F + pi) * I_LD + s * p.F + pj];
         }
-        p.out[b * p.out_stride + col] = v;
+      }
+      // Row 0 of every sample (loaded before the wait on the accumulator) and the padding.
+#pragma unroll
+      for (int r = 0; r < ROW0_PER_THREAD; ++r) {
+        const int idx = te + 128 * r;
+        const int s = idx / ID, col = idx - s * ID;
+        if (s < p.spt && b0 + s < p.batch) p.out[(b0 + s) * p.out_stride + col] = row0[r];
+      }
+      const int pad = (int)p.out_stride - ID - p.tri;
+      for (int e = te; e < p.spt * pad; e += 128) {
+        const int s = e / pad, col = ID + p.tri + (e - s * pad);
+        if (b0 + s < p.batch) p.out[(b0 + s) * p.out_stride + col] = 0.f;
       }
       epi_sync();  // dsm is rewritten by the next tile
     }
@@ -212,7 +230,11 @@ int dot_interaction_tc(const float* z, int64_t batch, int F, int dim, int64_t z_
     return ANNC_ERR_UNSUPPORTED;
   static bool attr_set = false;
   if (!attr_set) {
-    ANNC_CUDA(cudaFuncSetAttribute(dot_interaction_tc_kernel,
+    ANNC_CUDA(cudaFuncSetAttribute(dot_interaction_tc_kernel<2>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I_SMEM));
+    ANNC_CUDA(cudaFuncSetAttribute(dot_interaction_tc_kernel<8>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I_SMEM));
+    ANNC_CUDA(cudaFuncSetAttribute(dot_interaction_tc_kernel<32>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I_SMEM));
     attr_set = true;
   }
@@ -233,7 +255,10 @@ int dot_interaction_tc(const float* z, int64_t batch, int F, int dim, int64_t z_
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const unsigned grid = (unsigned)(p.tiles < sms ? p.tiles : sms);
-  dot_interaction_tc_kernel<<<grid, I_THREADS, I_SMEM, s>>>(tm, p);
+  const int need = (p.spt * ID + 127) / 128;
+  if (need <= 2) dot_interaction_tc_kernel<2><<<grid, I_THREADS, I_SMEM, s>>>(tm, p);
+  else if (need <= 8) dot_interaction_tc_kernel<8><<<grid, I_THREADS, I_SMEM, s>>>(tm, p);
+  else dot_interaction_tc_kernel<32><<<grid, I_THREADS, I_SMEM, s>>>(tm, p);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }
