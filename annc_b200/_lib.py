@@ -43,7 +43,7 @@ class GemmDesc(C.Structure):
                 ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
                 ("addend", C.c_void_p), ("bias", C.c_void_p),
                 ("activation", C.c_int32), ("b_format", C.c_int32), ("math", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_int64))

@@ -52,7 +52,45 @@ __global__ void kn4_convert_kernel(const float* src, float* dst, long long K, lo
   }
 }
 
+// kn4 -> [K,N] in 16-byte chunks (N % 4 == 0, so a chunk never straddles two panels);
+// thread per chunk, rows on blockIdx.y.
+__global__ void __launch_bounds__(256)
+kn4_unpack_chunks_kernel(const float* __restrict__ src, float* __restrict__ dst, int K, int N) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = c * 4;
+  if (n >= N) return;
+  const kn4::Chunk nc = kn4::axis_chunk(N, kn4::kTileN, n);
+  const kn4::Panel pn = kn4::panel_of(nc.len, n - nc.start);
+  const long long term = nc.start + pn.start, in0 = n - nc.start - pn.start;
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const kn4::Chunk kc = kn4::axis_chunk(K, kn4::kTileK, k);
+    const float* p = src + kc.start * N + kc.len * term + (k - kc.start) * pn.width + in0;
+    *reinterpret_cast<float4*>(dst + (long long)k * N + n) = __ldg(reinterpret_cast<const float4*>(p));
+  }
+}
+
 }  // namespace
+
+// Unpacks a kn4 B into `ws` when that pays off; returns true and fills `plain` with the
+// descriptor of the equivalent plain-layout GEMM.
+static bool unpack_kn4_into_workspace(const annc_gemm_desc& d, cudaStream_t s, annc_gemm_desc* plain) {
+  if (d.b_format != ANNC_B_KN4 || !d.workspace || d.batch != 1) return false;
+  if (d.workspace_bytes < (size_t)d.k * (size_t)d.n * sizeof(float)) return false;
+  if ((reinterpret_cast<uintptr_t>(d.workspace) & 15) || (d.n & 3) || d.m < 512) return false;
+  if (d.k >= (1LL << 31) || d.n >= (1LL << 31)) return false;
+  *plain = d;
+  plain->b = static_cast<const float*>(d.workspace);
+  plain->b_format = ANNC_B_PLAIN;
+  plain->ldb = d.n;
+  plain->workspace = nullptr;
+  plain->workspace_bytes = 0;
+  if (!tc_supported(*plain, ANNC_MATH_TF32)) return false;
+  dim3 grid((unsigned)((d.n / 4 + 255) / 256), (unsigned)(d.k < 1024 ? d.k : 1024));
+  kn4_unpack_chunks_kernel<<<grid, 256, 0, s>>>(d.b, static_cast<float*>(d.workspace), (int)d.k,
+                                                (int)d.n);
+  return true;
+}
+
 }  // namespace gemm
 }  // namespace annc
 
@@ -68,6 +106,8 @@ int annc_gemm_run(const annc_gemm_desc* desc, void* stream) {
   if (desc->math != ANNC_MATH_AUTO && desc->math != math)
     return fail(ANNC_ERR_UNSUPPORTED, "gemm: shape not supported by the requested math mode");
   if (math == ANNC_MATH_FP32) return gemm::run_simt(*desc, s);
+  annc_gemm_desc plain;
+  if (gemm::unpack_kn4_into_workspace(*desc, s, &plain)) return gemm::run_tc(plain, math, s);
   return gemm::run_tc(*desc, math, s);
 }
 

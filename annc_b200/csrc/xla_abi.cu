@@ -50,6 +50,12 @@ int gemm_host(const char* who, float* out, const float* a, const float* b, const
   d.activation = act;
   d.b_format = b_format;
   d.math = ANNC_MATH_AUTO;
+  if (b_format == ANNC_B_KN4 && m >= 512 && (n & 3) == 0) {
+    // scratch from the call's arena: the packed weight is re-laid once per call (2 x 4kn
+    // bytes of traffic against 2mnk flops) and the GEMM then runs on the TMA-fed route
+    d.workspace_bytes = (size_t)k * (size_t)n * sizeof(float);
+    d.workspace = call.scratch(d.workspace_bytes);
+  }
   if (call.status() != ANNC_OK) return call.status();
   ANNC_TRY(annc_gemm_run(&d, call.stream()));
   return call.finish();

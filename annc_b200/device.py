@@ -70,7 +70,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, m: int, n: int, k
          alpha: float = 1.0, beta: float = 0.0, addend: Optional[torch.Tensor] = None,
          ld_addend: Optional[int] = None, stride_addend: int = 0,
          bias: Optional[torch.Tensor] = None, activation: int = ACT_NONE,
-         b_format: int = B_PLAIN, math: int = MATH_AUTO) -> str:
+         b_format: int = B_PLAIN, math: int = MATH_AUTO,
+         workspace: Optional[torch.Tensor] = None) -> str:
     """annc_gemm_run; returns the name of the kernel family that ran."""
     d = GemmDesc()
     d.trans_a, d.trans_b = int(trans_a), int(trans_b)
@@ -85,6 +86,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, m: int, n: int, k
     d.addend = addend.data_ptr() if addend is not None else None
     d.bias = bias.data_ptr() if bias is not None else None
     d.activation, d.b_format, d.math = activation, b_format, math
+    if workspace is not None:
+        d.workspace, d.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     name = lib.annc_gemm_kernel_name(C.byref(d)).decode()
     check(lib.annc_gemm_run(C.byref(d), _stream()))
     return name

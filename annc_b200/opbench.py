@@ -52,6 +52,25 @@ def time_ms(fn, reps, flush):
     return float(np.median(ts))
 
 
+def bmm_case(name, b, m, n, k, reps):
+    hbm, tf32, src = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((b, m, k), device="cuda", generator=g)
+    w = torch.randn((b, k, n), device="cuda", generator=g)
+    c = torch.empty((b, m, n), device="cuda")
+    names = []
+    fn = lambda: names.append(dev.gemm(a, w, c, m=m, n=n, k=k, batch=b, stride_a=m * k,
+                                       stride_b=k * n, stride_c=m * n))
+    byt = 4 * b * (m * k + k * n + m * n)
+    ms = time_ms(fn, reps, flush=True)
+    fl = 2.0 * b * m * n * k
+    print(json.dumps({"op": name, "kernel": names[-1], "b": "kn", "m": m, "n": n, "k": k, "batch": b,
+                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                      "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
+                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
+                      "peak": src}), flush=True)
+
+
 def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False):
     hbm, tf32, src = peaks()
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -64,9 +83,11 @@ def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=F
     if bsrc == "nk":
         b = w.t().contiguous()
         kw["trans_b"] = True
-    elif bsrc == "kn4":
+    elif bsrc in ("kn4", "kn4+ws"):
         b = dev.kn4_pack(w)
         kw["b_format"] = B_KN4
+        if bsrc == "kn4+ws":
+            kw["workspace"] = torch.empty((k, n), device="cuda")
     else:
         b = w
     names = []
@@ -83,8 +104,9 @@ def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=F
 
 def run_gemm(reps):
     gemm_case("matmul_add_relu C1", 512, 1024, 1024, reps, addend=True, act=ACT_RELU)
-    for bsrc in ("kn4", "kn", "nk"):
+    for bsrc in ("kn4", "kn4+ws", "kn", "nk"):
         gemm_case("layout_matmul C2", 8192, 4096, 2048, reps, bsrc=bsrc)
+    bmm_case("batch_matmul C2", 64, 256, 256, 64, reps)
     for m in (128, 256, 512):
         gemm_case("small-M sweep", m, 1024, 1024, reps)
     for (k, n) in ((512, 256), (256, 64), (416, 512), (512, 256)):

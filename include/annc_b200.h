@@ -284,7 +284,9 @@ typedef struct annc_gemm_desc {
   int32_t b_format;              /* ANNC_B_*; KN4 = python/annc/optimize/data_pack.py layout */
   int32_t math;                  /* ANNC_MATH_*   */
   int32_t reserved;
-} annc_gemm_desc;
+  void* workspace;               /* optional device scratch, 16-byte aligned, or NULL      */
+  size_t workspace_bytes;        /* with >= 4*k*n bytes a large kn4 GEMM first unpacks B   */
+} annc_gemm_desc;                /* into it and then runs at the speed of the plain layout */
 
 int annc_gemm_run(const annc_gemm_desc* desc, void* stream);
 /* Synchronises `stream` and reports whether a tensor-core GEMM CTA has given up on one of

@@ -120,3 +120,23 @@ def test_layout_matmul_full_config_properties():
     y2 = torch.empty_like(y)
     device.gemm(xd * 2, packed, y2, m=8192, n=4096, k=2048, b_format=B_KN4)
     assert torch.equal(y2, y * 2)
+
+
+def test_kn4_with_workspace_matches_direct_route():
+    """With a workspace the packed weight is re-laid on the device first; the result must be
+    bit-identical to the plain-layout GEMM and within TF32 of the oracle."""
+    m, n, k = 1024, 520, 708
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+    packed = _dev(oracle.kn4_pack(w))
+    ws = torch.empty((k, n), device="cuda")
+    c_ws = torch.empty((m, n), device="cuda")
+    c_plain = torch.empty((m, n), device="cuda")
+    c_direct = torch.empty((m, n), device="cuda")
+    device.gemm(_dev(a), packed, c_ws, m=m, n=n, k=k, b_format=B_KN4, workspace=ws)
+    device.gemm(_dev(a), _dev(w), c_plain, m=m, n=n, k=k)
+    device.gemm(_dev(a), packed, c_direct, m=m, n=n, k=k, b_format=B_KN4)
+    assert torch.equal(ws, _dev(w))
+    assert torch.equal(c_ws, c_plain)
+    assert nerr(c_direct, a @ w) <= TF32_TOL and nerr(c_ws, a @ w) <= TF32_TOL
