@@ -67,6 +67,9 @@ struct TcParams {
   const float* bias;
   float alpha, beta;
   int act;
+  int batched;    // A (and B when b_batched) are rank-3 tensor maps, batch = blockIdx.z
+  int b_batched;
+  long long stride_c, stride_addend;
 };
 
 __device__ int g_gemm_error = 0;  // 1: an mbarrier wait ran out
@@ -133,13 +136,20 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, &g_gemm_error)) break;
         const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
         mbar_expect_tx(bar_full + 8 * s, b_by_loader ? A_BYTES : STAGE_BYTES);
-        tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
+        const int bz = blockIdx.z;
+        if (p.batched) tma_load_3d(sa, &tmap_a, it * BK, m0, bz, bar_full + 8 * s);
+        else tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
         if (p.b_mode == B_TMA_NK) {
-          tma_load_2d(sb, &tmap_b, it * BK, n0, bar_full + 8 * s);
+          if (p.b_batched) tma_load_3d(sb, &tmap_b, it * BK, n0, bz, bar_full + 8 * s);
+          else tma_load_2d(sb, &tmap_b, it * BK, n0, bar_full + 8 * s);
         } else if (p.b_mode == B_TMA_KN) {
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j)  // one 32-column x BK-row box per block
-            tma_load_2d(sb + j * (BK * 128), &tmap_b, n0 + 32 * j, it * BK, bar_full + 8 * s);
+          for (int j = 0; j < BN / 32; ++j) {  // one 32-column x BK-row box per block
+            if (p.b_batched)
+              tma_load_3d(sb + j * (BK * 128), &tmap_b, n0 + 32 * j, it * BK, bz, bar_full + 8 * s);
+            else
+              tma_load_2d(sb + j * (BK * 128), &tmap_b, n0 + 32 * j, it * BK, bar_full + 8 * s);
+          }
         }
       }
     }
@@ -312,8 +322,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const long long grow = (long long)(m0 + q * 32 + rr);
         const float4 a4 = *reinterpret_cast<const float4*>(slab + rr * LD + lane * 4);
         float v[4] = {a4.x, a4.y, a4.z, a4.w};
-        float* crow = p.C + grow * p.ldc + col;
-        const float* arow = p.addend ? p.addend + grow * p.ld_addend + col : nullptr;
+        float* crow = p.C + blockIdx.z * p.stride_c + grow * p.ldc + col;
+        const float* arow =
+            p.addend ? p.addend + blockIdx.z * p.stride_addend + grow * p.ld_addend + col : nullptr;
         if (vec && col + 3 < p.N) {
           if (p.beta != 0.f) {
             const float4 o = *reinterpret_cast<const float4*>(crow);
@@ -365,7 +376,12 @@ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 bool tc_supported(const annc_gemm_desc& d, int math) {
   if (math != ANNC_MATH_TF32) return false;
-  if (d.batch != 1 || d.trans_a) return false;
+  if (d.trans_a || d.batch < 1 || d.batch > 65535) return false;
+  if (d.batch > 1) {  // strided batch: rank-3 tensor maps need 16-byte batch pitches
+    if (d.b_format != ANNC_B_PLAIN || (d.stride_a & 3) || (d.stride_b & 3) || d.stride_a <= 0 ||
+        d.stride_c <= 0 || (d.stride_c & 3) || (d.addend && (d.stride_addend & 3)))
+      return false;
+  }
   if (d.m < 64 || d.n < 16 || d.k < 32) return false;
   if (d.m > 128LL * 65535 || d.n > (1LL << 30) || d.k > (1LL << 30)) return false;
   if (!al16(d.a) || (d.lda & 3) || (d.k & 3)) return false;  // TMA: 16-byte base and pitch
@@ -385,9 +401,15 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
     attr_set = true;
   }
   CUtensorMap ta, tb;
-  ANNC_TRY(make_map(&ta, d.a, d.m, d.k, d.lda, BM, false));
+  const bool batched = d.batch > 1, b_batched = batched && d.stride_b > 0;
+  if (batched) ANNC_TRY(make_map3(&ta, d.a, d.batch, d.m, d.k, d.lda, d.stride_a, BM, false));
+  else ANNC_TRY(make_map(&ta, d.a, d.m, d.k, d.lda, BM, false));
   TcParams p;
   memset(&p, 0, sizeof(p));
+  p.batched = batched;
+  p.b_batched = b_batched;
+  p.stride_c = batched ? d.stride_c : 0;
+  p.stride_addend = batched ? d.stride_addend : 0;
   p.M = (int)d.m;
   p.N = (int)d.n;
   p.K = (int)d.k;
@@ -396,10 +418,12 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
     tb = ta;
   } else if (d.trans_b) {
     p.b_mode = B_TMA_NK;
-    ANNC_TRY(make_map(&tb, d.b, d.n, d.k, d.ldb, BN, false));
+    if (b_batched) ANNC_TRY(make_map3(&tb, d.b, d.batch, d.n, d.k, d.ldb, d.stride_b, BN, false));
+    else ANNC_TRY(make_map(&tb, d.b, d.n, d.k, d.ldb, BN, false));
   } else {
     p.b_mode = B_TMA_KN;
-    ANNC_TRY(make_map(&tb, d.b, d.k, d.n, d.ldb, BK, true));
+    if (b_batched) ANNC_TRY(make_map3(&tb, d.b, d.batch, d.k, d.n, d.ldb, d.stride_b, BK, true));
+    else ANNC_TRY(make_map(&tb, d.b, d.k, d.n, d.ldb, BK, true));
   }
   p.B = d.b;
   p.ldb = d.ldb;
@@ -411,8 +435,8 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   p.alpha = d.alpha;
   p.beta = d.beta;
   p.act = d.activation;
-  dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM));
-  const long long ctas = (long long)grid.x * grid.y;
+  dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM), (unsigned)d.batch);
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
   if (ctas <= 148 * 3 / 2) {
     gemm_tf32_tcgen05_kernel<6><<<grid, NUM_THREADS, smem_bytes(6), s>>>(ta, tb, p);
   } else {

@@ -46,5 +46,24 @@ inline int make_map(CUtensorMap* map, const float* ptr, long long rows, long lon
   return ANNC_OK;
 }
 
+// 3-D variant for strided batches: [batch, rows, cols], box = 32 columns x box_rows rows x 1.
+inline int make_map3(CUtensorMap* map, const float* ptr, long long batch, long long rows,
+                     long long cols, long long ld, long long batch_stride, int box_rows,
+                     bool n_major) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float),
+                                 (cuuint64_t)batch_stride * sizeof(float)};
+  const cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  n_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled(3d) failed (%d)", (int)r);
+  return ANNC_OK;
+}
+
 }  // namespace tc
 }  // namespace annc

@@ -30,6 +30,7 @@ def _tol_for(m, n, k, **kw):
     d = _lib.GemmDesc()
     d.m, d.n, d.k, d.batch = m, n, k, kw.get("batch", 1)
     d.lda, d.ldb, d.ldc = k, n, n
+    d.stride_a, d.stride_b, d.stride_c = m * k, k * n, m * n
     d.a = d.b = d.c = 256  # alignment probe only
     d.trans_a, d.trans_b = int(kw.get("trA", False)), int(kw.get("trB", False))
     d.b_format = kw.get("b_format", 0)
@@ -175,3 +176,20 @@ def test_small_k_route(m, n, k):
     want = np.maximum(a @ b + bias, 0)
     assert name == "simt_fp32"
     assert nerr(c, want) <= 2e-5
+
+
+@pytest.mark.parametrize("shared_b", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_strided_batch_on_tensor_cores(shared_b, trans_b):
+    """Strided-batch GEMM through rank-3 tensor maps (tails in m, n and k inside every batch)."""
+    b, m, n, k = 5, 200, 136, 100
+    rng = np.random.default_rng(7)
+    A = rng.standard_normal((b, m, k)).astype(np.float32)
+    B = rng.standard_normal((1 if shared_b else b, k, n)).astype(np.float32)
+    want = np.matmul(A, B)
+    Bd = _dev(np.swapaxes(B, 1, 2)) if trans_b else _dev(B)
+    c = torch.full((b, m, n), float("nan"), device="cuda")
+    name = device.gemm(_dev(A), Bd, c, m=m, n=n, k=k, batch=b, trans_b=trans_b, stride_a=m * k,
+                       stride_b=0 if shared_b else k * n, stride_c=m * n)
+    assert name == "tcgen05_tf32" and not device.gemm_timed_out()
+    assert nerr(c, want) <= 2e-3
