@@ -66,7 +66,10 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
   if (batch <= 0) return ANNC_OK;
 
   dim3 pre_grid(grid_for(max_nnz + 1, 256), num_tables);
-  bag_prepass_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
+  bool seg16 = ncols == 2;
+  for (int t = 0; t < num_tables; ++t) seg16 = seg16 && aligned16(tables[t].slice_input);
+  if (seg16) bag_prepass2_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
+  else bag_prepass_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
 
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   timing_events(&ev0, &ev1);

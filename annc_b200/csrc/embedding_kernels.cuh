@@ -76,6 +76,40 @@ __global__ void bag_prepass_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 }
 
+// Same boundary walk for the common two-column index matrix (sample, position): every
+// thread reads its whole 16-byte row, so a warp reads 512 contiguous bytes, and takes the
+// previous lookup's segment id from its neighbour lane.
+__global__ void __launch_bounds__(256)
+bag_prepass2_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int t = blockIdx.y;
+  const BagTableDev& T = p.t[t];
+  int* off = offsets + (long long)t * (p.batch + 1);
+  const int lane = threadIdx.x & 31;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long n_round = (T.nnz + 1 + 31) / 32 * 32;  // whole warps walk the loop together
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
+    long long cur = p.batch;
+    if (i < T.nnz) {
+      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(T.seg) + i);
+      cur = p.col == 0 ? v.x : v.y;
+    }
+    long long prev = __shfl_up_sync(0xffffffffu, cur, 1);
+    if (lane == 0) prev = (i == 0) ? -1 : (i - 1 < T.nnz ? T.seg[(i - 1) * 2 + p.col] : p.batch);
+    if (i > T.nnz) continue;
+    if (i < T.nnz && (cur < 0 || cur >= p.batch)) {
+      atomicOr(&hdr->err_bits, kErrSegment);
+      cur = cur < 0 ? 0 : p.batch;
+    }
+    if (prev < -1) prev = -1;
+    if (prev > p.batch) prev = p.batch;
+    if (cur < prev) {
+      if (i < T.nnz) hdr->unsorted[t] = 1;
+      continue;
+    }
+    for (long long s = prev + 1; s <= cur; ++s) off[s] = (int)i;
+  }
+}
+
 __device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, long long i,
                                                  unsigned long long num_buckets) {
   if (id_kind == 0) return (long long)((const int*)ids)[i];

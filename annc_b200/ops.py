@@ -353,3 +353,58 @@ def selector_argmax3d(variant, invals, inidxs, init_value, init_idx):
     fn(None, C.c_int(B), C.c_int(M), C.c_int(N), C.c_void_p(_ptr(invals)), C.c_void_p(_ptr(inidxs)),
        C.c_float(init_value), C.c_int32(init_idx), C.c_void_p(_ptr(ov)), C.c_void_p(_ptr(oi)))
     return ov, oi
+
+
+# ---------------------------------------------------------------- adjacent fused ops
+
+def _scalar(v, dtype):
+    return np.asarray(v, dtype=dtype).reshape(())
+
+
+def kp_fused_embedding_padding(origin_shape, input, input_rows, reshape_sizes, pack, fast=False):
+    """KPFusedEmbeddingPadding{,Fast} -> (padding rows, padded+reshaped input | its row count)."""
+    input = _contig(input)
+    outs = _outputs_for(input)
+    os_ = np.array(origin_shape, dtype=np.int64)
+    ir = np.array(input_rows, dtype=np.int32)
+    rs = np.array(reshape_sizes, dtype=np.int32)
+    pk = np.array(pack, dtype=np.int32)
+    check(lib.annc_KPFusedEmbeddingPadding(C.byref(as_tensor(os_)), C.byref(as_tensor(input)),
+                                           C.byref(as_tensor(ir)), C.byref(as_tensor(rs)),
+                                           C.byref(as_tensor(pk)), C.c_int(int(fast)), outs.fn, None))
+    return outs[0], outs[1]
+
+
+def kp_fused_embedding_action_id_gather(indices1, params, indices2, pack_dim, pack):
+    """KPFusedEmbeddingActionIdGather -> f32[pack_dim, cols + pack]."""
+    indices1, params, indices2 = _contig(indices1), _contig(params), _contig(indices2)
+    outs = _outputs_for(params)
+    pd = np.array(pack_dim, dtype=np.int32)
+    pk = np.array(pack, dtype=np.int32)
+    check(lib.annc_KPFusedEmbeddingActionIdGather(
+        C.byref(as_tensor(indices1)), C.byref(as_tensor(params)), C.byref(as_tensor(indices2)),
+        C.byref(as_tensor(pd)), C.byref(as_tensor(pk)), outs.fn, None))
+    return outs[0]
+
+
+def kp_fused_sparse_reshape(slice_input, begin, new_shape, pack_const):
+    """KPFusedSparseReshape -> (indices i64[rows, 2], shape i64[2])."""
+    slice_input = _contig(slice_input)
+    outs = _outputs_for(slice_input)
+    bg = np.array(begin, dtype=np.int32)
+    ns = np.array(new_shape, dtype=np.int64)
+    pc = np.array(pack_const, dtype=np.int64)
+    check(lib.annc_KPFusedSparseReshape(C.byref(as_tensor(slice_input)), C.byref(as_tensor(bg)),
+                                        C.byref(as_tensor(ns)), C.byref(as_tensor(pc)), outs.fn, None))
+    return outs[0], outs[1]
+
+
+def kp_fused_sparse_select(a, b, c, greater, equal1, equal2, equal3=0):
+    """KPFusedSparseSelect -> (x f32[n,1], y f32[n,1], w f32[n,2])."""
+    a, b, c = _contig(a), _contig(b), _contig(c)
+    outs = _outputs_for(a)
+    sc = [_scalar(v, np.int32) for v in (greater, equal1, equal2, equal3)]
+    check(lib.annc_KPFusedSparseSelect(C.byref(as_tensor(a)), C.byref(as_tensor(b)),
+                                       C.byref(as_tensor(c)), *[C.byref(as_tensor(v)) for v in sc],
+                                       outs.fn, None))
+    return outs[0], outs[1], outs[2]

@@ -166,6 +166,38 @@ int annc_KPFusedSparseEmbedding(const annc_tensor* fingerprints, const annc_tens
 int annc_KPFusedBatchMatMulAddSigmoid(const annc_tensor* lhs, const annc_tensor* rhs,
                                       const annc_tensor* bias, annc_alloc_fn alloc, void* ctx);
 
+/* KPFusedEmbeddingPadding / KPFusedEmbeddingPaddingFast
+ * (annc/tensorflow/kernels/embedding_fused_padding.cc:35-113).  origin_shape i64[2];
+ * input f32[rows, D]; input_rows i32 scalar; reshape_sizes i32[2] = {-1, cols}; pack i32
+ * scalar (= D).  Output 0: i32 scalar padding rows; output 1: the zero-padded input
+ * reshaped to f32[-1, cols], or with `fast` only its row count as an i32 scalar. */
+int annc_KPFusedEmbeddingPadding(const annc_tensor* origin_shape, const annc_tensor* input,
+                                 const annc_tensor* input_rows, const annc_tensor* reshape_sizes,
+                                 const annc_tensor* pack, int fast, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedEmbeddingActionIdGather
+ * (annc/tensorflow/kernels/embedding_fused_action_id_gather.cc:59-129): gather(gather(params,
+ * indices1), indices2) reshaped to [pack_dim, -1] with `pack` zero columns appended.
+ * indices1, indices2 i32|i64 matrices; params f32[P0, P1].  Output 0: f32[pack_dim, cols + pack]. */
+int annc_KPFusedEmbeddingActionIdGather(const annc_tensor* indices1, const annc_tensor* params,
+                                        const annc_tensor* indices2, const annc_tensor* pack_dim,
+                                        const annc_tensor* pack, annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedSparseReshape (annc/tensorflow/kernels/embedding_fused_sparse_reshape.cc:152-190): the
+ * sparse tensor with indices (i, slice_input[i, begin[1]]) and shape [rows, pack_const] reshaped
+ * to new_shape i64[2] (one entry may be -1).  Outputs: 0 i64[rows, 2] indices, 1 i64[2] shape. */
+int annc_KPFusedSparseReshape(const annc_tensor* slice_input, const annc_tensor* begin,
+                              const annc_tensor* new_shape, const annc_tensor* pack_const,
+                              annc_alloc_fn alloc, void* ctx);
+
+/* KPFusedSparseSelect (annc/tensorflow/kernels/embedding_fused_sparse_select.cc:32-107).
+ * a, b, c i32 with equal element counts; greater, equal1..3 i32 scalars.  Outputs: 0 f32[n,1] =
+ * a; 1 f32[n,1] = (b == equal2 || b == equal1 || a > greater); 2 f32[n,2] = {output 1, 1}. */
+int annc_KPFusedSparseSelect(const annc_tensor* a, const annc_tensor* b, const annc_tensor* c,
+                             const annc_tensor* greater, const annc_tensor* equal1,
+                             const annc_tensor* equal2, const annc_tensor* equal3,
+                             annc_alloc_fn alloc, void* ctx);
+
 /* sparse_embedding2 fusion (annc/service/cpu/graph_opt.cc:8-41): the reference only
  * wraps the subgraph in a loop fusion; this is that loop.
  * out[i,:] = (lo <= ids[i] < hi) ? table[ids[i],:] * 1.0f : table[dflt,:] * 0.0f.

@@ -477,3 +477,59 @@ def dlrm_forward(model, sample: int | None = None, threads: int = 1) -> np.ndarr
         if i + 1 < len(model.top):
             h = np.maximum(h, np.float32(0))
     return (np.float32(1) / (np.float32(1) + np.exp(-h, dtype=np.float32))).astype(np.float32)
+
+
+# ---------------------------------------------------------------- adjacent fused ops (numpy)
+
+def embedding_padding(origin_shape, x, input_rows, reshape_sizes, fast=False):
+    """KPFusedEmbeddingPadding{,Fast} (annc/tensorflow/kernels/embedding_fused_padding.cc:35-113)."""
+    x = _c(x, np.float32)
+    pad = int(origin_shape[0]) - int(input_rows)
+    cols = int(reshape_sizes[1])
+    out_rows = pad + x.shape[0]
+    rr = out_rows * x.shape[1] // cols
+    if fast:
+        return np.int32(pad), np.int32(rr)
+    flat = np.zeros(out_rows * x.shape[1], np.float32)
+    live = int(input_rows) * x.shape[1]
+    flat[:live] = x.reshape(-1)[:live]
+    return np.int32(pad), flat.reshape(rr, cols)
+
+
+def action_id_gather(indices1, params, indices2, pack_dim, pack):
+    """KPFusedEmbeddingActionIdGather
+    (annc/tensorflow/kernels/embedding_fused_action_id_gather.cc:59-129)."""
+    t1 = _c(params, np.float32)[np.asarray(indices1)]
+    t2 = t1[np.asarray(indices2)]
+    a = t2.reshape(int(pack_dim), -1)
+    return np.concatenate([a, np.zeros((int(pack_dim), int(pack)), np.float32)], axis=1)
+
+
+def sparse_reshape(slice_input, begin, new_shape, pack_const):
+    """KPFusedSparseReshape (annc/tensorflow/kernels/embedding_fused_sparse_reshape.cc:28-190)."""
+    s = _c(slice_input, np.int64)
+    rows = s.shape[0]
+    in_shape = [rows, int(pack_const)]
+    tgt = [int(v) for v in new_shape]
+    dense = in_shape[0] * in_shape[1]
+    out_shape = list(tgt)
+    if -1 in tgt:
+        k = tgt.index(-1)
+        other = tgt[1 - k]
+        out_shape[k] = dense // other
+    ids = np.arange(rows, dtype=np.int64) * in_shape[1] + s[:, int(begin[1])]
+    if out_shape == in_shape:
+        idx = np.stack([np.arange(rows, dtype=np.int64), s[:, int(begin[1])]], 1)
+    else:
+        idx = np.stack([ids // out_shape[1], ids % out_shape[1]], 1)
+    return idx, np.array(out_shape, np.int64)
+
+
+def sparse_select(a, b, greater, equal1, equal2):
+    """KPFusedSparseSelect (annc/tensorflow/kernels/embedding_fused_sparse_select.cc:32-107)."""
+    a = np.asarray(a, np.int32).reshape(-1)
+    b = np.asarray(b, np.int32).reshape(-1)
+    g = (a > greater).astype(np.float32)
+    r1 = np.where(b == equal1, np.float32(1), g)
+    r2 = np.where(b == equal2, np.float32(1), r1).astype(np.float32)
+    return a.astype(np.float32).reshape(-1, 1), r2.reshape(-1, 1), np.stack([r2, np.ones_like(r2)], 1)

@@ -166,3 +166,45 @@ def bmm_reference(lhs, rhs, bias):
                     acc = f32(acc + f32(lhs[bi, i, kk] * R[kk, j]))
                 out[bi, i, j] = f32(1.0) / (f32(1.0) + np.exp(-acc, dtype=f32))
     return out
+
+
+# embedding_fused_padding_test.cc:87-245: (embedding_dims, table_size, pooling_size, reshape_size);
+# input = 1..pooling*dims row-major; expected = the input followed by zeros, reshaped.
+PADDING = [(10, 151, 151, 1510), (10, 1510, 151, 1510), (12, 2, 2, 24), (12, 200, 2, 24)]
+# :247-305: (dims, table, pooling, reshape_sizes, pack, message)
+PADDING_ERRORS = [
+    (12, 200, 2, [10, 24], 12, "reshape[0] is not -1"),
+    (12, 200, 2, [-1, 24], 10, "pack(10) is not equal to embedding dims"),
+    (12, 200, 201, [-1, 24], 12, "Pooling size(201) is greater than Input size(200)"),
+]
+
+# embedding_fused_action_id_gather_test.cc:71-145
+ACTION_ID_GATHER = dict(indices1=np.array([[0], [2]]), params=np.array([[1, 2], [3, 4], [5, 6]], f32),
+                        indices2=np.array([[1], [0]]), pack_dim=2, pack=1,
+                        out=np.array([[5, 6, 0], [1, 2, 0]], f32))
+
+# embedding_fused_sparse_select_test.cc:128-155: (shape, a, b, c, greater, equal1, equal2, y)
+SPARSE_SELECT = [
+    ((3,), [5, 3, 8], [1, 2, 1], [9, 8, 7], 4, 1, 3, [1, 0, 1]),
+    ((2, 2), [6, 3, 8, 2], [2, 1, 3, 4], [0, 0, 0, 0], 5, 2, 3, [1, 0, 1, 0]),
+]
+
+# embedding_fused_sparse_reshape_test.cc:100-127: (slice, begin, new_shape, pack_const, out_shape)
+SPARSE_RESHAPE = [
+    (np.array([[0, 1], [1, 2], [2, 3], [3, 0]], i64), [0, 1], [2, 4], 2, [2, 4]),
+    (np.array([[0, 1]], i64), [0, 1], [-1, 1], 1, [1, 1]),
+]
+# :129-277: (slice, begin, new_shape, message)
+SPARSE_RESHAPE_ERRORS = [
+    (np.zeros((4,), i64), [0, 1], [2, 2], "slice_input dims must == 2"),
+    (np.zeros((4, 2), i64), [0, 1], [2, 2, 1], "new_shape dim size must == 2"),
+    (np.zeros((4, 2), i64), [0, 2], [2, 4], "begin[1] must < slice_input.dim_size(1)"),
+    (np.zeros((4, 2), i64), [0, 1], [-1, -1], "only one output dimension may be -1"),
+    (np.array([[0, 0], [0, 1], [0, 2], [1, 0], [1, 1], [1, 2]], i64), [0, 0], [-1, 4],
+     "Input to reshape is a SparseTensor with"),
+    (np.zeros((4, 2), i64), [0, 1], [3, 3], "Input to reshape is a tensor with"),
+    (np.zeros((4, 2), i64), [0, 1], [2, -2], "size 1 must be non-negative, not -2"),
+    (np.zeros((4, 2), i64), [0, 1], [-1, 0], "reshape cannot infer the missing input size for an empty tensor"),
+    (np.zeros((4, 2), i64), [0], [2, 4], "begin must be 1D with at least 2 elements"),
+    (np.zeros((4, 2), i64), [0, 1, 2], [2, 4], "begin must be 1D with at least 2 elements"),
+]
