@@ -53,6 +53,8 @@ def time_ms(fn, reps, flush):
 
 
 def bmm_case(name, b, m, n, k, reps):
+    if MATCH and MATCH not in f"{name}/kn":
+        return
     hbm, tf32, src = peaks()
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randn((b, m, k), device="cuda", generator=g)
@@ -71,7 +73,12 @@ def bmm_case(name, b, m, n, k, reps):
                       "peak": src}), flush=True)
 
 
+MATCH = ""
+
+
 def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False):
+    if MATCH and MATCH not in f"{name}/{bsrc}":
+        return
     hbm, tf32, src = peaks()
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randn((m, k), device="cuda", generator=g)
@@ -150,7 +157,9 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="all")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--match", default="", help="run only GEMM cases whose 'name/b-source' contains this")
     a = ap.parse_args()
+    MATCH = a.match
     if a.only in ("all", "gemm"):
         run_gemm(a.reps)
     if a.only in ("all", "embed"):

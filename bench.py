@@ -41,9 +41,12 @@ def parse_args():
     ap.add_argument("--max-rows", type=float, default=1e7)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard", default="row", choices=["row", "table", "replica"],
-                    help="table partitioning for --gpus > 1 (row = mod row-sharding + all-to-all of "
-                         "partial sums; table = whole tables per rank; replica = no exchange)")
+    ap.add_argument("--shard", default="auto", choices=["auto", "row", "table", "replica"],
+                    help="table partitioning for --gpus > 1: row = mod row-sharding + all-to-all of "
+                         "partial sums; table = whole tables per rank; replica = no exchange; auto = "
+                         "row when the tables exceed --hbm-budget-gb per GPU, else replica")
+    ap.add_argument("--hbm-budget-gb", type=float, default=100.0,
+                    help="per-GPU memory the tables may take before auto switches to row sharding")
     return ap.parse_args()
 
 
@@ -180,6 +183,9 @@ def run_gpu(args):
                              input_seed=(1000 + rank) if world > 1 else None)
     if world > 1:
         from annc_b200.sharded import ShardedDlrmPipeline
+        if args.shard == "auto":
+            table_gb = sum(t.nbytes for t in model.emb.tables) / 1e9
+            args.shard = "row" if table_gb > args.hbm_budget_gb else "replica"
         pipe = ShardedDlrmPipeline(model, devi, args.shard, keep_host_inputs=True)
     else:
         pipe = DlrmPipeline(model, devi, keep_host_inputs=True)
