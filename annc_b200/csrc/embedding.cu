@@ -51,6 +51,8 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
   for (int t = 0; t < num_tables; ++t) {
     if (tables[t].nnz >= (int64_t(1) << 31) - 1)
       return fail(ANNC_ERR_UNSUPPORTED, "more than 2^31-2 lookups in one table");
+    if (tables[t].rows >= (int64_t(1) << 31))
+      return fail(ANNC_ERR_UNSUPPORTED, "more than 2^31-1 rows in one (local) table");
     if (id_kind == 2 && tables[t].num_buckets < 1)
       return fail(ANNC_ERR_INVALID_ARGUMENT, "num_buckets must be >= 1");
     p.t[t].table = tables[t].table;

@@ -141,7 +141,7 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) {
 // row loads are in flight per group.  For an unsorted table the group writes the
 // zero row and clears the bag's counter; the scatter kernels then do the work.
 template <int LANES, int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, VPL == 1 ? 5 : 3)
 bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   constexpr int GROUPS_PER_WARP = 32 / LANES;
   const int lane_in_warp = threadIdx.x & 31;
@@ -174,18 +174,16 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
 
   const int start = off[s], end = off[s + 1];
   for (int base = start; base < end; base += LANES) {
-    long long my = -1;
+    int my = -1;  // local row (tables have fewer than 2^31 rows), -1 = skip
     if (base + lane < end) {
-      my = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets), p.shard_count,
-                     p.shard_rank);
-      if (my != kNotMine && (my < 0 || my >= T.rows)) {
-        atomicOr(&hdr->err_bits, kErrRow);
-        my = -1;
-      }
+      const long long r64 = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets),
+                                      p.shard_count, p.shard_rank);
+      if (r64 != kNotMine && (r64 < 0 || r64 >= T.rows)) atomicOr(&hdr->err_bits, kErrRow);
+      else if (r64 != kNotMine) my = (int)r64;
     }
     const int n = min(LANES, end - base);
     for (int j = 0; j < n; j += 4) {
-      long long r[4];
+      int r[4];
       float4 v[4][VPL];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -195,7 +193,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         if (r[q] >= 0) {
-          const float* src = T.table + r[q] * p.dim;
+          const float* src = T.table + (long long)r[q] * p.dim;
 #pragma unroll
           for (int w = 0; w < VPL; ++w) v[q][w] = ldg4(src + (w * LANES + lane) * 4);
         }
