@@ -30,7 +30,7 @@ class Tensor(C.Structure):
 class BagTable(C.Structure):
     _fields_ = [("table", C.c_void_p), ("rows", C.c_int64), ("num_buckets", C.c_int64),
                 ("ids", C.c_void_p), ("slice_input", C.c_void_p), ("nnz", C.c_int64),
-                ("out", C.c_void_p)]
+                ("out", C.c_void_p), ("offsets", C.c_void_p)]
 
 
 class GemmDesc(C.Structure):

@@ -62,16 +62,23 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
     p.t[t].rows = tables[t].rows;
     p.t[t].num_buckets = (unsigned long long)tables[t].num_buckets;
     p.t[t].nnz = tables[t].nnz;
+    p.t[t].given_off = tables[t].offsets;
     max_nnz = std::max<long long>(max_nnz, tables[t].nnz);
     vec_ok = vec_ok && aligned16(tables[t].table) && aligned16(tables[t].out);
   }
   if (batch <= 0) return ANNC_OK;
 
   dim3 pre_grid(grid_for(max_nnz + 1, 256), num_tables);
-  bool seg16 = ncols == 2;
-  for (int t = 0; t < num_tables; ++t) seg16 = seg16 && aligned16(tables[t].slice_input);
-  if (seg16) bag_prepass2_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
-  else bag_prepass_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
+  bool seg16 = ncols == 2, need_prepass = false;
+  for (int t = 0; t < num_tables; ++t) {
+    if (tables[t].offsets) continue;
+    need_prepass = true;
+    seg16 = seg16 && aligned16(tables[t].slice_input);
+  }
+  if (need_prepass) {  // tables that brought their offsets are skipped inside the kernel
+    if (seg16) bag_prepass2_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
+    else bag_prepass_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
+  }
 
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   timing_events(&ev0, &ev1);
@@ -227,6 +234,46 @@ int annc_embed_bags_sharded_dev(const annc_bag_table* tables, int num_tables, in
   return ANNC_OK;
 }
 
+int annc_embed_bag_prepass_dev(const annc_bag_table* tables, int num_tables, int64_t ncols,
+                               int32_t col, int64_t batch, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  ANNC_REQUIRE(tables && num_tables >= 1, ANNC_ERR_INVALID_ARGUMENT, "no tables");
+  ANNC_REQUIRE(col >= 0 && col < ncols, ANNC_ERR_INVALID_ARGUMENT, "Column index out of range");
+  ANNC_REQUIRE(workspace && workspace_bytes >= annc_embed_bag_workspace_bytes(num_tables, batch),
+               ANNC_ERR_INVALID_ARGUMENT, "workspace too small");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto* hdr = static_cast<BagHeader*>(workspace);
+  int* offsets = reinterpret_cast<int*>(static_cast<char*>(workspace) + kHeaderBytes);
+  ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
+  if (batch <= 0) return ANNC_OK;
+  for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
+    const int nt = std::min(kMaxTables, num_tables - t0);
+    BagParams p;
+    memset(&p, 0, sizeof(p));
+    p.num_tables = nt;
+    p.col = col;
+    p.ncols = ncols;
+    p.batch = batch;
+    long long max_nnz = 0;
+    bool seg16 = ncols == 2;
+    for (int t = 0; t < nt; ++t) {
+      ANNC_REQUIRE(tables[t0 + t].nnz < (int64_t(1) << 31) - 1, ANNC_ERR_UNSUPPORTED,
+                   "more than 2^31-2 lookups in one table");
+      p.t[t].seg = tables[t0 + t].slice_input;
+      p.t[t].nnz = tables[t0 + t].nnz;
+      max_nnz = std::max<long long>(max_nnz, tables[t0 + t].nnz);
+      seg16 = seg16 && aligned16(tables[t0 + t].slice_input);
+    }
+    // the marks of unsorted tables are per launch; a later launch reuses the slots
+    dim3 grid(grid_for(max_nnz + 1, 256), nt);
+    int* off = offsets + (size_t)t0 * (size_t)(batch + 1);
+    if (seg16) bag_prepass2_kernel<<<grid, 256, 0, s>>>(p, hdr, off);
+    else bag_prepass_kernel<<<grid, 256, 0, s>>>(p, hdr, off);
+  }
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
 int annc_embed_bag_check(void* workspace, void* stream, int* error_bits) {
   ANNC_REQUIRE(workspace && error_bits, ANNC_ERR_INVALID_ARGUMENT, "null argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -353,6 +400,7 @@ int annc_KPFusedSparseSegmentReduce(const annc_tensor* data, const annc_tensor* 
   tb.slice_input = d_seg;
   tb.nnz = nnz;
   tb.out = d_out;
+  tb.offsets = nullptr;
   auto* hdr = static_cast<BagHeader*>(ws);
   ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
   ANNC_TRY(run_bags(&tb, 1, dim, indices->dtype == ANNC_I64 ? 1 : 0, ncols, col, combiner, batch,
@@ -452,6 +500,7 @@ int annc_KPFusedSparseSegmentReduceNonzero(const annc_tensor* data, const annc_t
     tb.slice_input = reinterpret_cast<const int64_t*>(d_inv64);
     tb.nnz = nnz;
     tb.out = d_dense;
+    tb.offsets = nullptr;
     ANNC_TRY(run_bags(&tb, 1, dim, indices->dtype == ANNC_I64 ? 1 : 0, 1, 0, combiner, nseg, dim,
                       hdr, reinterpret_cast<int*>(static_cast<char*>(ws) + kHeaderBytes), s));
     nonzero_flag_kernel<<<grid_for(total, 256), 256, 0, s>>>(d_dense, total, d_flag);

@@ -12,7 +12,7 @@
 namespace annc {
 namespace emb {
 
-constexpr int kMaxTables = 64;          // tables per grouped launch
+constexpr int kMaxTables = 56;          // tables per grouped launch (keeps BagParams under 4 KB)
 constexpr int kErrRow = 1;              // row index outside its table
 constexpr int kErrSegment = 2;          // segment id outside [0, batch)
 
@@ -33,6 +33,7 @@ struct BagTableDev {
   long long rows;
   unsigned long long num_buckets;
   long long nnz;
+  const int* given_off;  // caller-supplied bag offsets [batch + 1] (then `seg` is not read)
 };
 
 struct BagParams {
@@ -57,6 +58,7 @@ struct BagParams {
 __global__ void bag_prepass_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   const int t = blockIdx.y;
   const BagTableDev& T = p.t[t];
+  if (T.given_off) return;
   int* off = offsets + (long long)t * (p.batch + 1);
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i <= T.nnz; i += stride) {
@@ -83,6 +85,7 @@ __global__ void __launch_bounds__(256)
 bag_prepass2_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   const int t = blockIdx.y;
   const BagTableDev& T = p.t[t];
+  if (T.given_off) return;
   int* off = offsets + (long long)t * (p.batch + 1);
   const int lane = threadIdx.x & 31;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -157,6 +160,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   const long long s = group - (long long)t * p.batch;
   const BagTableDev& T = p.t[t];
   int* off = offsets + (long long)t * (p.batch + 1);
+  const int* roff = T.given_off ? T.given_off : off;
   float* orow = T.out + s * p.out_stride;
 
   float4 acc[VPL];
@@ -172,7 +176,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
     return;
   }
 
-  const int start = off[s], end = off[s + 1];
+  const int start = roff[s], end = roff[s + 1];
   for (int base = start; base < end; base += LANES) {
     int my = -1;  // local row (tables have fewer than 2^31 rows), -1 = skip
     if (base + lane < end) {
@@ -241,7 +245,8 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
     if (lane == 0) off[s] = 0;
     return;
   }
-  const int start = off[s], end = off[s + 1];
+  const int* roff = T.given_off ? T.given_off : off;
+  const int start = roff[s], end = roff[s + 1];
   const float inv = (p.combiner == 1 && end > start) ? __fdiv_rn(1.0f, (float)(end - start)) : 1.0f;
   for (long long c0 = 0; c0 < p.dim; c0 += 32) {
     const long long c = c0 + lane;

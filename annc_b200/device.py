@@ -140,7 +140,8 @@ def gemm_timed_out() -> bool:
 class BagLaunch:
     """Grouped embedding-bag launch over explicit (table, ids, segments, output) entries,
     optionally row-sharded (annc_embed_bags_sharded_dev).  Each entry is a tuple
-    (table_ptr, local_rows, num_buckets, ids_ptr, seg_ptr, nnz, out_ptr)."""
+    (table_ptr, local_rows, num_buckets, ids_ptr, seg_ptr, nnz, out_ptr[, offsets_ptr]); with
+    offsets_ptr (i32[batch + 1] bag offsets) the segment matrix is not read."""
 
     def __init__(self, entries, dim: int, batch: int, ncols: int, out_stride: int,
                  device: torch.device, id_kind: int = 2, col: int = 0, combiner: int = 0,
@@ -150,10 +151,12 @@ class BagLaunch:
         self.id_kind, self.col, self.combiner = id_kind, col, combiner
         self.shard_count, self.shard_rank = shard_count, shard_rank
         self.desc = (BagTable * self.n)()
-        for i, (tp, rows, nb, ip, sp, nnz, op) in enumerate(entries):
+        for i, e in enumerate(entries):
+            tp, rows, nb, ip, sp, nnz, op = e[:7]
             d = self.desc[i]
             d.table, d.rows, d.num_buckets, d.ids, d.slice_input, d.nnz, d.out = \
                 tp, int(rows), int(nb), ip, sp, int(nnz), op
+            d.offsets = e[7] if len(e) > 7 else None
         self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
 
@@ -183,3 +186,24 @@ def copy_rows(dst_ptr: int, dst_stride: int, src_ptr: int, src_stride: int, widt
     """2-D device copy of `rows` rows of `width` floats between pitched buffers."""
     check(lib.annc_copy_rows_dev(C.c_void_p(dst_ptr), C.c_int64(dst_stride), C.c_void_p(src_ptr),
                                  C.c_int64(src_stride), C.c_int64(width), C.c_int64(rows), _stream()))
+
+
+class BagPrepass:
+    """Segment prepass alone (annc_embed_bag_prepass_dev): bag offsets of every table's
+    lookups into `ws` (512-byte header, then i32 offsets[tables][batch + 1])."""
+
+    def __init__(self, slice_inputs: Sequence[torch.Tensor], batch: int, col: int = 0):
+        self.n = len(slice_inputs)
+        self.batch, self.col = int(batch), col
+        self.ncols = int(slice_inputs[0].shape[1])
+        self.desc = (BagTable * self.n)()
+        for t, s in enumerate(slice_inputs):
+            self.desc[t].slice_input = s.data_ptr()
+            self.desc[t].nnz = int(s.shape[0])
+        self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
+
+    def run(self, ws: torch.Tensor) -> None:
+        check(lib.annc_embed_bag_prepass_dev(self.desc, C.c_int(self.n), C.c_int64(self.ncols),
+                                             C.c_int32(self.col), C.c_int64(self.batch),
+                                             C.c_void_p(ws.data_ptr()), C.c_size_t(self.ws_bytes),
+                                             _stream()))

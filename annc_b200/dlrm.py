@@ -101,6 +101,9 @@ class DlrmPipeline:
                                      id_kind=2, col=0, combiner=0)
         self._use(self.cur)
 
+    def embed_prefetch(self) -> None:
+        """Hook called before the bottom MLP (multi-GPU variants start their exchange here)."""
+
     def embed(self) -> None:
         self.plan.run()
 
@@ -113,6 +116,7 @@ class DlrmPipeline:
         B, F, D = self.batch, self.F, self.dim
         x = self.dense
         nb = len(self.bottom)
+        self.embed_prefetch()
         for i, (w, b) in enumerate(self.bottom):
             last = i == nb - 1
             y = self.z if last else self.acts_b[i]

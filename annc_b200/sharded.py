@@ -103,12 +103,18 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 self.exchange_bytes = 0
                 return
             if mode == "row":
+                # Only the raw ids (8 bytes per lookup) and the bag offsets of each rank's
+                # batch travel: every rank runs the prepass on its own index matrices and
+                # the offsets (4 bytes per bag) are gathered with the ids.
                 self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
                 L = plan.gathered_len()
                 self.ids_pad = torch.zeros(L, **i64)
-                self.seg_pad = torch.zeros((L, 2), **i64)
                 self.ids_g = torch.zeros((world, L), **i64)
-                self.seg_g = torch.zeros((world, L, 2), **i64)
+                for st in self.sets:
+                    st["prepass"] = dev.BagPrepass(st["segs"], B)
+                wsb = self.sets[0]["prepass"].ws_bytes
+                self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
+                self.off_g = torch.zeros((world, wsb), dtype=torch.uint8, device=self.device)
                 self.partial = torch.empty((world, B, T, D), **f32)
                 self.recv = torch.empty((world, B, T, D), **f32)
                 entries = []
@@ -117,14 +123,15 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                         off = plan.gathered_offset(s, t)
                         entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
                                         plan.table_rows[t],
-                                        self.ids_g.data_ptr() + (s * L + off) * 8,
-                                        self.seg_g.data_ptr() + (s * L + off) * 16,
+                                        self.ids_g.data_ptr() + (s * L + off) * 8, None,
                                         int(plan.nnz[s, t]),
-                                        self.partial.data_ptr() + ((s * B) * T + t) * D * 4))
+                                        self.partial.data_ptr() + ((s * B) * T + t) * D * 4,
+                                        self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
                 self.launch = dev.BagLaunch(entries, D, B, 2, T * D, self.device, shard_count=world,
                                             shard_rank=rank)
-                self.embed_launches = 3 * ((len(entries) + 63) // 64) + 1
-                self.exchange_bytes = (world - 1) * B * T * D * 4 + (world - 1) * L * 24
+                self.embed_launches = 2 * ((len(entries) + 55) // 56) + 2
+                self.exchange_bytes = (world - 1) * (B * T * D * 4 + L * 8 + wsb)
+                self._works = None
                 return
             # table mode
             mine = plan.owned[rank]
@@ -132,8 +139,15 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             sc, rc = plan.send_counts(), plan.recv_counts()
             self.sc, self.rc = sc, rc
             self.ids_r = torch.zeros(max(1, sum(rc)), **i64)
-            self.seg_r = torch.zeros((max(1, sum(rc)), 2), **i64)
             To = len(mine)
+            # bag offsets travel instead of the index matrices: 4 bytes per bag, not 16 per lookup
+            for st in self.sets:
+                st["prepass"] = dev.BagPrepass(st["segs"], B)
+            wsb = self.sets[0]["prepass"].ws_bytes
+            self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
+            self.off_send = self.off_ws[512:512 + T * (B + 1) * 4].view(torch.int32)
+            self.off_sc = [len(plan.owned[p]) * (B + 1) for p in range(world)]
+            self.off_r = torch.zeros(max(1, world * To * (B + 1)), dtype=torch.int32, device=self.device)
             self.pooled = torch.empty((world, B, max(To, 1), D), **f32)
             counts_back = [len(plan.owned[p]) * B * D for p in range(world)]
             self.back = torch.empty(sum(counts_back), **f32)
@@ -143,12 +157,12 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 for j, t in enumerate(mine):
                     off = plan.recv_offset(s, j)
                     entries.append((self.tables[j].data_ptr(), plan.table_rows[t], plan.table_rows[t],
-                                    self.ids_r.data_ptr() + off * 8, self.seg_r.data_ptr() + off * 16,
-                                    int(plan.nnz[s, t]),
-                                    self.pooled.data_ptr() + ((s * B) * To + j) * D * 4))
+                                    self.ids_r.data_ptr() + off * 8, None, int(plan.nnz[s, t]),
+                                    self.pooled.data_ptr() + ((s * B) * To + j) * D * 4,
+                                    self.off_r.data_ptr() + ((s * To + j) * (B + 1)) * 4))
             self.launch = dev.BagLaunch(entries, D, B, 2, max(To, 1) * D, self.device) if entries else None
             self.embed_launches = 3 * ((len(entries) + 63) // 64) + world
-            self.exchange_bytes = (sum(sc) - sc[rank]) * 24 + (T - To) * B * D * 4
+            self.exchange_bytes = (sum(sc) - sc[rank]) * 8 + (T - To) * (B + 1) * 4 + (T - To) * B * D * 4
 
         def embed(self) -> None:
             plan = self.shard
@@ -156,20 +170,22 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "replica":
                 return DlrmPipeline.embed(self)
             if mode == "row":
-                n = self.nnz_total
-                self.ids_pad[:n].copy_(self.ids_all)
-                self.seg_pad[:n].copy_(self.seg_all)
-                dist.all_gather_into_tensor(self.ids_g, self.ids_pad)
-                dist.all_gather_into_tensor(self.seg_g, self.seg_pad)
+                if self._works is None:
+                    self.embed_prefetch()
+                for w in self._works:
+                    w.wait()
+                self._works = None
                 self.launch.run()
                 dist.all_to_all_single(self.recv, self.partial)
                 dev.sum_partials(self.recv, world, B * T * D, B, T * D, T * D,
                                  self.z.data_ptr() + D * 4, F * D)
                 return
             # table mode: ids to the owners, pooled vectors back
-            dist.all_to_all_single(self.ids_r[:sum(self.rc)], self.ids_all, self.rc, self.sc)
-            dist.all_to_all_single(self.seg_r[:sum(self.rc)], self.seg_all, self.rc, self.sc)
             To = len(plan.owned[rank])
+            self.sets[self.cur]["prepass"].run(self.off_ws)
+            dist.all_to_all_single(self.ids_r[:sum(self.rc)], self.ids_all, self.rc, self.sc)
+            dist.all_to_all_single(self.off_r[:world * To * (B + 1)], self.off_send,
+                                   [To * (B + 1)] * world, self.off_sc)
             if self.launch is not None:
                 self.launch.run()
             send = self.pooled.view(-1)[:world * B * To * D]
@@ -182,6 +198,17 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                     dev.copy_rows(self.z.data_ptr() + (1 + first) * D * 4, F * D,
                                   self.back.data_ptr() + off * 4, tp * D, tp * D, B)
                 off += self.back_counts[p]
+
+        def embed_prefetch(self) -> None:
+            """Row mode: starts the gathers of ids and bag offsets; the bottom MLP runs
+            while they are in flight."""
+            if mode != "row":
+                return
+            n = self.nnz_total
+            self.ids_pad[:n].copy_(self.ids_all)
+            self.sets[self.cur]["prepass"].run(self.off_ws)
+            self._works = [dist.all_gather_into_tensor(self.ids_g, self.ids_pad, async_op=True),
+                           dist.all_gather_into_tensor(self.off_g, self.off_ws, async_op=True)]
 
         def embed_error_bits(self) -> int:
             if mode == "replica":

@@ -225,6 +225,11 @@ typedef struct annc_bag_table {
   const int64_t* slice_input;  /* i64[nnz, ncols]                      */
   int64_t nnz;
   float* out;                  /* first output row of this table       */
+  const int32_t* offsets;      /* optional i32[batch + 1] bag offsets (lookups of bag s are
+                                  ids[offsets[s] .. offsets[s+1])); when set, slice_input is
+                                  not read and may be NULL.  Produced by
+                                  annc_embed_bag_prepass_dev, e.g. on the rank that owns the
+                                  batch, so that only ids and offsets need to travel */
 } annc_bag_table;
 
 size_t annc_embed_bag_workspace_bytes(int num_tables, int64_t batch);
@@ -240,8 +245,7 @@ int annc_embed_bags_dev(const annc_bag_table* tables /* host array */, int num_t
  * annc_bag_table is the local row count, num_buckets stays the global modulus.  Lookups
  * owned by other ranks are skipped, so `out` receives this rank's partial sums; with
  * combiner 1 the partial is scaled by 1/len(bag) (the full bag length), so the partials of
- * all ranks add up to the mean.  The marks of unsorted tables are kept per launch of up to
- * 64 tables. */
+ * all ranks add up to the mean. */
 int annc_embed_bags_sharded_dev(const annc_bag_table* tables /* host array */, int num_tables,
                                 int64_t dim, int id_kind, int64_t ncols, int32_t col, int combiner,
                                 int64_t batch, int64_t out_stride, int shard_count,
@@ -280,6 +284,14 @@ int annc_embed_bags_static_dev(const annc_bag_table* tables /* host array */, in
                                int64_t dim, int id_kind, int64_t ncols, int32_t col, int combiner,
                                int64_t batch, int64_t out_stride, int* error_bits_dev,
                                void* stream);
+
+/* Runs only the segment prepass: fills the workspace (layout of
+ * annc_embed_bag_workspace_bytes: 512-byte header, then i32 offsets[num_tables][batch + 1])
+ * from column `col` of every table's slice_input.  The offsets of table t start at byte
+ * 512 + 4 * t * (batch + 1) of the workspace. */
+int annc_embed_bag_prepass_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                               int64_t ncols, int32_t col, int64_t batch, void* workspace,
+                               size_t workspace_bytes, void* stream);
 
 /* Reads the device-side error word the embedding kernels set (0 = clean,
  * bit 0 = row index outside its table, bit 1 = segment id outside [0,batch)).
