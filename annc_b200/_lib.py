@@ -52,7 +52,7 @@ ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m annc_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python annc_b200/build.py` "
             "(nvcc, sm_100a). annc_b200 has no CPU fallback.")
     lib = C.CDLL(LIB_PATH)
     lib.annc_last_error.restype = C.c_char_p

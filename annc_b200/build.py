@@ -1,6 +1,6 @@
 """Builds libannc_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m annc_b200.build [--force] [--verbose]
+    python annc_b200/build.py [--force] [--verbose]
 
 Every .cu under annc_b200/csrc is compiled to an object in annc_b200/build/ and the
 objects are linked into annc_b200/lib/libannc_b200.so.  Objects are rebuilt when a
