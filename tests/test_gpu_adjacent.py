@@ -8,8 +8,8 @@ from oracle import oracle
 from tests.golden import reference_cases as rc
 
 pytestmark = pytest.mark.gpu
-torch = pytest.importorskip("torch")
-ops = pytest.importorskip("annc_b200.ops")
+import torch
+from annc_b200 import ops  # noqa: E402  (no fallback: a missing library fails the collection)
 from annc_b200 import AnncError  # noqa: E402
 
 

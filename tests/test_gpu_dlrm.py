@@ -6,8 +6,8 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-torch = pytest.importorskip("torch")
-pytest.importorskip("annc_b200")
+import torch
+import annc_b200  # noqa: F401,E402  (no fallback: a missing library fails the collection)
 from annc_b200 import synth  # noqa: E402
 from annc_b200._lib import MATH_AUTO, MATH_FP32  # noqa: E402
 from annc_b200.dlrm import DlrmPipeline  # noqa: E402

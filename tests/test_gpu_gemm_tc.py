@@ -8,8 +8,8 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-torch = pytest.importorskip("torch")
-pytest.importorskip("annc_b200")
+import torch
+import annc_b200  # noqa: F401,E402  (no fallback: a missing library fails the collection)
 from annc_b200 import device  # noqa: E402
 from annc_b200._lib import (ACT_NONE, ACT_RELU, ACT_SIGMOID, B_KN4, B_PLAIN, MATH_FP32,  # noqa: E402
                             MATH_TF32)

@@ -7,7 +7,7 @@ import sys
 import pytest
 
 pytestmark = pytest.mark.gpu
-torch = pytest.importorskip("torch")
+import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 

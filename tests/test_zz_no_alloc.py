@@ -10,8 +10,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-torch = pytest.importorskip("torch")
-pytest.importorskip("annc_b200")
+import torch
+import annc_b200  # noqa: F401,E402  (no fallback: a missing library fails the collection)
 from annc_b200 import AnncError, synth  # noqa: E402
 from annc_b200._lib import BagTable, check, lib  # noqa: E402
 from annc_b200.device import BagPlan  # noqa: E402
