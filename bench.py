@@ -30,6 +30,11 @@ if ROOT not in sys.path:
 METRIC = "dlrm_inference_samples_per_s"
 UNIT = "samples/s"
 
+# DRAM bytes (read + write) of one bag-kernel launch, from a single-pass ncu capture of this
+# command's default workload (profiles/bag_reduce_kernel_dlrm_batch65536_traffic_and_launch_list.md).
+# Keyed by (batch, max_rows, seed); any other workload reports null.
+NCU_BAG_TRAFFIC_BYTES = {(65536, 1e7, 0): 1.573e9}
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -263,7 +268,10 @@ def run_gpu(args):
                 "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
                 "algorithmic_bytes_per_launch": emb_bytes, "lookups_per_launch": nnz,
-                "kernel_ms": bag_avg_ms, "traffic": None}
+                "kernel_ms": bag_avg_ms,
+                "traffic": NCU_BAG_TRAFFIC_BYTES.get((args.batch, float(args.max_rows), args.seed)),
+                "traffic_note": "dram read+write bytes per launch from ncu; below the algorithmic "
+                                "bytes because Zipf-hot rows are served by L2"}
 
     if world > 1:
         roofline = {"bound": "hbm", "kernel": roofline["kernel"], "achieved": None, "peak": hbm_peak,
