@@ -181,6 +181,51 @@ def sum_partials(src: torch.Tensor, parts: int, part_stride: int, rows: int, wid
                                     C.c_void_p(out_ptr), C.c_int64(out_stride), _stream()))
 
 
+def sum_partials_ptr(src_ptr: int, parts: int, part_stride: int, rows: int, width: int,
+                     src_stride: int, out_ptr: int, out_stride: int) -> None:
+    check(lib.annc_sum_partials_dev(C.c_void_p(src_ptr), C.c_int(parts), C.c_int64(part_stride),
+                                    C.c_int64(rows), C.c_int64(width), C.c_int64(src_stride),
+                                    C.c_void_p(out_ptr), C.c_int64(out_stride), _stream()))
+
+
+class PeerBuffers:
+    """One receive buffer per rank, mapped into every rank (annc_peer_buffer_*).  `local` is
+    this rank's buffer, `ptrs[p]` the address under which rank p's buffer is seen here.
+    Handles travel through torch.distributed (host side); the data path is plain stores."""
+
+    def __init__(self, nbytes: int, world: int, rank: int):
+        import torch.distributed as dist
+        ptr = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        check(lib.annc_peer_buffer_create(C.c_size_t(nbytes), C.byref(ptr), handle))
+        self.local = int(ptr.value)
+        self.nbytes, self.rank = nbytes, rank
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle))
+        self.ptrs = []
+        for p in range(world):
+            if p == rank:
+                self.ptrs.append(self.local)
+                continue
+            q = C.c_void_p()
+            buf = (C.c_ubyte * 64).from_buffer_copy(handles[p])
+            check(lib.annc_peer_buffer_open(buf, C.byref(q)))
+            self.ptrs.append(int(q.value))
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers, waits for every rank to have done so, frees this one."""
+        import torch.distributed as dist
+        for p, q in enumerate(self.ptrs):
+            if p != self.rank and q:
+                check(lib.annc_peer_buffer_close(C.c_void_p(q)))
+        self.ptrs = []
+        if dist.is_initialized():
+            dist.barrier()
+        if self.local:
+            check(lib.annc_peer_buffer_destroy(C.c_void_p(self.local)))
+            self.local = 0
+
+
 def copy_rows(dst_ptr: int, dst_stride: int, src_ptr: int, src_stride: int, width: int,
               rows: int) -> None:
     """2-D device copy of `rows` rows of `width` floats between pitched buffers."""

@@ -6,8 +6,14 @@ Three partitionings of the tables, the MLPs always run on the rank's own batch s
   row      every table row-sharded with the reference's mod rule
            (owner = bucket % G, local row = bucket / G,
            annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71).
-           Ids are all-gathered, every rank pools the lookups it owns for the global
-           batch, partial sums go through an NCCL all-to-all and are added in rank order.
+           Ids and bag offsets are all-gathered, every rank pools the lookups it owns for
+           the global batch, and the bag kernel stores each partial sum straight into the
+           memory of the rank that owns the sample (peer-mapped receive buffers,
+           annc_peer_buffer_*): pooling and exchange are one kernel.  A one-element
+           all-reduce orders the stores before the owner adds the parts in rank order.
+  row_nccl the same partitioning with the exchange as a separate step: partial sums are
+           written locally, then go through an NCCL all-to-all (kept as the baseline the
+           fused step is measured against).
   table    whole tables per rank (contiguous blocks); ids travel to the owners by
            all-to-all, finished pooled vectors come back by all-to-all, no add.
   replica  every rank holds every table; no exchange (scaling ceiling when tables fit).
@@ -25,7 +31,7 @@ class ShardPlan:
     """Sizes and offsets of the exchange.  nnz[s][t] = lookups of rank s in table t."""
 
     def __init__(self, mode: str, world: int, rank: int, table_rows: List[int], nnz: np.ndarray):
-        assert mode in ("row", "table", "replica")
+        assert mode in ("row", "row_nccl", "table", "replica")
         self.mode, self.world, self.rank = mode, world, rank
         self.table_rows = list(table_rows)
         self.T = len(table_rows)
@@ -102,7 +108,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 DlrmPipeline._setup_embedding(self, m)
                 self.exchange_bytes = 0
                 return
-            if mode == "row":
+            if mode in ("row", "row_nccl"):
                 # Only the raw ids (8 bytes per lookup) and the bag offsets of each rank's
                 # batch travel: every rank runs the prepass on its own index matrices and
                 # the offsets (4 bytes per bag) are gathered with the ids.
@@ -115,20 +121,34 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 wsb = self.sets[0]["prepass"].ws_bytes
                 self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
                 self.off_g = torch.zeros((world, wsb), dtype=torch.uint8, device=self.device)
-                self.partial = torch.empty((world, B, T, D), **f32)
-                self.recv = torch.empty((world, B, T, D), **f32)
-                entries = []
-                for s in range(world):
-                    for t in range(T):
-                        off = plan.gathered_offset(s, t)
-                        entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
-                                        plan.table_rows[t],
-                                        self.ids_g.data_ptr() + (s * L + off) * 8, None,
-                                        int(plan.nnz[s, t]),
-                                        self.partial.data_ptr() + ((s * B) * T + t) * D * 4,
-                                        self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
-                self.launch = dev.BagLaunch(entries, D, B, 2, T * D, self.device, shard_count=world,
-                                            shard_rank=rank)
+                part_bytes = B * T * D * 4
+                if mode == "row":
+                    # Two receive buffers [world, B, T, D] used on alternate steps: a peer may
+                    # start storing step i+1 while this rank still adds the parts of step i.
+                    self.peer = dev.PeerBuffers(2 * world * part_bytes, world, rank)
+                    self.flag = torch.zeros(1, **f32)
+                    out_of = lambda buf, s: self.peer.ptrs[s] + (buf * world + rank) * part_bytes
+                    nbuf = 2
+                else:
+                    self.partial = torch.empty((world, B, T, D), **f32)
+                    self.recv = torch.empty((world, B, T, D), **f32)
+                    out_of = lambda buf, s: self.partial.data_ptr() + s * part_bytes
+                    nbuf = 1
+                self.launches = []
+                for buf in range(nbuf):
+                    entries = []
+                    for s in range(world):
+                        for t in range(T):
+                            off = plan.gathered_offset(s, t)
+                            entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
+                                            plan.table_rows[t],
+                                            self.ids_g.data_ptr() + (s * L + off) * 8, None,
+                                            int(plan.nnz[s, t]), out_of(buf, s) + t * D * 4,
+                                            self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
+                    self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device,
+                                                       shard_count=world, shard_rank=rank))
+                self.launch = self.launches[0]
+                self._row_step = 0
                 self.embed_launches = 2 * ((len(entries) + 55) // 56) + 2
                 self.exchange_bytes = (world - 1) * (B * T * D * 4 + L * 8 + wsb)
                 self._works = None
@@ -169,12 +189,22 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             T, B, D, F = self.T, self.batch, self.dim, self.F
             if mode == "replica":
                 return DlrmPipeline.embed(self)
-            if mode == "row":
+            if mode in ("row", "row_nccl"):
                 if self._works is None:
                     self.embed_prefetch()
                 for w in self._works:
                     w.wait()
                 self._works = None
+                if mode == "row":
+                    buf = self._row_step % 2
+                    self._row_step += 1
+                    self.launch = self.launches[buf]
+                    self.launch.run()           # partial sums land in their owners' memory
+                    dist.all_reduce(self.flag)  # every rank's bag kernel has finished
+                    dev.sum_partials_ptr(self.peer.local + buf * world * B * T * D * 4, world,
+                                         B * T * D, B, T * D, T * D,
+                                         self.z.data_ptr() + D * 4, F * D)
+                    return
                 self.launch.run()
                 dist.all_to_all_single(self.recv, self.partial)
                 dev.sum_partials(self.recv, world, B * T * D, B, T * D, T * D,
@@ -202,7 +232,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def embed_prefetch(self) -> None:
             """Row mode: starts the gathers of ids and bag offsets; the bottom MLP runs
             while they are in flight."""
-            if mode != "row":
+            if mode not in ("row", "row_nccl"):
                 return
             n = self.nnz_total
             self.ids_pad[:n].copy_(self.ids_all)
@@ -213,6 +243,8 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def embed_error_bits(self) -> int:
             if mode == "replica":
                 return DlrmPipeline.embed_error_bits(self)
+            if mode == "row":
+                return self.launches[0].error_bits() | self.launches[1].error_bits()
             return self.launch.error_bits() if self.launch is not None else 0
 
     return _Pipe(model, device, math=MATH_AUTO if math is None else math,

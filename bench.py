@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--max-rows", type=float, default=1e7)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard", default="auto", choices=["auto", "row", "table", "replica"],
-                    help="table partitioning for --gpus > 1: row = mod row-sharding + all-to-all of "
-                         "partial sums; table = whole tables per rank; replica = no exchange; auto = "
+    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_nccl", "table", "replica"],
+                    help="table partitioning for --gpus > 1: row = mod row-sharding, the bag kernel "
+                         "stores partial sums into the owner rank's memory; row_nccl = the same with "
+                         "a separate NCCL all-to-all; table = whole tables per rank; replica = no exchange; auto = "
                          "row when the tables exceed --hbm-budget-gb per GPU, else replica")
     ap.add_argument("--hbm-budget-gb", type=float, default=100.0,
                     help="per-GPU memory the tables may take before auto switches to row sharding")
@@ -300,6 +301,9 @@ def run_gpu(args):
                                               % args.batch}
         print(json.dumps(line), flush=True)
     if world > 1:
+        if hasattr(pipe, "peer"):
+            torch.cuda.synchronize()
+            pipe.peer.close()
         dist.destroy_process_group()
 
 

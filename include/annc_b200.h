@@ -263,6 +263,22 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
 int annc_copy_rows_dev(float* dst, int64_t dst_stride, const float* src, int64_t src_stride,
                        int64_t width, int64_t rows, void* stream);
 
+/* Receive buffers for the fused pooling + exchange step of a row-sharded table (one process
+ * per GPU, GPUs of one node).  annc_peer_buffer_create allocates `bytes` of device memory on
+ * the current device and fills the 64-byte `handle64`; the owner sends the handle to its peers
+ * over any host channel, and each peer maps the buffer with annc_peer_buffer_open.  The mapped
+ * pointer can be used as `out` of annc_bag_table: the bag kernel then stores this rank's
+ * partial sums directly into the owner's memory (ordinary 16-byte stores over NVLink; no
+ * multicast), where annc_sum_partials_dev adds the parts in rank order once every rank's
+ * kernel has finished (a stream-ordered barrier between the two is the caller's, e.g. a
+ * one-element all-reduce).  This replaces the reference-side pattern "pool, then exchange"
+ * (the mod partition of embedding_fused_sparse_dynamic_stitch.cc:70-71 across parameter
+ * servers) by one kernel.  Peers close their mapping before the owner destroys the buffer. */
+int annc_peer_buffer_create(size_t bytes, void** dev_ptr, void* handle64);
+int annc_peer_buffer_open(const void* handle64, void** dev_ptr);
+int annc_peer_buffer_close(void* dev_ptr);
+int annc_peer_buffer_destroy(void* dev_ptr);
+
 /* Same operation as annc_embed_bags_dev for callers that must not allocate device
  * memory and have none to lend: code running inside a framework callback where
  * cudaMalloc is forbidden or would deadlock (an allocator hook, a stream-ordered

@@ -26,6 +26,11 @@ def main():
     pipe = ShardedDlrmPipeline(model, dev, mode)
     got = pipe.forward().cpu().numpy()
     assert pipe.embed_error_bits() == 0
+    if mode == "row":
+        # the receive buffers alternate between steps: a second and third step must agree
+        for _ in range(2):
+            again = pipe.forward().cpu().numpy()
+            assert np.array_equal(again, got), "row-sharded steps differ between receive buffers"
     want = oracle.dlrm_forward(model, threads=4)
     z = pipe.z.cpu().numpy()
     emb = model.emb
@@ -39,6 +44,9 @@ def main():
     assert perr <= 1e-5, perr          # fp32 pooling tolerance under row sharding
     assert np.abs(got - want).max() <= 2e-3  # TF32 MLP
     dist.barrier()
+    if hasattr(pipe, "peer"):
+        torch.cuda.synchronize()
+        pipe.peer.close()
     dist.destroy_process_group()
     print(f"rank {rank} mode {mode} ok pooled_err {perr:.2e}")
 

@@ -1,4 +1,5 @@
-"""Multi-GPU parity of the row-sharded, table-sharded and replica embedding steps.
+"""Multi-GPU parity of the row-sharded (fused peer-store exchange and NCCL all-to-all),
+table-sharded and replica embedding steps.
 Runs tests/sharded_worker.py under torchrun on 2 (or up to 4) GPUs; skipped on one GPU."""
 import os
 import subprocess
@@ -11,7 +12,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("mode", ["row", "table", "replica"])
+@pytest.mark.parametrize("mode", ["row", "row_nccl", "table", "replica"])
 def test_sharded_pipeline_matches_oracle(mode):
     n = torch.cuda.device_count()
     if n < 2:
