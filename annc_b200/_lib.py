@@ -75,6 +75,10 @@ def _load() -> C.CDLL:
     lib.annc_peer_buffer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     lib.annc_peer_buffer_close.argtypes = [C.c_void_p]
     lib.annc_peer_buffer_destroy.argtypes = [C.c_void_p]
+    lib.annc_embed_bag_owner_mask_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int,
+                                                  C.c_void_p, C.c_void_p]
+    lib.annc_sum_partials_masked_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                                                 C.c_int, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
     lib.annc_register_constant.argtypes = [C.c_void_p, C.c_size_t]
     lib.annc_unregister_constant.argtypes = [C.c_void_p]
     return lib

@@ -26,18 +26,20 @@ static void launch_bag(const BagParams& p, BagHeader* hdr, int* offsets, cudaStr
   const long long groups = (long long)p.num_tables * p.batch;
   const long long groups_per_block = (256 / 32) * (32 / LANES);
   const long long blocks = (groups + groups_per_block - 1) / groups_per_block;
-  bag_reduce_kernel<LANES, VPL><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
+  if (p.shard_count > 1) bag_reduce_kernel<LANES, VPL, true><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
+  else bag_reduce_kernel<LANES, VPL, false><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
 }
 
 // Launches prepass + bag kernels (+ the atomic route) for up to kMaxTables tables.
 static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, int id_kind,
                     int64_t ncols, int32_t col, int combiner, int64_t batch, int64_t out_stride,
                     BagHeader* hdr, int* offsets, cudaStream_t s, int shard_count = 1,
-                    int shard_rank = 0) {
+                    int shard_rank = 0, int skip_empty = 0) {
   BagParams p;
   memset(&p, 0, sizeof(p));
   p.shard_count = shard_count;
   p.shard_rank = shard_rank;
+  p.skip_empty = skip_empty;
   p.num_tables = num_tables;
   p.id_kind = id_kind;
   p.combiner = combiner;
@@ -207,20 +209,23 @@ int annc_embed_bags_dev(const annc_bag_table* tables, int num_tables, int64_t di
   return ANNC_OK;
 }
 
-int annc_embed_bags_sharded_dev(const annc_bag_table* tables, int num_tables, int64_t dim,
-                                int id_kind, int64_t ncols, int32_t col, int combiner,
-                                int64_t batch, int64_t out_stride, int shard_count,
-                                int shard_rank, void* workspace, size_t workspace_bytes,
-                                void* stream) {
+static int bags_sharded(const annc_bag_table* tables, int num_tables, int64_t dim, int id_kind,
+                        int64_t ncols, int32_t col, int combiner, int64_t batch,
+                        int64_t out_stride, int shard_count, int shard_rank, int skip_empty,
+                        void* workspace, size_t workspace_bytes, void* stream) {
   ANNC_REQUIRE(tables && num_tables >= 1, ANNC_ERR_INVALID_ARGUMENT, "no tables");
   ANNC_REQUIRE(combiner == 0 || combiner == 1, ANNC_ERR_INVALID_ARGUMENT, "combiner must be 0 or 1");
   ANNC_REQUIRE(id_kind >= 0 && id_kind <= 2, ANNC_ERR_INVALID_ARGUMENT, "id_kind must be 0, 1 or 2");
   ANNC_REQUIRE(col >= 0 && col < ncols, ANNC_ERR_INVALID_ARGUMENT, "Column index out of range");
   ANNC_REQUIRE(dim >= 1 && out_stride >= dim, ANNC_ERR_INVALID_ARGUMENT, "bad dim / out_stride");
-  ANNC_REQUIRE(shard_count >= 1 && shard_rank >= 0 && shard_rank < shard_count,
+  ANNC_REQUIRE(shard_count >= 1 && shard_count <= 32 && shard_rank >= 0 && shard_rank < shard_count,
                ANNC_ERR_INVALID_ARGUMENT, "bad shard_count / shard_rank");
   ANNC_REQUIRE(workspace && workspace_bytes >= annc_embed_bag_workspace_bytes(num_tables, batch),
                ANNC_ERR_INVALID_ARGUMENT, "workspace too small");
+  if (skip_empty)
+    for (int t = 0; t < num_tables; ++t)
+      ANNC_REQUIRE(tables[t].offsets, ANNC_ERR_INVALID_ARGUMENT,
+                   "skipping unowned bags needs caller-supplied sorted bag offsets");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto* hdr = static_cast<BagHeader*>(workspace);
   int* offsets = reinterpret_cast<int*>(static_cast<char*>(workspace) + kHeaderBytes);
@@ -229,8 +234,60 @@ int annc_embed_bags_sharded_dev(const annc_bag_table* tables, int num_tables, in
     const int nt = std::min(kMaxTables, num_tables - t0);
     if (t0 > 0) ANNC_CUDA(cudaMemsetAsync(hdr->unsorted, 0, sizeof(hdr->unsorted), s));
     ANNC_TRY(run_bags(tables + t0, nt, dim, id_kind, ncols, col, combiner, batch, out_stride, hdr,
-                      offsets + (size_t)t0 * (size_t)(batch + 1), s, shard_count, shard_rank));
+                      offsets + (size_t)t0 * (size_t)(batch + 1), s, shard_count, shard_rank,
+                      skip_empty));
   }
+  return ANNC_OK;
+}
+
+int annc_embed_bags_sharded_dev(const annc_bag_table* tables, int num_tables, int64_t dim,
+                                int id_kind, int64_t ncols, int32_t col, int combiner,
+                                int64_t batch, int64_t out_stride, int shard_count,
+                                int shard_rank, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  return bags_sharded(tables, num_tables, dim, id_kind, ncols, col, combiner, batch, out_stride,
+                      shard_count, shard_rank, 0, workspace, workspace_bytes, stream);
+}
+
+int annc_embed_bags_exchange_dev(const annc_bag_table* tables, int num_tables, int64_t dim,
+                                 int id_kind, int combiner, int64_t batch, int64_t out_stride,
+                                 int shard_count, int shard_rank, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  return bags_sharded(tables, num_tables, dim, id_kind, 1, 0, combiner, batch, out_stride,
+                      shard_count, shard_rank, 1, workspace, workspace_bytes, stream);
+}
+
+int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables, int num_tables, int id_kind,
+                                  int64_t batch, int shard_count, uint32_t* mask, void* stream) {
+  ANNC_REQUIRE(tables && num_tables >= 1 && mask, ANNC_ERR_INVALID_ARGUMENT, "null argument");
+  ANNC_REQUIRE(id_kind >= 0 && id_kind <= 2, ANNC_ERR_INVALID_ARGUMENT, "id_kind must be 0, 1 or 2");
+  ANNC_REQUIRE(shard_count >= 1 && shard_count <= 32, ANNC_ERR_INVALID_ARGUMENT, "bad shard_count");
+  if (batch <= 0) return ANNC_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
+    const int nt = std::min(kMaxTables, num_tables - t0);
+    BagParams p;
+    memset(&p, 0, sizeof(p));
+    p.num_tables = nt;
+    p.id_kind = id_kind;
+    p.batch = batch;
+    p.shard_count = shard_count;
+    for (int t = 0; t < nt; ++t) {
+      const annc_bag_table& T = tables[t0 + t];
+      ANNC_REQUIRE(T.offsets && (T.ids || T.nnz == 0), ANNC_ERR_INVALID_ARGUMENT,
+                   "owner mask needs ids and bag offsets");
+      if (id_kind == 2 && T.num_buckets < 1)
+        return fail(ANNC_ERR_INVALID_ARGUMENT, "num_buckets must be >= 1");
+      p.t[t].ids = T.ids;
+      p.t[t].num_buckets = (unsigned long long)T.num_buckets;
+      p.t[t].nnz = T.nnz;
+      p.t[t].given_off = T.offsets;
+    }
+    const long long groups = (long long)nt * batch;
+    bag_owner_mask_kernel<<<(unsigned)((groups + 15) / 16), 256, 0, s>>>(
+        p, mask + (size_t)t0 * (size_t)batch);
+  }
+  ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }
 

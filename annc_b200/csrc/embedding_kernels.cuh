@@ -48,6 +48,7 @@ struct BagParams {
   long long out_stride;
   int shard_count;  // row sharding: this rank owns rows r with r % shard_count == shard_rank,
   int shard_rank;   // stored at local row r / shard_count (the reference's mod-partition rule)
+  int skip_empty;   // row sharding: bags without a lookup owned by this rank are not written
 };
 
 // ---- prepass: CSR offsets from the (sorted) segment column --------------------
@@ -138,12 +139,31 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) {
   a.w = __fadd_rn(a.w, b.w);
 }
 
+// Position of the k-th (0-based) set bit of m; k must be below popc(m).
+__device__ __forceinline__ int kth_set_bit(unsigned m, int k) {
+  int pos = 0;
+  int c = __popc(m & 0xffffu);
+  if (k >= c) { k -= c; pos += 16; m >>= 16; }
+  c = __popc(m & 0xffu);
+  if (k >= c) { k -= c; pos += 8; m >>= 8; }
+  c = __popc(m & 0xfu);
+  if (k >= c) { k -= c; pos += 4; m >>= 4; }
+  c = __popc(m & 0x3u);
+  if (k >= c) { k -= c; pos += 2; m >>= 2; }
+  if (k >= (int)(m & 1u)) pos += 1;
+  return pos;
+}
+
 // ---- bag kernel: LANES lanes own one bag; each lane owns VPL float4 columns -----
 // Rows are added in lookup order into a zero accumulator, the order of the
 // reference's scalar loop, so sums are bit-identical for sorted input.  Four
 // row loads are in flight per group.  For an unsorted table the group writes the
 // zero row and clears the bag's counter; the scatter kernels then do the work.
-template <int LANES, int VPL>
+// SHARDED (row sharding): the lookups this rank owns are first compacted inside the group
+// (lookup order kept), so that the four loads in flight are all real ones, and with
+// skip_empty a bag without an owned lookup is left unwritten (its owner knows from the
+// bag's ids which ranks contribute, see bag_owner_mask_kernel).
+template <int LANES, int VPL, bool SHARDED>
 __global__ void __launch_bounds__(256, VPL == 1 ? 5 : 3)
 bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   constexpr int GROUPS_PER_WARP = 32 / LANES;
@@ -177,15 +197,28 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 
   const int start = roff[s], end = roff[s + 1];
+  int owned = 0;  // SHARDED: lookups of this bag that belong to this rank (group-uniform)
   for (int base = start; base < end; base += LANES) {
     int my = -1;  // local row (tables have fewer than 2^31 rows), -1 = skip
+    bool mine = false;
     if (base + lane < end) {
       const long long r64 = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets),
                                       p.shard_count, p.shard_rank);
+      mine = r64 != kNotMine;
       if (r64 != kNotMine && (r64 < 0 || r64 >= T.rows)) atomicOr(&hdr->err_bits, kErrRow);
       else if (r64 != kNotMine) my = (int)r64;
     }
-    const int n = min(LANES, end - base);
+    int n = min(LANES, end - base);
+    if (SHARDED) {
+      const int shift = (lane_in_warp / LANES) * LANES;
+      owned += __popc(__ballot_sync(gmask, mine) >> shift & (LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u)));
+      const unsigned bal = (__ballot_sync(gmask, my >= 0) >> shift) &
+                           (LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u));
+      n = __popc(bal);
+      const int src = lane < n ? kth_set_bit(bal, lane) : lane;
+      const int comp = __shfl_sync(gmask, my, src, LANES);
+      my = lane < n ? comp : -1;
+    }
     for (int j = 0; j < n; j += 4) {
       int r[4];
       float4 v[4][VPL];
@@ -211,6 +244,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
       }
     }
   }
+  if (SHARDED && p.skip_empty && owned == 0) return;
   if (p.combiner == 1 && end > start) {
     const float inv = __fdiv_rn(1.0f, (float)(end - start));
 #pragma unroll
@@ -224,6 +258,31 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
 #pragma unroll
   for (int w = 0; w < VPL; ++w)
     *reinterpret_cast<float4*>(orow + (w * LANES + lane) * 4) = acc[w];
+}
+
+// Which ranks contribute to each bag under row sharding: mask[t][s] has bit g set when bag s
+// of table t has at least one lookup whose row r satisfies r % shard_count == g (in or out
+// of range: the rule the senders use to decide whether they write the bag).  Half a warp per
+// bag; `off` are the bag offsets of the table (given_off).
+__global__ void __launch_bounds__(256)
+bag_owner_mask_kernel(BagParams p, unsigned* mask) {
+  const int lane = threadIdx.x & 15;
+  const unsigned gmask = 0xffffu << (threadIdx.x & 16);
+  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const long long total = (long long)p.num_tables * p.batch;
+  if (group >= total) return;
+  const int t = (int)(group / p.batch);
+  const long long s = group - (long long)t * p.batch;
+  const BagTableDev& T = p.t[t];
+  const int start = T.given_off[s], end = T.given_off[s + 1];
+  unsigned m = 0;
+  for (int i = start + lane; i < end; i += 16) {
+    const long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
+    if (r >= 0) m |= 1u << (int)(r % p.shard_count);  // a negative row is nobody's
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) m |= __shfl_xor_sync(gmask, m, o, 16);
+  if (lane == 0) mask[group] = m;
 }
 
 // Any dim (not a multiple of 4, or unaligned tables): one warp per bag, lanes
@@ -248,6 +307,13 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   const int* roff = T.given_off ? T.given_off : off;
   const int start = roff[s], end = roff[s + 1];
   const float inv = (p.combiner == 1 && end > start) ? __fdiv_rn(1.0f, (float)(end - start)) : 1.0f;
+  if (p.shard_count > 1 && p.skip_empty) {
+    bool any = false;
+    for (int i = start + lane; i < end; i += 32)
+      any = any || shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+                             p.shard_rank) != kNotMine;
+    if (!__any_sync(0xffffffffu, any)) return;
+  }
   for (long long c0 = 0; c0 < p.dim; c0 += 32) {
     const long long c = c0 + lane;
     float acc = 0.f;

@@ -251,6 +251,42 @@ sum_partials_kernel(const float* __restrict__ src, int parts, long long part_str
   }
 }
 
+// Same sum restricted to the parts named by mask[slot][row] (bit p = part p holds this row's
+// slot); parts whose bit is clear were never written and are not read.
+__global__ void __launch_bounds__(256)
+sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __restrict__ mask,
+                           int parts, long long part_stride, long long rows, int slots,
+                           int slot_w4, float* __restrict__ out, long long out_stride) {
+  const long long width4 = (long long)slots * slot_w4;
+  const long long total = rows * width4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long r = e / width4;
+    const int c4 = (int)(e - r * width4);
+    const int slot = c4 / slot_w4;
+    unsigned m = __ldg(mask + (long long)slot * rows + r);
+    const float* s0 = src + (r * width4 + c4) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool first = true;
+    while (m) {
+      const int p = __ffs(m) - 1;
+      m &= m - 1;
+      if (p >= parts) break;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(s0 + p * part_stride));
+      if (first) {
+        acc = v;
+        first = false;
+      } else {
+        acc.x = __fadd_rn(acc.x, v.x);
+        acc.y = __fadd_rn(acc.y, v.y);
+        acc.z = __fadd_rn(acc.z, v.z);
+        acc.w = __fadd_rn(acc.w, v.w);
+      }
+    }
+    *reinterpret_cast<float4*>(out + r * out_stride + (long long)c4 * 4) = acc;
+  }
+}
+
 }  // namespace
 }  // namespace annc
 
@@ -342,6 +378,24 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
   if (g > 148 * 16) g = 148 * 16;
   sum_partials_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       src, parts, part_stride, rows, width / 4, src_stride, out, out_stride);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
+                                 int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
+                                 float* out, int64_t out_stride, void* stream) {
+  ANNC_REQUIRE(src && out && mask && parts >= 1 && parts <= 32 && slots >= 1,
+               ANNC_ERR_INVALID_ARGUMENT, "null or bad argument");
+  ANNC_REQUIRE((slot_width & 3) == 0 && slot_width > 0 && (out_stride & 3) == 0 &&
+                   (part_stride & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+               ANNC_ERR_INVALID_ARGUMENT, "sum_partials needs 16-byte aligned rows");
+  if (rows <= 0) return ANNC_OK;
+  long long g = (rows * slots * (slot_width / 4) + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  sum_partials_masked_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), out, out_stride);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

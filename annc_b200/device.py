@@ -145,7 +145,8 @@ class BagLaunch:
 
     def __init__(self, entries, dim: int, batch: int, ncols: int, out_stride: int,
                  device: torch.device, id_kind: int = 2, col: int = 0, combiner: int = 0,
-                 shard_count: int = 1, shard_rank: int = 0):
+                 shard_count: int = 1, shard_rank: int = 0, exchange: bool = False):
+        self.exchange = exchange  # annc_embed_bags_exchange_dev: bags without an owned lookup are not written
         self.n = len(entries)
         self.dim, self.batch, self.ncols, self.out_stride = dim, batch, ncols, out_stride
         self.id_kind, self.col, self.combiner = id_kind, col, combiner
@@ -161,6 +162,13 @@ class BagLaunch:
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
 
     def run(self) -> None:
+        if self.exchange:
+            check(lib.annc_embed_bags_exchange_dev(
+                self.desc, C.c_int(self.n), C.c_int64(self.dim), C.c_int(self.id_kind),
+                C.c_int(self.combiner), C.c_int64(self.batch), C.c_int64(self.out_stride),
+                C.c_int(self.shard_count), C.c_int(self.shard_rank),
+                C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws_bytes), _stream()))
+            return
         check(lib.annc_embed_bags_sharded_dev(
             self.desc, C.c_int(self.n), C.c_int64(self.dim), C.c_int(self.id_kind),
             C.c_int64(self.ncols), C.c_int32(self.col), C.c_int(self.combiner),
@@ -186,6 +194,32 @@ def sum_partials_ptr(src_ptr: int, parts: int, part_stride: int, rows: int, widt
     check(lib.annc_sum_partials_dev(C.c_void_p(src_ptr), C.c_int(parts), C.c_int64(part_stride),
                                     C.c_int64(rows), C.c_int64(width), C.c_int64(src_stride),
                                     C.c_void_p(out_ptr), C.c_int64(out_stride), _stream()))
+
+
+class OwnerMask:
+    """annc_embed_bag_owner_mask_dev over fixed id / offset buffers: which ranks hold a part
+    of each bag of this rank's batch.  entries: (ids_ptr, nnz, num_buckets, offsets_ptr)."""
+
+    def __init__(self, entries, batch: int, shard_count: int, device: torch.device, id_kind: int = 2):
+        self.n, self.batch, self.shard_count, self.id_kind = len(entries), batch, shard_count, id_kind
+        self.desc = (BagTable * self.n)()
+        for i, (ip, nnz, nb, op) in enumerate(entries):
+            d = self.desc[i]
+            d.ids, d.nnz, d.num_buckets, d.offsets = ip, int(nnz), int(nb), op
+        self.mask = torch.zeros(self.n * batch, dtype=torch.int32, device=device)
+
+    def run(self) -> None:
+        check(lib.annc_embed_bag_owner_mask_dev(self.desc, C.c_int(self.n), C.c_int(self.id_kind),
+                                                C.c_int64(self.batch), C.c_int(self.shard_count),
+                                                C.c_void_p(self.mask.data_ptr()), _stream()))
+
+
+def sum_partials_masked(src_ptr: int, mask: torch.Tensor, parts: int, part_stride: int, rows: int,
+                        slots: int, slot_width: int, out_ptr: int, out_stride: int) -> None:
+    check(lib.annc_sum_partials_masked_dev(C.c_void_p(src_ptr), C.c_void_p(mask.data_ptr()),
+                                           C.c_int(parts), C.c_int64(part_stride), C.c_int64(rows),
+                                           C.c_int(slots), C.c_int64(slot_width), C.c_void_p(out_ptr),
+                                           C.c_int64(out_stride), _stream()))
 
 
 class PeerBuffers:

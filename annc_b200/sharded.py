@@ -146,7 +146,15 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                                             int(plan.nnz[s, t]), out_of(buf, s) + t * D * 4,
                                             self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
                     self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device,
-                                                       shard_count=world, shard_rank=rank))
+                                                       shard_count=world, shard_rank=rank,
+                                                       exchange=(mode == "row")))
+                if mode == "row":
+                    # which ranks write a part for each bag of this rank's own batch
+                    for st in self.sets:
+                        st["owners"] = dev.OwnerMask(
+                            [(st["ids"][t].data_ptr(), self.nnz[t], plan.table_rows[t],
+                              self.off_ws.data_ptr() + 512 + t * (B + 1) * 4) for t in range(T)],
+                            B, world, self.device)
                 self.launch = self.launches[0]
                 self._row_step = 0
                 self.embed_launches = 2 * ((len(entries) + 55) // 56) + 2
@@ -201,9 +209,9 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                     self.launch = self.launches[buf]
                     self.launch.run()           # partial sums land in their owners' memory
                     dist.all_reduce(self.flag)  # every rank's bag kernel has finished
-                    dev.sum_partials_ptr(self.peer.local + buf * world * B * T * D * 4, world,
-                                         B * T * D, B, T * D, T * D,
-                                         self.z.data_ptr() + D * 4, F * D)
+                    dev.sum_partials_masked(self.peer.local + buf * world * B * T * D * 4,
+                                            self._owners.mask, world, B * T * D, B, T, D,
+                                            self.z.data_ptr() + D * 4, F * D)
                     return
                 self.launch.run()
                 dist.all_to_all_single(self.recv, self.partial)
@@ -237,6 +245,9 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             n = self.nnz_total
             self.ids_pad[:n].copy_(self.ids_all)
             self.sets[self.cur]["prepass"].run(self.off_ws)
+            if mode == "row":
+                self._owners = self.sets[self.cur]["owners"]
+                self._owners.run()
             self._works = [dist.all_gather_into_tensor(self.ids_g, self.ids_pad, async_op=True),
                            dist.all_gather_into_tensor(self.off_g, self.off_ws, async_op=True)]
 

@@ -251,6 +251,29 @@ int annc_embed_bags_sharded_dev(const annc_bag_table* tables /* host array */, i
                                 int64_t batch, int64_t out_stride, int shard_count,
                                 int shard_rank, void* workspace, size_t workspace_bytes,
                                 void* stream);
+/* Fused pooling + exchange step of a row-sharded table: annc_embed_bags_sharded_dev with
+ * caller-supplied bag offsets (every table's `offsets` set, slice_input unused) that leaves
+ * a bag unwritten when this rank owns none of its lookups.  Each table's `out` normally
+ * points into the receive buffer of the rank that owns the samples (annc_peer_buffer_open),
+ * so the partial sums cross NVLink as the kernel's own stores and nothing is sent for bags
+ * this rank does not contribute to.  The owner learns which parts exist from its own ids
+ * (annc_embed_bag_owner_mask_dev) and adds them with annc_sum_partials_masked_dev. */
+int annc_embed_bags_exchange_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                                 int64_t dim, int id_kind, int combiner, int64_t batch,
+                                 int64_t out_stride, int shard_count, int shard_rank,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+/* mask[t * batch + s], bit g set when bag s of table t (ids, offsets, num_buckets of
+ * tables[t]) has a lookup whose row r has r % shard_count == g: the ranks that write a part
+ * for this bag in annc_embed_bags_exchange_dev.  shard_count <= 32. */
+int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                                  int id_kind, int64_t batch, int shard_count, uint32_t* mask,
+                                  void* stream);
+/* out[r, slot, :] = sum, in ascending p, of the parts p whose bit is set in
+ * mask[slot * rows + r]; part p holds f32[rows, slots, slot_width] at src + p * part_stride
+ * floats; zero when no bit is set.  Parts whose bit is clear are not read. */
+int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
+                                 int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
+                                 float* out, int64_t out_stride, void* stream);
 /* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
  * reduce step after the all-to-all of partial sums).  src part p starts at
  * src + p * part_stride floats, rows are src_stride / out_stride floats apart. */

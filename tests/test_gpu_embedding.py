@@ -277,3 +277,58 @@ def test_hash_bags_full_size_properties():
         t.mul_(2.0)
     plan.run()
     assert torch.equal(out, base * 2.0)
+
+
+@pytest.mark.parametrize("shards,combiner", [(2, 0), (3, 1), (8, 0)])
+def test_row_sharded_exchange_on_one_gpu(shards, combiner):
+    """The fused pooling + exchange step with its ranks run one after the other on one GPU:
+    each rank pools the lookups it owns (mod partition) into its part of a receive buffer and
+    leaves bags it does not contribute to unwritten (the buffer is poisoned with NaN first);
+    the owner mask, computed from the ids alone, must name exactly the written parts, and the
+    masked rank-order sum must match the unsharded oracle within the fp32 pooling tolerance."""
+    from annc_b200.device import BagLaunch, BagPrepass, OwnerMask, sum_partials_masked
+    rows = [1000, 37, 50_000, 5, 3]
+    B, D = 1024, 64
+    T = len(rows)
+    w = synth.embedding_workload(11, rows, D, B, 12, 1.05)
+    dev = torch.device("cuda")
+    ids = [_dev(b.raw_ids) for b in w.bags]
+    segs = [_dev(b.slice_input) for b in w.bags]
+    pre = BagPrepass(segs, B)
+    ws = torch.zeros(pre.ws_bytes, dtype=torch.uint8, device=dev)
+    pre.run(ws)
+    off_ptr = lambda t: ws.data_ptr() + 512 + t * (B + 1) * 4
+    recv = torch.full((shards, B, T, D), float("nan"), device=dev)
+    keep = []
+    for g in range(shards):
+        shard_tabs = [_dev(np.ascontiguousarray(t[g::shards]) if t[g::shards].shape[0] else
+                           np.zeros((1, D), np.float32)) for t in w.tables]
+        keep.append(shard_tabs)
+        entries = [(shard_tabs[t].data_ptr(), len(range(g, rows[t], shards)), rows[t],
+                    ids[t].data_ptr(), None, ids[t].shape[0],
+                    recv.data_ptr() + ((g * B) * T + t) * D * 4, off_ptr(t)) for t in range(T)]
+        launch = BagLaunch(entries, D, B, 2, T * D, dev, combiner=combiner, shard_count=shards,
+                           shard_rank=g, exchange=True)
+        launch.run()
+        assert launch.error_bits() == 0
+    owners = OwnerMask([(ids[t].data_ptr(), ids[t].shape[0], rows[t], off_ptr(t)) for t in range(T)],
+                       B, shards, dev)
+    owners.run()
+    mask = owners.mask.cpu().numpy().reshape(T, B)
+    written = ~torch.isnan(recv[:, :, :, 0]).cpu().numpy()  # [shards, B, T]
+    for t, bag in enumerate(w.bags):
+        bucket = bag.raw_ids.view(np.uint64) % np.uint64(rows[t])
+        want_mask = np.zeros(B, np.int64)
+        np.bitwise_or.at(want_mask, bag.slice_input[:, 0], 1 << (bucket % np.uint64(shards)).astype(np.int64))
+        np.testing.assert_array_equal(mask[t], want_mask)
+        for g in range(shards):
+            np.testing.assert_array_equal(written[g, :, t], (want_mask >> g) & 1 == 1)
+    out = torch.full((B, T, D), 3.0, device=dev)
+    sum_partials_masked(recv.data_ptr(), owners.mask, shards, B * T * D, B, T, D, out.data_ptr(), T * D)
+    got = out.cpu().numpy()
+    for t, (tab, bag) in enumerate(zip(w.tables, w.bags)):
+        idx = oracle.hash_bucket(bag.raw_ids.view(np.uint64), rows[t])
+        want, _ = oracle.sparse_segment_reduce(tab, idx, bag.slice_input, np.array([0, 0], np.int32),
+                                               np.array([0], np.int32), combiner)
+        scale = max(float(np.abs(want).max()), 1e-30)
+        assert float(np.abs(got[:, t, :] - want).max()) / scale <= 1e-5
