@@ -61,9 +61,10 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
     p.t[t].ids = tables[t].ids;
     p.t[t].seg = tables[t].slice_input;
     p.t[t].out = tables[t].out;
-    p.t[t].rows = tables[t].rows;
+    p.t[t].rows = (int)tables[t].rows;
     p.t[t].num_buckets = (unsigned long long)tables[t].num_buckets;
-    p.t[t].nnz = tables[t].nnz;
+    p.t[t].magic = id_kind == 2 ? mod_magic(p.t[t].num_buckets) : 0;
+    p.t[t].nnz = (int)tables[t].nnz;
     p.t[t].given_off = tables[t].offsets;
     max_nnz = std::max<long long>(max_nnz, tables[t].nnz);
     vec_ok = vec_ok && aligned16(tables[t].table) && aligned16(tables[t].out);
@@ -279,8 +280,11 @@ int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables, int num_tables, 
       if (id_kind == 2 && T.num_buckets < 1)
         return fail(ANNC_ERR_INVALID_ARGUMENT, "num_buckets must be >= 1");
       p.t[t].ids = T.ids;
+      ANNC_REQUIRE(T.nnz < (int64_t(1) << 31) - 1, ANNC_ERR_UNSUPPORTED,
+                   "more than 2^31-2 lookups in one table");
       p.t[t].num_buckets = (unsigned long long)T.num_buckets;
-      p.t[t].nnz = T.nnz;
+      p.t[t].magic = id_kind == 2 ? mod_magic(p.t[t].num_buckets) : 0;
+      p.t[t].nnz = (int)T.nnz;
       p.t[t].given_off = T.offsets;
     }
     const long long groups = (long long)nt * batch;

@@ -30,11 +30,13 @@ struct BagTableDev {
   const void* ids;
   const int64_t* seg;  // slice_input
   float* out;
-  long long rows;
   unsigned long long num_buckets;
-  long long nnz;
-  const int* given_off;  // caller-supplied bag offsets [batch + 1] (then `seg` is not read)
+  unsigned long long magic;  // floor((2^64 - 1) / num_buckets): reciprocal for the exact modulo
+  const int* given_off;      // caller-supplied bag offsets [batch + 1] (then `seg` is not read)
+  int rows;                  // (local) table rows and lookups: both below 2^31
+  int nnz;
 };
+static_assert(sizeof(BagTableDev) == 64, "BagParams must stay under the 4 KB parameter space");
 
 struct BagParams {
   BagTableDev t[kMaxTables];
@@ -114,19 +116,45 @@ bag_prepass2_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 }
 
-__device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, long long i,
-                                                 unsigned long long num_buckets) {
-  if (id_kind == 0) return (long long)((const int*)ids)[i];
-  if (id_kind == 1) return ((const long long*)ids)[i];
-  return (long long)(((const unsigned long long*)ids)[i] % num_buckets);
+// x % d in uint64 without a division: with magic = floor((2^64 - 1) / d) the estimate
+// q = hi64(x * magic) is floor(x / d) or one less, for every x and every d >= 1, so the
+// remainder needs at most one correction (a second one is kept as a guard).  Bit-exact with
+// the `hash % num_buckets` of fused_embedding_with_hash_bucket.cc:63-64.
+__host__ __device__ __forceinline__ unsigned long long mod_magic(unsigned long long d) {
+  return ~0ull / d;
+}
+__device__ __forceinline__ unsigned long long fast_mod_u64(unsigned long long x, unsigned long long d,
+                                                           unsigned long long magic) {
+  unsigned long long r = x - __umul64hi(x, magic) * d;
+  if (r >= d) r -= d;
+  if (r >= d) r -= d;
+  return r;
 }
 
-// Row sharding.  Returns the local row, or -2 when another rank owns the row.
+__device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, long long i,
+                                                 unsigned long long num_buckets,
+                                                 unsigned long long magic) {
+  if (id_kind == 0) return (long long)((const int*)ids)[i];
+  if (id_kind == 1) return ((const long long*)ids)[i];
+  return (long long)fast_mod_u64(((const unsigned long long*)ids)[i], num_buckets, magic);
+}
+
+// Row sharding.  Returns the local row, or -2 when another rank owns the row.  Rows below
+// 2^32 (every real table) take 32-bit arithmetic.
 constexpr long long kNotMine = -2;
 __device__ __forceinline__ long long shard_row(long long r, int shard_count, int shard_rank) {
   if (shard_count <= 1 || r < 0) return r;
+  if ((unsigned long long)r <= 0xffffffffull) {
+    const unsigned b = (unsigned)r, q = b / (unsigned)shard_count;
+    return (b - q * (unsigned)shard_count == (unsigned)shard_rank) ? (long long)q : kNotMine;
+  }
   if ((int)(r % shard_count) != shard_rank) return kNotMine;
   return r / shard_count;
+}
+// Owner rank of row r >= 0 under the same rule.
+__device__ __forceinline__ int shard_owner(long long r, int shard_count) {
+  if ((unsigned long long)r <= 0xffffffffull) return (int)((unsigned)r % (unsigned)shard_count);
+  return (int)(r % shard_count);
 }
 
 __device__ __forceinline__ float4 ldg4(const float* p) {
@@ -202,7 +230,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
     int my = -1;  // local row (tables have fewer than 2^31 rows), -1 = skip
     bool mine = false;
     if (base + lane < end) {
-      const long long r64 = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets),
+      const long long r64 = shard_row(load_row_id(T.ids, p.id_kind, base + lane, T.num_buckets, T.magic),
                                       p.shard_count, p.shard_rank);
       mine = r64 != kNotMine;
       if (r64 != kNotMine && (r64 < 0 || r64 >= T.rows)) atomicOr(&hdr->err_bits, kErrRow);
@@ -277,8 +305,8 @@ bag_owner_mask_kernel(BagParams p, unsigned* mask) {
   const int start = T.given_off[s], end = T.given_off[s + 1];
   unsigned m = 0;
   for (int i = start + lane; i < end; i += 16) {
-    const long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets);
-    if (r >= 0) m |= 1u << (int)(r % p.shard_count);  // a negative row is nobody's
+    const long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic);
+    if (r >= 0) m |= 1u << shard_owner(r, p.shard_count);  // a negative row is nobody's
   }
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) m |= __shfl_xor_sync(gmask, m, o, 16);
@@ -310,7 +338,7 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   if (p.shard_count > 1 && p.skip_empty) {
     bool any = false;
     for (int i = start + lane; i < end; i += 32)
-      any = any || shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+      any = any || shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic), p.shard_count,
                              p.shard_rank) != kNotMine;
     if (!__any_sync(0xffffffffu, any)) return;
   }
@@ -318,7 +346,7 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
     const long long c = c0 + lane;
     float acc = 0.f;
     for (int i = start; i < end; ++i) {
-      long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+      long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic), p.shard_count,
                               p.shard_rank);
       if (r == kNotMine) continue;
       if (r < 0 || r >= T.rows) {
@@ -343,7 +371,7 @@ bag_scatter_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < T.nnz;
        i += warps) {
     long long seg = T.seg[i * p.ncols + p.col];
-    long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets), p.shard_count,
+    long long r = shard_row(load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic), p.shard_count,
                             p.shard_rank);
     if (seg < 0 || seg >= p.batch) continue;  // flagged by the prepass
     if (lane == 0) atomicAdd(&counts[seg], 1);  // bag length counts every rank's lookups

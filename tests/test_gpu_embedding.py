@@ -332,3 +332,27 @@ def test_row_sharded_exchange_on_one_gpu(shards, combiner):
                                                np.array([0], np.int32), combiner)
         scale = max(float(np.abs(want).max()), 1e-30)
         assert float(np.abs(got[:, t, :] - want).max()) / scale <= 1e-5
+
+
+@pytest.mark.parametrize("num_buckets", [1, 2, 3, 7, 10**6, 2**31 - 1, 2**32 + 1, 2**62 + 3, 2**63 - 1])
+def test_division_free_modulo_is_exact(num_buckets):
+    """The kernels compute `fingerprint % num_buckets` with a reciprocal multiply and a
+    correction step.  The owner-mask kernel exposes (id % num_buckets) % G without needing a
+    table of num_buckets rows; three coprime G pin the bucket on edge and random ids."""
+    from annc_b200.device import OwnerMask
+    rng = np.random.default_rng(3)
+    d = num_buckets
+    edge = [0, 1, d - 1, d, d + 1, 2 * d - 1, 2 * d, 2**62 - 1, 2**63 - 1, 2**63, 2**64 - 1,
+            2**64 - d, (2**64 - 1) // d * d, (2**64 - 1) // d * d - 1]
+    ids = np.array([e % 2**64 for e in edge if e >= 0], dtype=np.uint64)
+    ids = np.concatenate([ids, rng.integers(0, 2**64, 4096, dtype=np.uint64)])
+    n = ids.shape[0]
+    ids_d = _dev(ids.view(np.int64))
+    off = _dev(np.arange(n + 1, dtype=np.int32))  # one lookup per bag
+    want_bucket = np.array([int(x) % d for x in ids.tolist()], dtype=object)
+    for g in (32, 31, 29):
+        m = OwnerMask([(ids_d.data_ptr(), n, d, off.data_ptr())], n, g, torch.device("cuda"))
+        m.run()
+        got = m.mask.cpu().numpy().view(np.uint32)
+        want = np.array([1 << (int(b) % g) for b in want_bucket], dtype=np.uint32)
+        np.testing.assert_array_equal(got, want)
