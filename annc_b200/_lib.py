@@ -13,6 +13,7 @@ ANNC_F32, ANNC_I32, ANNC_I64, ANNC_BOOL, ANNC_U64 = 1, 3, 9, 10, 23
 ACT_NONE, ACT_RELU, ACT_SIGMOID = 0, 1, 2
 B_PLAIN, B_KN4 = 0, 1
 MATH_AUTO, MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2, 3
+IO_A_BF16, IO_B_BF16, IO_C_BF16, IO_SOFTMAX = 1, 2, 4, 8
 
 
 class AnncError(RuntimeError):
@@ -43,7 +44,7 @@ class GemmDesc(C.Structure):
                 ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
                 ("addend", C.c_void_p), ("bias", C.c_void_p),
                 ("activation", C.c_int32), ("b_format", C.c_int32), ("math", C.c_int32),
-                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("io_flags", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_int64))

@@ -1,4 +1,7 @@
 // GEMM dispatcher, the kn4 converters and the KPFusedBatchMatMulAddSigmoid twin.
+#include <cuda_bf16.h>
+
+#include <cstdlib>
 #include <cstring>
 
 #include "common.h"
@@ -23,17 +26,42 @@ static int validate(const annc_gemm_desc& d) {
   return ANNC_OK;
 }
 
-// AUTO: tensor cores (TF32) when the shape fits the tcgen05 kernel, else CUDA cores.
+// ANNC_GEMM_ROUTE=single|pair forces one tensor-core kernel where both fit (for A/B timing).
+static int forced_route() {
+  static const int v = []() {
+    const char* e = getenv("ANNC_GEMM_ROUTE");
+    if (!e) return 0;
+    if (!strcmp(e, "single")) return 1;
+    if (!strcmp(e, "pair")) return 2;
+    return 0;
+  }();
+  return v;
+}
+
+// The CTA-pair kernel works on 256 x 256 tiles: it takes the GEMMs that fill them.
+static bool use_pair(const annc_gemm_desc& d, int math) {
+  if (!pair_supported(d, math)) return false;
+  if (math == ANNC_MATH_BF16 || (d.io_flags & ANNC_IO_SOFTMAX)) return true;
+  if (!tc_supported(d, math)) return true;
+  const int f = forced_route();
+  if (f) return f == 2;
+  return d.m >= 256 && d.n >= 192;
+}
+
+// AUTO: tensor cores (TF32) when the shape fits a tcgen05 kernel, else CUDA cores.
 static int pick_math(const annc_gemm_desc& d) {
   if (d.math == ANNC_MATH_FP32) return ANNC_MATH_FP32;
   const int want = d.math == ANNC_MATH_AUTO ? ANNC_MATH_TF32 : d.math;
-  return tc_supported(d, want) ? want : ANNC_MATH_FP32;
+  if (d.math == ANNC_MATH_AUTO && d.io_flags == 0 && (d.m < 64 || d.n < 16 || d.k < 32))
+    return ANNC_MATH_FP32;  // tiny shapes stay on the CUDA cores
+  return (tc_supported(d, want) || pair_supported(d, want)) ? want : ANNC_MATH_FP32;
 }
 
 const char* route_name(const annc_gemm_desc& d) {
-  switch (pick_math(d)) {
-    case ANNC_MATH_TF32: return "tcgen05_tf32";
-    case ANNC_MATH_BF16: return "tcgen05_bf16";
+  const int math = pick_math(d);
+  switch (math) {
+    case ANNC_MATH_TF32: return use_pair(d, math) ? "tcgen05_pair_tf32" : "tcgen05_tf32";
+    case ANNC_MATH_BF16: return "tcgen05_pair_bf16";
     default: return "simt_fp32";
   }
 }
@@ -67,6 +95,27 @@ kn4_unpack_chunks_kernel(const float* __restrict__ src, float* __restrict__ dst,
     const float* p = src + kc.start * N + kc.len * term + (k - kc.start) * pn.width + in0;
     *reinterpret_cast<float4*>(dst + (long long)k * N + n) = __ldg(reinterpret_cast<const float4*>(p));
   }
+}
+
+__global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                 long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// [K,N] fp32 -> [N,K] bf16 through a 32 x 32 shared-memory tile.
+__global__ void __launch_bounds__(256)
+bf16_weight_kernel(const float* __restrict__ src, long long ldb, __nv_bfloat16* __restrict__ dst,
+                   long long K, long long N) {
+  __shared__ float tile[32][33];
+  const long long k0 = (long long)blockIdx.y * 32, n0 = (long long)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8)
+    tile[r][tx] = (k0 + r < K && n0 + tx < N) ? src[(k0 + r) * ldb + n0 + tx] : 0.f;
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8)
+    if (n0 + r < N && k0 + tx < K) dst[(n0 + r) * K + k0 + tx] = __float2bfloat16_rn(tile[tx][r]);
 }
 
 }  // namespace
@@ -105,15 +154,43 @@ int annc_gemm_run(const annc_gemm_desc* desc, void* stream) {
   const int math = gemm::pick_math(*desc);
   if (desc->math != ANNC_MATH_AUTO && desc->math != math)
     return fail(ANNC_ERR_UNSUPPORTED, "gemm: shape not supported by the requested math mode");
-  if (math == ANNC_MATH_FP32) return gemm::run_simt(*desc, s);
+  if (math == ANNC_MATH_FP32) {
+    if (desc->io_flags != 0)
+      return fail(ANNC_ERR_UNSUPPORTED, "gemm: io_flags need a tensor-core route this shape does not fit");
+    return gemm::run_simt(*desc, s);
+  }
   annc_gemm_desc plain;
-  if (gemm::unpack_kn4_into_workspace(*desc, s, &plain)) return gemm::run_tc(plain, math, s);
-  return gemm::run_tc(*desc, math, s);
+  if (gemm::unpack_kn4_into_workspace(*desc, s, &plain))
+    return gemm::use_pair(plain, math) ? gemm::run_pair(plain, math, s) : gemm::run_tc(plain, math, s);
+  return gemm::use_pair(*desc, math) ? gemm::run_pair(*desc, math, s) : gemm::run_tc(*desc, math, s);
 }
 
 const char* annc_gemm_kernel_name(const annc_gemm_desc* desc) {
   if (!desc) return "";
   return gemm::route_name(*desc);
+}
+
+int annc_cast_bf16_dev(const float* src, void* dst_bf16, int64_t n, void* stream) {
+  ANNC_REQUIRE(src && dst_bf16 && n >= 0, ANNC_ERR_INVALID_ARGUMENT, "cast: bad arguments");
+  if (n == 0) return ANNC_OK;
+  long long g = (n + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  gemm::cast_bf16_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, static_cast<__nv_bfloat16*>(dst_bf16), n);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_bf16_weight_dev(const float* b_kn, int64_t ldb, void* b_nk_bf16, int64_t k, int64_t n,
+                         void* stream) {
+  ANNC_REQUIRE(b_kn && b_nk_bf16 && k >= 1 && n >= 1 && ldb >= n, ANNC_ERR_INVALID_ARGUMENT,
+               "bf16 weight: bad arguments");
+  dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k + 31) / 32));
+  ANNC_REQUIRE(grid.y <= 65535, ANNC_ERR_UNSUPPORTED, "bf16 weight: k too large");
+  gemm::bf16_weight_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      b_kn, ldb, static_cast<__nv_bfloat16*>(b_nk_bf16), k, n);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
 }
 
 int annc_kn4_pack_dev(const float* b_kn, float* b_packed, int64_t k, int64_t n, void* stream) {

@@ -21,6 +21,10 @@ int run_simt(const annc_gemm_desc& d, cudaStream_t s, const BiasBroadcast* bb = 
 bool tc_supported(const annc_gemm_desc& d, int math);
 int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s);
 
+// Persistent CTA-pair tcgen05 kernel (TF32 with fp32 operands, BF16 with bf16 operands).
+bool pair_supported(const annc_gemm_desc& d, int math);
+int run_pair(const annc_gemm_desc& d, int math, cudaStream_t s);
+
 // Picks the route the way annc_gemm_run does; returns a static name.
 const char* route_name(const annc_gemm_desc& d);
 

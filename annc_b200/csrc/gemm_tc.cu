@@ -375,7 +375,7 @@ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 }  // namespace
 
 bool tc_supported(const annc_gemm_desc& d, int math) {
-  if (math != ANNC_MATH_TF32) return false;
+  if (math != ANNC_MATH_TF32 || d.io_flags != 0) return false;
   if (d.trans_a || d.batch < 1 || d.batch > 65535) return false;
   if (d.batch > 1) {  // strided batch: rank-3 tensor maps need 16-byte batch pitches
     if (d.b_format != ANNC_B_PLAIN || (d.stride_a & 3) || (d.stride_b & 3) || d.stride_a <= 0 ||
@@ -444,6 +444,14 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   }
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
+}
+
+int* gemm_error_word() {
+  static int* addr = []() -> int* {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_gemm_error) == cudaSuccess ? static_cast<int*>(p) : nullptr;
+  }();
+  return addr;
 }
 
 int read_error_flag(int* flag) {

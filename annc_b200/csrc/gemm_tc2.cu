@@ -1,0 +1,484 @@
+// Persistent CTA-pair GEMM on the 5th-generation tensor cores (tcgen05, cta_group::2).
+//
+//   C[M,N] = epilogue(alpha * A[M,K] * B + beta * C + addend + bias)
+//
+// Two CTAs of a cluster own one 256 x 256 tile of C: CTA r holds rows 128 r .. 128 r + 127 of
+// the accumulator in its tensor memory and loads, per k-step, its own 128 rows of A and its
+// own 128 columns of B (32 KB per CTA per 128-byte k-step, half of what a single-CTA 128 x 128
+// tile moves per flop; the MMA of the leader CTA reads both halves of B from the two shared
+// memories).  No load is multicast.  TF32 takes fp32 operands as they lie in memory (B as [N,K]
+// or [K,N]); BF16 takes bf16 A [M,K] and B [N,K].
+//
+//   warp 0   TMA producer of this CTA's operand halves; every load counts on the leader's
+//            "full" barrier of the stage (cp.async.bulk.tensor ... cta_group::2)
+//   warp 1   allocates tensor memory for the pair; in the leader one thread issues the MMAs
+//            (UMMA 256 x 256 x {8,16}), commits to the "empty" barrier of both CTAs and, after
+//            the last k-step of a tile, to the "accumulator full" barrier of both CTAs
+//   warps 2-5  epilogue: tcgen05.ld of the CTA's 128 accumulator rows, scale / addend / bias /
+//            activation or row softmax, stores; then release the accumulator to the leader
+//
+// The kernel is persistent (one pair per two SMs, tiles taken round robin) and the accumulator
+// is double-buffered in the 512 tensor-memory columns, so the epilogue of tile i runs under
+// the main loop of tile i + 1.  Every wait is bounded (about a second): a role that gives up
+// raises the error word read by annc_gemm_check and leaves; all roles meet at the end, where
+// tensor memory is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+#include <cstring>
+
+#include "common.h"
+#include "gemm.h"
+#include "tc_host.h"
+#include "tc_ptx.cuh"
+
+namespace annc {
+namespace gemm {
+
+int* gemm_error_word();  // device address of the tcgen05 GEMM error word (gemm_tc.cu)
+
+namespace {
+
+using namespace annc::tc;
+
+constexpr int PM = 128;           // accumulator rows per CTA
+constexpr int PN = 256;           // tile columns (each CTA loads 128 of them)
+constexpr int P_A_BYTES = 16384;  // 128 rows x 128 bytes
+constexpr int P_B_BYTES = 16384;  // 128 columns x 128 bytes
+constexpr int P_STAGE = P_A_BYTES + P_B_BYTES;
+constexpr int P_STAGES = 6;
+constexpr int P_THREADS = 192;
+constexpr int P_TMEM_COLS = 512;
+constexpr size_t P_SMEM = 1024 + (size_t)P_STAGES * P_STAGE + 256;
+
+struct PairParams {
+  int M, N, K;
+  int b_n_major;  // B stored [K,N] (TF32 only)
+  void* C;
+  long long ldc;
+  const float* addend;
+  long long ld_addend;
+  const float* bias;
+  float alpha, beta;
+  int act;
+  int softmax;  // row softmax over the N <= 256 columns after the epilogue
+  int c_bf16;   // C is bf16
+  int batched, b_batched;
+  long long stride_c, stride_addend;
+  int tiles_m, tiles_n;
+  long long tiles;
+  int* error_word;
+};
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  if (act == ANNC_ACT_RELU) return fmaxf(v, 0.0f);
+  if (act == ANNC_ACT_SIGMOID) return __fdiv_rn(1.0f, 1.0f + expf(-v));
+  return v;
+}
+
+// Values of one 32-column chunk of this thread's row before the activation:
+// alpha * acc (+ beta * C) (+ addend) (+ bias).  Columns at or past N come out as -inf-safe
+// zeros; the caller masks them.
+__device__ __forceinline__ void chunk_values(const PairParams& p, const uint32_t (&r)[32], float (&v)[32],
+                                             long long grow, int col0, long long bz, bool row_ok) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+  if (!row_ok) return;
+  if (p.beta != 0.f) {
+    if (p.c_bf16) {
+      const __nv_bfloat16* c = static_cast<const __nv_bfloat16*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += p.beta * __bfloat162float(c[j]);
+    } else {
+      const float* c = static_cast<const float*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += p.beta * c[j];
+    }
+  }
+  if (p.addend) {
+    const float* a = p.addend + bz * p.stride_addend + grow * p.ld_addend + col0;
+    const bool vec = ((p.ld_addend & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0) &&
+                     ((p.stride_addend & 3) == 0) && col0 + 31 < p.N;
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(a + j));
+        v[j] += x.x; v[j + 1] += x.y; v[j + 2] += x.z; v[j + 3] += x.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += __ldg(a + j);
+    }
+  }
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+  }
+}
+
+__device__ __forceinline__ void chunk_store(const PairParams& p, const float (&v)[32], long long grow,
+                                            int col0, long long bz) {
+  if (p.c_bf16) {
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
+    const bool vec = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                     ((p.stride_c & 7) == 0) && col0 + 31 < p.N;
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        o.x = *reinterpret_cast<uint32_t*>(&t0);
+        o.y = *reinterpret_cast<uint32_t*>(&t1);
+        o.z = *reinterpret_cast<uint32_t*>(&t2);
+        o.w = *reinterpret_cast<uint32_t*>(&t3);
+        *reinterpret_cast<uint4*>(c + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) c[j] = __float2bfloat16_rn(v[j]);
+    }
+    return;
+  }
+  float* c = static_cast<float*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
+  const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                   ((p.stride_c & 3) == 0) && col0 + 31 < p.N;
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4*>(c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) c[j] = v[j];
+  }
+}
+
+// DT 0: TF32 (fp32 elements, 32 per 128-byte k-step, UMMA K = 8); DT 1: BF16 (64, K = 16).
+template <int DT>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, PairParams p) {
+  constexpr int KELTS = DT == 0 ? 32 : 64;  // elements per 128-byte k-step row
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + P_STAGES * P_STAGE;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * P_STAGES;
+  const uint32_t bar_tfull = bars + 16 * P_STAGES, bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + P_STAGES * P_STAGE + 16 * P_STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const long long pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int KT = (p.K + KELTS - 1) / KELTS;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);   // the leader's expect_tx arrival; bytes come from both CTAs
+      mbar_init(bar_empty + 8 * s, 1);  // one commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);   // one commit
+      mbar_init(bar_tempty + 8 * a, 8);  // four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), P_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool poisoned = *reinterpret_cast<volatile int*>(p.error_word) != 0;  // an earlier launch gave up
+
+  if (!poisoned) {
+    if (warp == 0) {
+      // ---------------- producer (both CTAs)
+      if (lane == 0) {
+        uint32_t kit = 0;
+        bool ok = true;
+        for (long long tile = pair; tile < p.tiles && ok; tile += pairs) {
+          const long long bz = tile / ((long long)p.tiles_m * p.tiles_n);
+          const int t2 = (int)(tile - bz * p.tiles_m * p.tiles_n);
+          const int tn = t2 / p.tiles_m, tm = t2 - tn * p.tiles_m;
+          const int m0 = tm * (2 * PM) + (int)rank * PM;
+          const int n0 = tn * PN + (int)rank * (PN / 2);
+          for (int kt = 0; kt < KT; ++kt, ++kit) {
+            const int s = kit % P_STAGES;
+            const uint32_t ph = (kit / P_STAGES) & 1u;
+            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.error_word);
+            if (!ok) break;
+            const uint32_t sa = base + s * P_STAGE, sb = sa + P_A_BYTES;
+            const uint32_t full_leader = mapa_u32(bar_full + 8 * s, 0);
+            if (leader) mbar_expect_tx(bar_full + 8 * s, 2 * P_STAGE);
+            const int k0 = kt * KELTS;
+            if (p.batched) tma_load_3d_pair(sa, &tmap_a, k0, m0, (int)bz, full_leader);
+            else tma_load_2d_pair(sa, &tmap_a, k0, m0, full_leader);
+            if (!p.b_n_major) {
+              if (p.b_batched) tma_load_3d_pair(sb, &tmap_b, k0, n0, (int)bz, full_leader);
+              else tma_load_2d_pair(sb, &tmap_b, k0, n0, full_leader);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {  // one 32-column x 32-row box per 4 KB block
+                if (p.b_batched)
+                  tma_load_3d_pair(sb + j * 4096, &tmap_b, n0 + 32 * j, k0, (int)bz, full_leader);
+                else
+                  tma_load_2d_pair(sb + j * 4096, &tmap_b, n0 + 32 * j, k0, full_leader);
+              }
+            }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------- MMA issuer (leader CTA only)
+      if (leader && lane == 0) {
+        // D fp32; A/B tf32 or bf16; A K-major; B K- or N-major; N = 256; M = 256
+        const uint32_t fmt = DT == 0 ? 2u : 1u;
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((p.b_n_major ? 1u : 0u) << 16) |
+                               ((uint32_t)(PN >> 3) << 17) | ((uint32_t)((2 * PM) >> 4) << 24);
+        uint32_t kit = 0, tcount = 0;
+        bool ok = true;
+        for (long long tile = pair; tile < p.tiles && ok; tile += pairs, ++tcount) {
+          const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+          ok = mbar_wait(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.error_word);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + acc * (uint32_t)PN;
+          for (int kt = 0; kt < KT; ++kt, ++kit) {
+            const int s = kit % P_STAGES;
+            const uint32_t ph = (kit / P_STAGES) & 1u;
+            ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.error_word);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = base + s * P_STAGE, sb = sa + P_A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {  // four UMMA k-steps of 32 bytes per stage
+              const uint64_t ad = smem_desc(sa + kk * 32, 16, 1024, 2);
+              const uint64_t bd = p.b_n_major ? smem_desc(sb + kk * 1024, 4096, 512, 1)
+                                              : smem_desc(sb + kk * 32, 16, 1024, 2);
+              if (DT == 0) umma_pair_tf32(tmem_d, ad, bd, idesc, (kt | kk) != 0 ? 1u : 0u);
+              else umma_pair_f16(tmem_d, ad, bd, idesc, (kt | kk) != 0 ? 1u : 0u);
+            }
+            umma_commit_pair(bar_empty + 8 * s);
+          }
+          if (ok) umma_commit_pair(bar_tfull + 8 * acc);
+        }
+      }
+    } else {
+      // ---------------- epilogue (both CTAs): warp q owns TMEM lanes 32 q .. 32 q + 31
+      const int q = warp & 3;
+      uint32_t tcount = 0;
+      bool ok = true;
+      for (long long tile = pair; tile < p.tiles && ok; tile += pairs, ++tcount) {
+        const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+        const long long bz = tile / ((long long)p.tiles_m * p.tiles_n);
+        const int t2 = (int)(tile - bz * p.tiles_m * p.tiles_n);
+        const int tn = t2 / p.tiles_m, tm = t2 - tn * p.tiles_m;
+        const long long grow = (long long)tm * (2 * PM) + rank * PM + q * 32 + lane;
+        const bool row_ok = grow < p.M;
+        const int nb = tn * PN;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.error_word)) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)PN;
+        if (!p.softmax) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < PN && nb + c0 < p.N; c0 += 32) {
+            uint32_t r[32];
+            float v[32];
+            tmem_ld32(taddr + (uint32_t)c0, r);
+            tmem_ld_wait();
+            chunk_values(p, r, v, grow, nb + c0, bz, row_ok);
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = act_apply(v[j], p.act);
+              chunk_store(p, v, grow, nb + c0, bz);
+            }
+          }
+        } else {
+          // three passes over the row in tensor memory: max, sum of exp, normalised store
+          float mx = -INFINITY, sum = 0.f;
+#pragma unroll 1
+          for (int pass = 0; pass < 3; ++pass) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < PN && c0 < p.N; c0 += 32) {
+              uint32_t r[32];
+              float v[32];
+              tmem_ld32(taddr + (uint32_t)c0, r);
+              tmem_ld_wait();
+              chunk_values(p, r, v, grow, c0, bz, row_ok);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = act_apply(v[j], p.act);
+              if (pass == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (c0 + j < p.N) mx = fmaxf(mx, v[j]);
+              } else if (pass == 1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (c0 + j < p.N) sum += expf(v[j] - mx);
+              } else if (row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __fdiv_rn(expf(v[j] - mx), sum);
+                chunk_store(p, v, grow, c0, bz);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_tempty + 8 * acc, 0));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may read this CTA's shared memory until its last MMA is done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, P_TMEM_COLS);
+  }
+}
+
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Tensor map over [batch,] rows x cols elements (fp32 or bf16), box = `box_cols` x `box_rows`.
+int make_map_any(CUtensorMap* map, const void* ptr, bool bf16, long long batch, long long rows,
+                 long long cols, long long ld, long long batch_stride, int box_cols, int box_rows,
+                 bool n_major) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  const size_t es = bf16 ? 2 : 4;
+  const bool three = batch > 1;
+  const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * es, (cuuint64_t)batch_stride * es};
+  const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1u};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  three ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  n_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ANNC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return ANNC_OK;
+}
+
+}  // namespace
+
+bool pair_supported(const annc_gemm_desc& d, int math) {
+  const int io = d.io_flags;
+  const bool bf16 = math == ANNC_MATH_BF16;
+  if (math != ANNC_MATH_TF32 && !bf16) return false;
+  if (d.trans_a || d.b_format != ANNC_B_PLAIN || d.batch < 1 || d.batch > (1 << 20)) return false;
+  if (bf16) {
+    if ((io & (ANNC_IO_A_BF16 | ANNC_IO_B_BF16)) != (ANNC_IO_A_BF16 | ANNC_IO_B_BF16)) return false;
+    if (!d.trans_b) return false;  // bf16 B is [N,K]
+  } else if (io & (ANNC_IO_A_BF16 | ANNC_IO_B_BF16)) {
+    return false;
+  }
+  const int es = bf16 ? 2 : 4, per16 = 16 / es;
+  if (d.m < 1 || d.n < 8 || d.k < 1) return false;
+  if (d.m > (1LL << 30) || d.n > (1LL << 30) || d.k > (1LL << 30)) return false;
+  if (!al16(d.a) || (d.lda % per16) || !al16(d.b) || (d.ldb % per16)) return false;
+  if (!d.trans_b && (d.n & 3)) return false;
+  if (d.batch > 1) {
+    if ((d.stride_a % per16) || d.stride_a <= 0 || (d.stride_b % per16) || d.stride_b < 0 ||
+        d.stride_c <= 0)
+      return false;
+  }
+  if ((io & ANNC_IO_SOFTMAX) && d.n > PN) return false;
+  return true;
+}
+
+int run_pair(const annc_gemm_desc& d, int math, cudaStream_t s) {
+  if (!pair_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 pair gemm: unsupported shape");
+  const bool bf16 = math == ANNC_MATH_BF16;
+  static int max_pairs[2] = {0, 0};
+  auto kern = bf16 ? gemm_pair_tcgen05_kernel<1> : gemm_pair_tcgen05_kernel<0>;
+  if (max_pairs[bf16] == 0) {
+    ANNC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM));
+    cudaLaunchConfig_t q;
+    memset(&q, 0, sizeof(q));
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    q.gridDim = dim3(2, 1, 1);
+    q.blockDim = dim3(P_THREADS, 1, 1);
+    q.dynamicSmemBytes = P_SMEM;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int n = 0;
+    ANNC_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &q));
+    if (n < 1) return fail(ANNC_ERR_CUDA, "no CTA pair fits this device");
+    max_pairs[bf16] = n;
+  }
+  const int kelts = bf16 ? 64 : 32;
+  const bool batched = d.batch > 1, b_batched = batched && d.stride_b > 0;
+  CUtensorMap ta, tb;
+  ANNC_TRY(make_map_any(&ta, d.a, bf16, batched ? d.batch : 1, d.m, d.k, d.lda, d.stride_a, kelts, PM, false));
+  PairParams p;
+  memset(&p, 0, sizeof(p));
+  if (d.trans_b) {
+    ANNC_TRY(make_map_any(&tb, d.b, bf16, b_batched ? d.batch : 1, d.n, d.k, d.ldb, d.stride_b, kelts,
+                          PN / 2, false));
+  } else {
+    p.b_n_major = 1;
+    ANNC_TRY(make_map_any(&tb, d.b, false, b_batched ? d.batch : 1, d.k, d.n, d.ldb, d.stride_b, 32, 32, true));
+  }
+  p.M = (int)d.m;
+  p.N = (int)d.n;
+  p.K = (int)d.k;
+  p.C = d.c;
+  p.ldc = d.ldc;
+  p.addend = d.addend;
+  p.ld_addend = d.ld_addend;
+  p.bias = d.bias;
+  p.alpha = d.alpha;
+  p.beta = d.beta;
+  p.act = d.activation;
+  p.softmax = (d.io_flags & ANNC_IO_SOFTMAX) ? 1 : 0;
+  p.c_bf16 = (d.io_flags & ANNC_IO_C_BF16) ? 1 : 0;
+  p.batched = batched;
+  p.b_batched = b_batched;
+  p.stride_c = batched ? d.stride_c : 0;
+  p.stride_addend = batched ? d.stride_addend : 0;
+  p.tiles_m = (int)((d.m + 2 * PM - 1) / (2 * PM));
+  p.tiles_n = (int)((d.n + PN - 1) / PN);
+  p.tiles = (long long)p.tiles_m * p.tiles_n * d.batch;
+  p.error_word = gemm_error_word();
+  if (!p.error_word) return fail(ANNC_ERR_CUDA, "gemm error word is not addressable");
+  const long long pairs = p.tiles < max_pairs[bf16] ? p.tiles : max_pairs[bf16];
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(P_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ANNC_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+  return ANNC_OK;
+}
+
+}  // namespace gemm
+}  // namespace annc

@@ -71,7 +71,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, m: int, n: int, k
          ld_addend: Optional[int] = None, stride_addend: int = 0,
          bias: Optional[torch.Tensor] = None, activation: int = ACT_NONE,
          b_format: int = B_PLAIN, math: int = MATH_AUTO,
-         workspace: Optional[torch.Tensor] = None) -> str:
+         workspace: Optional[torch.Tensor] = None, io_flags: int = 0) -> str:
     """annc_gemm_run; returns the name of the kernel family that ran."""
     d = GemmDesc()
     d.trans_a, d.trans_b = int(trans_a), int(trans_b)
@@ -86,6 +86,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, m: int, n: int, k
     d.addend = addend.data_ptr() if addend is not None else None
     d.bias = bias.data_ptr() if bias is not None else None
     d.activation, d.b_format, d.math = activation, b_format, math
+    d.io_flags = io_flags
     if workspace is not None:
         d.workspace, d.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     name = lib.annc_gemm_kernel_name(C.byref(d)).decode()
@@ -112,6 +113,22 @@ def dot_interaction(z: torch.Tensor, out: torch.Tensor, math: int = MATH_AUTO) -
     check(lib.annc_dot_interaction_dev(C.c_void_p(z.data_ptr()), C.c_int64(batch), C.c_int(F),
                                        C.c_int(D), C.c_int64(F * D), C.c_void_p(out.data_ptr()),
                                        C.c_int64(out.shape[1]), C.c_int(math), _stream()))
+
+
+def bf16_weight(b_kn: torch.Tensor) -> torch.Tensor:
+    """fp32 [K,N] -> bf16 [N,K] for the BF16 route (annc_bf16_weight_dev)."""
+    k, n = b_kn.shape
+    out = torch.empty((n, k), dtype=torch.bfloat16, device=b_kn.device)
+    check(lib.annc_bf16_weight_dev(C.c_void_p(b_kn.data_ptr()), C.c_int64(b_kn.stride(0)),
+                                   C.c_void_p(out.data_ptr()), C.c_int64(k), C.c_int64(n), _stream()))
+    return out
+
+
+def cast_bf16(x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    check(lib.annc_cast_bf16_dev(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+                                 C.c_int64(x.numel()), _stream()))
+    return out
 
 
 def kn4_pack(b_kn: torch.Tensor) -> torch.Tensor:

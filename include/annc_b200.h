@@ -350,6 +350,13 @@ void annc_embed_bag_set_timing_events(void* start, void* stop);
 enum { ANNC_ACT_NONE = 0, ANNC_ACT_RELU = 1, ANNC_ACT_SIGMOID = 2 };
 enum { ANNC_B_PLAIN = 0, ANNC_B_KN4 = 1 };
 enum { ANNC_MATH_AUTO = 0, ANNC_MATH_FP32 = 1, ANNC_MATH_TF32 = 2, ANNC_MATH_BF16 = 3 };
+/* io_flags.  The reference's operators are fp32 end to end; the BF16 route is for graphs that
+ * ask for it: weights converted once (annc_bf16_weight_dev), activations produced in bf16 by
+ * the previous layer's epilogue (ANNC_IO_C_BF16).  With ANNC_MATH_BF16, a and b point to bf16
+ * data: A [M,K], B [N,K] (trans_b = 1), lda / ldb / stride_a / stride_b in elements.
+ * ANNC_IO_SOFTMAX applies a row softmax over the n <= 256 columns after bias and activation
+ * (batch_matmul followed by the XNNPACK softmax, in one kernel). */
+enum { ANNC_IO_A_BF16 = 1, ANNC_IO_B_BF16 = 2, ANNC_IO_C_BF16 = 4, ANNC_IO_SOFTMAX = 8 };
 
 typedef struct annc_gemm_desc {
   int32_t trans_a, trans_b;
@@ -366,7 +373,7 @@ typedef struct annc_gemm_desc {
   int32_t activation;            /* ANNC_ACT_*    */
   int32_t b_format;              /* ANNC_B_*; KN4 = python/annc/optimize/data_pack.py layout */
   int32_t math;                  /* ANNC_MATH_*   */
-  int32_t reserved;
+  int32_t io_flags;              /* ANNC_IO_* */
   void* workspace;               /* optional device scratch, 16-byte aligned, or NULL      */
   size_t workspace_bytes;        /* with >= 4*k*n bytes a large kn4 GEMM first unpacks B   */
 } annc_gemm_desc;                /* into it and then runs at the speed of the plain layout */
@@ -375,8 +382,16 @@ int annc_gemm_run(const annc_gemm_desc* desc, void* stream);
 /* Synchronises `stream` and reports whether a tensor-core GEMM CTA has given up on one of
  * its bounded mbarrier waits since the library was loaded (its output is then invalid). */
 int annc_gemm_check(void* stream, int* timed_out);
-/* Name of the kernel family annc_gemm_run would pick ("tcgen05_tf32", "simt_fp32", ...). */
+/* Name of the kernel family annc_gemm_run would pick: "tcgen05_pair_tf32" / "tcgen05_pair_bf16"
+ * (persistent CTA-pair kernel), "tcgen05_tf32" (single-CTA tiles, also the kn4 loader),
+ * "simt_fp32" (CUDA cores). */
 const char* annc_gemm_kernel_name(const annc_gemm_desc* desc);
+
+/* fp32 -> bf16 (round to nearest even), n elements. */
+int annc_cast_bf16_dev(const float* src, void* dst_bf16, int64_t n, void* stream);
+/* Weight for the BF16 route: fp32 B[K,N] (row pitch ldb) -> bf16 [N,K], converted once. */
+int annc_bf16_weight_dev(const float* b_kn, int64_t ldb, void* b_nk_bf16, int64_t k, int64_t n,
+                         void* stream);
 
 /* kn4 <-> [K,N] conversion on the device (layout of python/annc/optimize/data_pack.py,
  * vector 12, tiles 352 x 128, python/annc/optimize/constant_folding.py:77-88). */

@@ -43,7 +43,7 @@ def test_tf32_gemm_sources(m, n, k, bsrc):
         name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, math=MATH_TF32)
     else:
         name = device.gemm(_dev(a), _dev(oracle.kn4_pack(b)), c, m=m, n=n, k=k, b_format=B_KN4, math=MATH_TF32)
-    assert name == "tcgen05_tf32"
+    assert name.startswith("tcgen05") and name.endswith("tf32")
     assert not device.gemm_timed_out()
     assert nerr(c, want) <= TF32_TOL
 
@@ -85,7 +85,7 @@ def test_tf32_epilogues(act, with_addend, with_bias, alpha, beta):
     name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, alpha=alpha, beta=beta,
                        addend=_dev(add) if with_addend else None, bias=_dev(bias) if with_bias else None,
                        activation=act, math=MATH_TF32)
-    assert name == "tcgen05_tf32" and not device.gemm_timed_out()
+    assert name.startswith("tcgen05") and name.endswith("tf32") and not device.gemm_timed_out()
     pre = alpha * (a @ b) + beta * c0
     scale = np.abs(pre).max()
     assert np.abs(c.cpu().numpy() - want).max() <= TF32_TOL * scale
@@ -113,7 +113,7 @@ def test_layout_matmul_full_config_properties():
     xd = _dev(x)
     y = torch.empty((8192, 4096), device="cuda")
     name = device.gemm(xd, packed, y, m=8192, n=4096, k=2048, b_format=B_KN4)
-    assert name == "tcgen05_tf32" and not device.gemm_timed_out()
+    assert name.startswith("tcgen05") and name.endswith("tf32") and not device.gemm_timed_out()
     rows = np.random.default_rng(0).integers(0, 8192, 64)
     want = x[rows] @ w
     assert np.abs(y[torch.from_numpy(rows).cuda()].cpu().numpy() - want).max() <= TF32_TOL * np.abs(want).max()
