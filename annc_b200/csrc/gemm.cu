@@ -38,14 +38,16 @@ static int forced_route() {
   return v;
 }
 
-// The CTA-pair kernel works on 256 x 256 tiles: it takes the GEMMs that fill them.
+// The CTA-pair kernel works on 256 x 256 tiles with a long main loop per tile: it takes the
+// compute-bound GEMMs.  Skinny layers (small K, output-bound) stay on the single-CTA kernel,
+// whose two resident CTAs per SM and staged, coalesced epilogue stream C faster.
 static bool use_pair(const annc_gemm_desc& d, int math) {
   if (!pair_supported(d, math)) return false;
   if (math == ANNC_MATH_BF16 || (d.io_flags & ANNC_IO_SOFTMAX)) return true;
   if (!tc_supported(d, math)) return true;
   const int f = forced_route();
   if (f) return f == 2;
-  return d.m >= 256 && d.n >= 192;
+  return d.m >= 256 && d.n >= 192 && d.k >= 1024;
 }
 
 // AUTO: tensor cores (TF32) when the shape fits a tcgen05 kernel, else CUDA cores.

@@ -16,7 +16,8 @@ import torch
 
 from . import device as dev
 from . import synth
-from ._lib import ACT_NONE, ACT_RELU, B_KN4, B_PLAIN, MATH_AUTO
+from ._lib import (ACT_NONE, ACT_RELU, B_KN4, B_PLAIN, IO_A_BF16, IO_B_BF16, IO_C_BF16, IO_SOFTMAX,
+                   MATH_AUTO, MATH_BF16)
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -30,6 +31,21 @@ def peaks():
 
 
 _flush = None
+_nvml = None
+
+
+def sm_clock_mhz():
+    """Current SM clock (read only), reported beside each timing: the tensor-core cases move
+    with the clock the power cap allows."""
+    global _nvml
+    try:
+        if _nvml is None:
+            import pynvml
+            pynvml.nvmlInit()
+            _nvml = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device()))
+        return int(_nvml[0].nvmlDeviceGetClockInfo(_nvml[1], _nvml[0].NVML_CLOCK_SM))
+    except Exception:
+        return None
 
 
 def time_ms(fn, reps, flush):
@@ -49,7 +65,12 @@ def time_ms(fn, reps, flush):
         e1.record()
         e1.synchronize()
         ts.append(e0.elapsed_time(e1))
+    global LAST_CLOCK
+    LAST_CLOCK = sm_clock_mhz()
     return float(np.median(ts))
+
+
+LAST_CLOCK = None
 
 
 def bmm_case(name, b, m, n, k, reps):
@@ -70,10 +91,56 @@ def bmm_case(name, b, m, n, k, reps):
                       "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
                       "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
                       "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "peak": src}), flush=True)
+                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
 
 
 MATCH = ""
+
+
+def bf16_case(name, m, n, k, reps):
+    """bf16 A [M,K] x bf16 B [N,K] -> bf16 C with bias + ReLU (the large recsys MLP layers)."""
+    if MATCH and MATCH not in f"{name}/bf16":
+        return
+    hbm, tf32, src = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
+    b = (torch.randn((n, k), device="cuda", generator=g) / k ** 0.5).to(torch.bfloat16)
+    bv = torch.randn(n, device="cuda", generator=g)
+    c = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    names = []
+    fn = lambda: names.append(dev.gemm(a, b, c, m=m, n=n, k=k, trans_b=True, bias=bv, activation=ACT_RELU,
+                                       math=MATH_BF16, io_flags=IO_A_BF16 | IO_B_BF16 | IO_C_BF16))
+    byt = 2 * (m * k + k * n + m * n)
+    ms = time_ms(fn, reps, flush=byt < (200 << 20))
+    fl = 2.0 * m * n * k
+    print(json.dumps({"op": name, "kernel": names[-1], "b": "nk bf16", "m": m, "n": n, "k": k,
+                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                      "frac_bf16_peak": round(fl / ms / 1e9 / (2 * tf32), 3),
+                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
+                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
+
+
+def bmm_softmax_case(name, b, m, n, k, reps):
+    """batch_matmul + row softmax: two kernels (matmul, then softmax) against the fused epilogue."""
+    if MATCH and MATCH not in f"{name}/kn":
+        return
+    hbm, _, src = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((b, m, k), device="cuda", generator=g) / 8
+    w = torch.randn((b, k, n), device="cuda", generator=g)
+    c = torch.empty((b, m, n), device="cuda")
+    y = torch.empty((b, m, n), device="cuda")
+    kw = dict(m=m, n=n, k=k, batch=b, stride_a=m * k, stride_b=k * n, stride_c=m * n)
+
+    def two():
+        dev.gemm(a, w, c, **kw)
+        dev.softmax(c.view(-1, n), y.view(-1, n))
+    ms2 = time_ms(two, reps, flush=True)
+    ms1 = time_ms(lambda: dev.gemm(a, w, y, io_flags=IO_SOFTMAX, **kw), reps, flush=True)
+    byt = 4 * b * (m * k + k * n + m * n)
+    print(json.dumps({"op": name, "two_kernels_ms": round(ms2, 4), "fused_ms": round(ms1, 4),
+                      "fused_gbs": round(byt / ms1 / 1e6, 1), "fused_frac_hbm": round(byt / ms1 / 1e6 / hbm, 3),
+                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
 
 
 def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False):
@@ -106,7 +173,7 @@ def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=F
                       "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
                       "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
                       "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "peak": src}), flush=True)
+                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
 
 
 def run_gemm(reps):
@@ -114,6 +181,10 @@ def run_gemm(reps):
     for bsrc in ("kn4", "kn4+ws", "kn", "nk"):
         gemm_case("layout_matmul C2", 8192, 4096, 2048, reps, bsrc=bsrc)
     bmm_case("batch_matmul C2", 64, 256, 256, 64, reps)
+    bmm_softmax_case("batch_matmul + softmax C2", 64, 256, 256, 64, reps)
+    for (m, n, k) in ((16384, 1024, 8192), (131072, 1024, 8192), (131072, 512, 1024), (8192, 8192, 8192)):
+        bf16_case("recsys MLP bf16", m, n, k, reps)
+    gemm_case("square tf32", 8192, 8192, 8192, reps, bsrc="nk")
     for m in (128, 256, 512):
         gemm_case("small-M sweep", m, 1024, 1024, reps)
     for (k, n) in ((512, 256), (256, 64), (416, 512), (512, 256)):
@@ -134,7 +205,7 @@ def run_embed(reps):
     print(json.dumps({"op": "embed_hash_bucket + segment sum C3 (prepass + bags)", "ms": round(ms, 4),
                       "lookups": w.nnz, "gbs": round(byt / ms / 1e6, 1),
                       "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "samples_per_s": round(w.batch / ms * 1e3), "peak": src}), flush=True)
+                      "samples_per_s": round(w.batch / ms * 1e3), "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
 
 
 def run_misc(reps):
