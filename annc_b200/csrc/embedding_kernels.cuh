@@ -225,6 +225,7 @@ bag_reduce_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 
   const int start = roff[s], end = roff[s + 1];
+  if (!SHARDED && p.skip_empty && start == end) return;  // exchange: an empty part is not written
   int owned = 0;  // SHARDED: lookups of this bag that belong to this rank (group-uniform)
   for (int base = start; base < end; base += LANES) {
     int my = -1;  // local row (tables have fewer than 2^31 rows), -1 = skip
@@ -311,6 +312,100 @@ bag_owner_mask_kernel(BagParams p, unsigned* mask) {
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) m |= __shfl_xor_sync(gmask, m, o, 16);
   if (lane == 0) mask[group] = m;
+}
+
+// ---- row sharding, ids partitioned at the source -------------------------------------
+// The rank that owns a batch splits every bag's lookups by owner rank (row % shard_count)
+// and resolves them to local rows (row / shard_count): owner g receives, for every bag, only
+// the int32 local rows it has to read, in lookup order.  Two passes of the same walk, half a
+// warp per bag: COUNT writes cnt[(g * tables + t) * batch + s]; after an exclusive scan of
+// that array (positions, with one extra closing entry) SCATTER writes the local rows at
+// pos[(g * tables + t) * batch + s] + (rank of the lookup among the bag's lookups of owner g)
+// and the owner mask of the bag.  Lane g of the group keeps the running count of owner g.
+template <bool SCATTER>
+__global__ void __launch_bounds__(256)
+bag_partition_kernel(BagParams p, int tables_total, int t0, int* __restrict__ cnt_or_pos,
+                     int* __restrict__ rows_out, unsigned* __restrict__ mask) {
+  const int lane = threadIdx.x & 15;
+  const int shift = threadIdx.x & 16;
+  const unsigned gmask = 0xffffu << shift;
+  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const long long total = (long long)p.num_tables * p.batch;
+  if (group >= total) return;
+  const int t = (int)(group / p.batch);
+  const long long s = group - (long long)t * p.batch;
+  const BagTableDev& T = p.t[t];
+  const int G = p.shard_count;
+  const int start = T.given_off[s], end = T.given_off[s + 1];
+  const long long slot = ((long long)lane * tables_total + (t0 + t)) * p.batch + s;  // lane = owner
+  int run = 0;
+  int my_pos = (SCATTER && lane < G) ? cnt_or_pos[slot] : 0;
+  for (int base = start; base < end; base += 16) {
+    const int i = base + lane;
+    int owner = -1, local = -1;
+    if (i < end) {
+      const long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic);
+      if (r >= 0 && (unsigned long long)r <= 0xffffffffull) {
+        const unsigned b = (unsigned)r, q = b / (unsigned)G;
+        owner = (int)(b - q * (unsigned)G);
+        local = (int)q;
+      } else if (r >= 0) {
+        owner = (int)(r % G);
+        const long long q = r / G;
+        local = q > 0x7fffffffLL ? 0x7fffffff : (int)q;  // past any table: flagged by the owner
+      } else {
+        owner = 0;  // a negative row goes to rank 0 as -1, which flags it
+      }
+    }
+    for (int g = 0; g < G; ++g) {
+      const unsigned m = (__ballot_sync(gmask, owner == g) >> shift) & 0xffffu;
+      if (SCATTER) {
+        const int first = __shfl_sync(gmask, my_pos + run, g, 16);
+        if (owner == g) rows_out[first + __popc(m & ((1u << lane) - 1u))] = local;
+      }
+      if (lane == g) run += __popc(m);
+    }
+  }
+  if (!SCATTER) {
+    if (lane < G) cnt_or_pos[slot] = run;
+  } else {
+    const unsigned m = (__ballot_sync(gmask, lane < G && run > 0) >> shift) & 0xffffu;
+    if (lane == 0) mask[(long long)(t0 + t) * p.batch + s] = m;
+  }
+}
+
+// Pull step of the exchange: copies from every peer the positions and local rows it prepared
+// for this rank.  Source q's arrays are read through peer-mapped pointers with plain loads;
+// rows keep their index, so positions stay valid in the copy.  blockIdx.y = source.
+struct PullParams {
+  const int* pos[32];   // source q: positions, int32[shards * per_rank + 1]
+  const int* rows[32];  // source q: local rows
+  int* pos_out[32];     // int32[per_rank + 1]
+  int* rows_out[32];    // indexed like rows[q]
+  long long per_rank;   // tables * batch
+  int me;
+};
+__global__ void __launch_bounds__(256)
+bag_pull_kernel(PullParams a) {
+  const int q = blockIdx.y;
+  const int* __restrict__ pos = a.pos[q] + (long long)a.me * a.per_rank;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long i = tid; i <= a.per_rank; i += stride) a.pos_out[q][i] = pos[i];
+  const int lo = pos[0], hi = pos[a.per_rank];
+  const int* __restrict__ src = a.rows[q];
+  int* __restrict__ dst = a.rows_out[q];
+  // 16-byte body between the aligned bounds, scalar head and tail
+  const int lo4 = (lo + 3) & ~3, hi4 = hi & ~3;
+  if (lo4 >= hi4) {
+    for (long long i = lo + tid; i < hi; i += stride) dst[i] = src[i];
+    return;
+  }
+  for (long long i = lo + tid; i < lo4; i += stride) dst[i] = src[i];
+  for (long long i = hi4 + tid; i < hi; i += stride) dst[i] = src[i];
+  const int4* s4 = reinterpret_cast<const int4*>(src);
+  int4* d4 = reinterpret_cast<int4*>(dst);
+  for (long long i = lo4 / 4 + tid; i < hi4 / 4; i += stride) d4[i] = s4[i];
 }
 
 // Any dim (not a multiple of 4, or unaligned tables): one warp per bag, lanes

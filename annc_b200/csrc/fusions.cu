@@ -256,7 +256,8 @@ sum_partials_kernel(const float* __restrict__ src, int parts, long long part_str
 __global__ void __launch_bounds__(256)
 sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __restrict__ mask,
                            int parts, long long part_stride, long long rows, int slots,
-                           int slot_w4, float* __restrict__ out, long long out_stride) {
+                           int slot_w4, const int* __restrict__ mean_off, float* __restrict__ out,
+                           long long out_stride) {
   const long long width4 = (long long)slots * slot_w4;
   const long long total = rows * width4;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -281,6 +282,17 @@ sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __rest
         acc.y = __fadd_rn(acc.y, v.y);
         acc.z = __fadd_rn(acc.z, v.z);
         acc.w = __fadd_rn(acc.w, v.w);
+      }
+    }
+    if (mean_off) {  // mean pooling: the sum times 1/len(bag), like the reference's second pass
+      const int* o = mean_off + (long long)slot * (rows + 1) + r;
+      const int len = o[1] - o[0];
+      if (len > 0) {
+        const float inv = __fdiv_rn(1.0f, (float)len);
+        acc.x = __fmul_rn(acc.x, inv);
+        acc.y = __fmul_rn(acc.y, inv);
+        acc.z = __fmul_rn(acc.z, inv);
+        acc.w = __fmul_rn(acc.w, inv);
       }
     }
     *reinterpret_cast<float4*>(out + r * out_stride + (long long)c4 * 4) = acc;
@@ -384,7 +396,8 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
 
 int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
-                                 float* out, int64_t out_stride, void* stream) {
+                                 const int32_t* mean_offsets, float* out, int64_t out_stride,
+                                 void* stream) {
   ANNC_REQUIRE(src && out && mask && parts >= 1 && parts <= 32 && slots >= 1,
                ANNC_ERR_INVALID_ARGUMENT, "null or bad argument");
   ANNC_REQUIRE((slot_width & 3) == 0 && slot_width > 0 && (out_stride & 3) == 0 &&
@@ -395,7 +408,7 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
   long long g = (rows * slots * (slot_width / 4) + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
   sum_partials_masked_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), out, out_stride);
+      src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), mean_offsets, out, out_stride);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

@@ -6,14 +6,18 @@ Three partitionings of the tables, the MLPs always run on the rank's own batch s
   row      every table row-sharded with the reference's mod rule
            (owner = bucket % G, local row = bucket / G,
            annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71).
-           Ids and bag offsets are all-gathered, every rank pools the lookups it owns for
-           the global batch, and the bag kernel stores each partial sum straight into the
-           memory of the rank that owns the sample (peer-mapped receive buffers,
-           annc_peer_buffer_*): pooling and exchange are one kernel.  A one-element
-           all-reduce orders the stores before the owner adds the parts in rank order.
-  row_nccl the same partitioning with the exchange as a separate step: partial sums are
-           written locally, then go through an NCCL all-to-all (kept as the baseline the
-           fused step is measured against).
+           Each rank splits its own lookups by owner and resolves them to int32 local rows
+           (annc_embed_bag_partition_dev); the owners pull their slices through peer-mapped
+           pointers, pool them, and the bag kernel stores each partial sum straight into the
+           memory of the rank that owns the sample (annc_peer_buffer_*): pooling and
+           exchange are one kernel, and nothing is computed or sent for a (bag, rank) pair
+           without lookups.  One-element all-reduces order the steps; the owner adds the
+           parts in rank order.
+  row_gather  the same fused stores, but raw ids and bag offsets are all-gathered and every
+           rank filters the global batch's ids itself (G times the id work per rank).
+  row_nccl the all-gathered ids with the exchange as a separate step: partial sums are
+           written locally, then go through an NCCL all-to-all (the baseline the fused
+           step is measured against).
   table    whole tables per rank (contiguous blocks); ids travel to the owners by
            all-to-all, finished pooled vectors come back by all-to-all, no add.
   replica  every rank holds every table; no exchange (scaling ceiling when tables fit).
@@ -31,7 +35,7 @@ class ShardPlan:
     """Sizes and offsets of the exchange.  nnz[s][t] = lookups of rank s in table t."""
 
     def __init__(self, mode: str, world: int, rank: int, table_rows: List[int], nnz: np.ndarray):
-        assert mode in ("row", "row_nccl", "table", "replica")
+        assert mode in ("row", "row_gather", "row_nccl", "table", "replica")
         self.mode, self.world, self.rank = mode, world, rank
         self.table_rows = list(table_rows)
         self.T = len(table_rows)
@@ -108,7 +112,10 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 DlrmPipeline._setup_embedding(self, m)
                 self.exchange_bytes = 0
                 return
-            if mode in ("row", "row_nccl"):
+            if mode == "row":
+                self._setup_row_partitioned(m, plan)
+                return
+            if mode in ("row_gather", "row_nccl"):
                 # Only the raw ids (8 bytes per lookup) and the bag offsets of each rank's
                 # batch travel: every rank runs the prepass on its own index matrices and
                 # the offsets (4 bytes per bag) are gathered with the ids.
@@ -122,7 +129,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
                 self.off_g = torch.zeros((world, wsb), dtype=torch.uint8, device=self.device)
                 part_bytes = B * T * D * 4
-                if mode == "row":
+                if mode == "row_gather":
                     # Two receive buffers [world, B, T, D] used on alternate steps: a peer may
                     # start storing step i+1 while this rank still adds the parts of step i.
                     self.peer = dev.PeerBuffers(2 * world * part_bytes, world, rank)
@@ -147,8 +154,8 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                                             self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
                     self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device,
                                                        shard_count=world, shard_rank=rank,
-                                                       exchange=(mode == "row")))
-                if mode == "row":
+                                                       exchange=(mode == "row_gather")))
+                if mode == "row_gather":
                     # which ranks write a part for each bag of this rank's own batch
                     for st in self.sets:
                         st["owners"] = dev.OwnerMask(
@@ -192,18 +199,88 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             self.embed_launches = 3 * ((len(entries) + 63) // 64) + world
             self.exchange_bytes = (sum(sc) - sc[rank]) * 8 + (T - To) * (B + 1) * 4 + (T - To) * B * D * 4
 
+        def _setup_row_partitioned(self, m, plan) -> None:
+            """Row sharding with the ids split at their source.  Each rank resolves its own
+            lookups to (owner, local row), the owners pull their slices through peer-mapped
+            pointers, pool them, and store the partial sums into the source's receive buffer."""
+            emb = m.emb
+            T, B, D = self.T, self.batch, self.dim
+            TB = T * B
+            self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
+            L = max(1, plan.gathered_len())
+            for st in self.sets:
+                st["prepass"] = dev.BagPrepass(st["segs"], B)
+            wsb = self.sets[0]["prepass"].ws_bytes
+            self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
+            part_bytes = B * T * D * 4
+            up256 = lambda n: (n + 255) // 256 * 256
+            off_pos = 2 * world * part_bytes          # after the two receive buffers [world, B, T, D]
+            off_rows = off_pos + up256((world * TB + 1) * 4)
+            self.peer = dev.PeerBuffers(off_rows + up256(L * 4), world, rank)
+            self.flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+            pos_of = lambda q: self.peer.ptrs[q] + off_pos
+            rows_of = lambda q: self.peer.ptrs[q] + off_rows
+            off_ptr = lambda t: self.off_ws.data_ptr() + 512 + t * (B + 1) * 4
+            for st in self.sets:
+                st["partition"] = dev.BagPartition(
+                    [(st["ids"][t].data_ptr(), self.nnz[t], plan.table_rows[t], off_ptr(t)) for t in range(T)],
+                    B, world, pos_of(rank), rows_of(rank), self.device)
+            i32 = dict(dtype=torch.int32, device=self.device)
+            self.pos_in = torch.zeros((world, TB + 1), **i32)
+            self.rows_in = torch.zeros((world, L), **i32)
+            srcs = [q for q in range(world) if q != rank]
+            self.pull = dev.BagPull([pos_of(q) for q in srcs], [rows_of(q) for q in srcs], rank, TB,
+                                    [self.pos_in[q].data_ptr() for q in srcs],
+                                    [self.rows_in[q].data_ptr() for q in srcs]) if srcs else None
+            self.launches = []
+            for buf in range(2):
+                entries = []
+                for s in range(world):
+                    if s == rank:  # own lookups are read in place
+                        ids_ptr, pos_ptr = rows_of(rank), pos_of(rank) + rank * TB * 4
+                    else:
+                        ids_ptr, pos_ptr = self.rows_in[s].data_ptr(), self.pos_in[s].data_ptr()
+                    for t in range(T):
+                        entries.append((self.tables[t].data_ptr(), plan.local_rows(t), 1, ids_ptr, None, L,
+                                        self.peer.ptrs[s] + (buf * world + rank) * part_bytes + t * D * 4,
+                                        pos_ptr + t * B * 4))
+                self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device, id_kind=0,
+                                                   shard_count=1, shard_rank=0, exchange=True))
+            self.launch = self.launches[0]
+            self._row_step = 0
+            self.embed_launches = 2 * ((len(entries) + 55) // 56) + 8
+            self.exchange_bytes = (world - 1) * (B * T * D * 4 + TB * 4) + L * 4
+            self._works = None
+
         def embed(self) -> None:
             plan = self.shard
             T, B, D, F = self.T, self.batch, self.dim, self.F
             if mode == "replica":
                 return DlrmPipeline.embed(self)
-            if mode in ("row", "row_nccl"):
+            if mode == "row":
+                if self._works is None:
+                    self.embed_prefetch()
+                for w in self._works:
+                    w.wait()                    # every rank has split its lookups
+                self._works = None
+                buf = self._row_step % 2
+                self._row_step += 1
+                if self.pull is not None:
+                    self.pull.run()             # my slices of the peers' positions and local rows
+                self.launch = self.launches[buf]
+                self.launch.run()               # partial sums land in their owners' memory
+                dist.all_reduce(self.flag)      # every rank's bag kernel has finished
+                dev.sum_partials_masked(self.peer.local + buf * world * B * T * D * 4,
+                                        self._partition.mask, world, B * T * D, B, T, D,
+                                        self.z.data_ptr() + D * 4, F * D)
+                return
+            if mode in ("row_gather", "row_nccl"):
                 if self._works is None:
                     self.embed_prefetch()
                 for w in self._works:
                     w.wait()
                 self._works = None
-                if mode == "row":
+                if mode == "row_gather":
                     buf = self._row_step % 2
                     self._row_step += 1
                     self.launch = self.launches[buf]
@@ -240,12 +317,18 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def embed_prefetch(self) -> None:
             """Row mode: starts the gathers of ids and bag offsets; the bottom MLP runs
             while they are in flight."""
-            if mode not in ("row", "row_nccl"):
+            if mode == "row":
+                self.sets[self.cur]["prepass"].run(self.off_ws)
+                self._partition = self.sets[self.cur]["partition"]
+                self._partition.run()
+                self._works = [dist.all_reduce(self.flag, async_op=True)]
+                return
+            if mode not in ("row_gather", "row_nccl"):
                 return
             n = self.nnz_total
             self.ids_pad[:n].copy_(self.ids_all)
             self.sets[self.cur]["prepass"].run(self.off_ws)
-            if mode == "row":
+            if mode == "row_gather":
                 self._owners = self.sets[self.cur]["owners"]
                 self._owners.run()
             self._works = [dist.all_gather_into_tensor(self.ids_g, self.ids_pad, async_op=True),
@@ -254,7 +337,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def embed_error_bits(self) -> int:
             if mode == "replica":
                 return DlrmPipeline.embed_error_bits(self)
-            if mode == "row":
+            if mode in ("row", "row_gather"):
                 return self.launches[0].error_bits() | self.launches[1].error_bits()
             return self.launch.error_bits() if self.launch is not None else 0
 

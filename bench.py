@@ -46,10 +46,11 @@ def parse_args():
     ap.add_argument("--max-rows", type=float, default=1e7)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_nccl", "table", "replica"],
-                    help="table partitioning for --gpus > 1: row = mod row-sharding, the bag kernel "
-                         "stores partial sums into the owner rank's memory; row_nccl = the same with "
-                         "a separate NCCL all-to-all; table = whole tables per rank; replica = no exchange; auto = "
+    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_gather", "row_nccl", "table", "replica"],
+                    help="table partitioning for --gpus > 1: row = mod row-sharding, lookups split by "
+                         "owner at their source, the bag kernel stores partial sums into the owner "
+                         "rank's memory; row_gather = the same stores with all-gathered ids; row_nccl = "
+                         "all-gathered ids and a separate NCCL all-to-all; table = whole tables per rank; replica = no exchange; auto = "
                          "row when the tables exceed --hbm-budget-gb per GPU, else replica")
     ap.add_argument("--hbm-budget-gb", type=float, default=100.0,
                     help="per-GPU memory the tables may take before auto switches to row sharding")

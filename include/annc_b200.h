@@ -257,7 +257,10 @@ int annc_embed_bags_sharded_dev(const annc_bag_table* tables /* host array */, i
  * points into the receive buffer of the rank that owns the samples (annc_peer_buffer_open),
  * so the partial sums cross NVLink as the kernel's own stores and nothing is sent for bags
  * this rank does not contribute to.  The owner learns which parts exist from its own ids
- * (annc_embed_bag_owner_mask_dev) and adds them with annc_sum_partials_masked_dev. */
+ * (annc_embed_bag_owner_mask_dev) and adds them with annc_sum_partials_masked_dev.
+ * With shard_count 1 the ids are already this rank's local rows (annc_embed_bag_partition_dev
+ * ran at the source): every lookup is read and bags with offsets[s] == offsets[s + 1] are the
+ * ones left unwritten. */
 int annc_embed_bags_exchange_dev(const annc_bag_table* tables /* host array */, int num_tables,
                                  int64_t dim, int id_kind, int combiner, int64_t batch,
                                  int64_t out_stride, int shard_count, int shard_rank,
@@ -270,10 +273,40 @@ int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables /* host array */,
                                   void* stream);
 /* out[r, slot, :] = sum, in ascending p, of the parts p whose bit is set in
  * mask[slot * rows + r]; part p holds f32[rows, slots, slot_width] at src + p * part_stride
- * floats; zero when no bit is set.  Parts whose bit is clear are not read. */
+ * floats; zero when no bit is set.  Parts whose bit is clear are not read.  With
+ * mean_offsets (i32[slots][rows + 1], the bag offsets of the prepass) the sum is multiplied by
+ * 1.0f / len(bag), the reference's mean (embedding_fused_sparse_segment_reduce.cc:112-130). */
 int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
-                                 float* out, int64_t out_stride, void* stream);
+                                 const int32_t* mean_offsets, float* out, int64_t out_stride,
+                                 void* stream);
+
+/* Row sharding with the ids partitioned at their source (the exchange the multi-GPU pipeline
+ * uses).  The rank that owns a batch splits the lookups of every bag by owner rank
+ * (row % shard_count, the mod partition of embedding_fused_sparse_dynamic_stitch.cc:70-71) and
+ * resolves them to local rows (row / shard_count), keeping lookup order:
+ *   positions  i32[shard_count * num_tables * batch + 1]: exclusive prefix of the per-(owner g,
+ *              table t, bag s) counts in (g, t, s) order; the lookups owner g needs of bag s of
+ *              table t are local_rows[positions[i] .. positions[i + 1]), i = (g * T + t) * batch + s
+ *   local_rows i32[sum of nnz]
+ *   owner_mask u32[num_tables * batch]: bit g set when owner g has a lookup of the bag
+ * tables[t] supplies ids, nnz, num_buckets and offsets (bag offsets of the prepass).  Owner g
+ * then copies its slice of both arrays from every source (annc_embed_bag_pull_dev, plain loads
+ * through peer-mapped pointers), pools it with annc_embed_bags_exchange_dev (shard_count 1,
+ * id_kind 0, offsets = the copied positions) straight into the sources' receive buffers, and each
+ * source adds the parts named by owner_mask.  shard_count <= 16. */
+size_t annc_embed_bag_partition_scratch_bytes(int num_tables, int64_t batch, int shard_count);
+int annc_embed_bag_partition_dev(const annc_bag_table* tables /* host array */, int num_tables,
+                                 int id_kind, int64_t batch, int shard_count, int32_t* positions,
+                                 int32_t* local_rows, uint32_t* owner_mask, void* scratch,
+                                 size_t scratch_bytes, void* stream);
+/* For each source q < num_sources: positions_out[q][0 .. per_rank] = peer_positions[q][me *
+ * per_rank .. (me + 1) * per_rank] and rows_out[q][i] = peer_rows[q][i] for i between the
+ * first and the last of those positions (indices are kept, so the positions address the copy).
+ * All four arguments are host arrays of device pointers; per_rank = num_tables * batch. */
+int annc_embed_bag_pull_dev(const int32_t* const* peer_positions, const int32_t* const* peer_rows,
+                            int num_sources, int me, int64_t per_rank, int32_t* const* positions_out,
+                            int32_t* const* rows_out, void* stream);
 /* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
  * reduce step after the all-to-all of partial sums).  src part p starts at
  * src + p * part_stride floats, rows are src_stride / out_stride floats apart. */
