@@ -397,7 +397,8 @@ bag_pull_kernel(PullParams a) {
   int* __restrict__ dst = a.rows_out[q];
   // 16-byte body between the aligned bounds, scalar head and tail
   const int lo4 = (lo + 3) & ~3, hi4 = hi & ~3;
-  if (lo4 >= hi4) {
+  const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  if (!aligned || lo4 >= hi4) {
     for (long long i = lo + tid; i < hi; i += stride) dst[i] = src[i];
     return;
   }

@@ -2,6 +2,8 @@
 // values, arg-max with last-wins ties, GEMV and the DLRM dot interaction.
 #include <cfloat>
 
+#include <cuda_bf16.h>
+
 #include "common.h"
 
 namespace annc {
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(256)
 sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __restrict__ mask,
                            int parts, long long part_stride, long long rows, int slots,
                            int slot_w4, const int* __restrict__ mean_off, float* __restrict__ out,
-                           long long out_stride) {
+                           long long out_stride, int out_bf16) {
   const long long width4 = (long long)slots * slot_w4;
   const long long total = rows * width4;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -295,7 +297,49 @@ sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __rest
         acc.w = __fmul_rn(acc.w, inv);
       }
     }
-    *reinterpret_cast<float4*>(out + r * out_stride + (long long)c4 * 4) = acc;
+    if (out_bf16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + r * out_stride + (long long)c4 * 4) = o;
+    } else {
+      *reinterpret_cast<float4*>(out + r * out_stride + (long long)c4 * 4) = acc;
+    }
+  }
+}
+
+// ---- synthetic table rows from a counter-based hash ---------------------------------
+// value(seed, table, row, col) in [-0.05, 0.05): splitmix64 of the counter, top 24 bits scaled
+// with one fp32 multiply and one fp32 subtract (no fused multiply-add), so a numpy restatement
+// of the same integer and fp32 steps reproduces every element bit for bit and a table too
+// large for host memory can still be checked row by row.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__global__ void __launch_bounds__(256)
+synth_fill_rows_kernel(float* __restrict__ table, long long local_rows, int dim4,
+                       unsigned long long seed, unsigned long long table_id,
+                       unsigned long long first_row, unsigned long long row_step) {
+  const long long total = local_rows * dim4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const unsigned long long base = seed ^ (table_id * 0x9E3779B97F4A7C15ull);
+  const float scale = 0.1f * 5.9604644775390625e-8f;  // 0.1f * 2^-24, exact
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long i = e / dim4;
+    const int c0 = (int)(e - i * dim4) * 4;
+    const unsigned long long row = first_row + (unsigned long long)i * row_step;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned long long h = splitmix64(base + row * 0xD1B54A32D192ED03ull +
+                                              (unsigned long long)(c0 + j) * 0x8CB92BA72F3D8DD7ull);
+      v[j] = __fsub_rn(__fmul_rn((float)(unsigned)(h >> 40), scale), 0.05f);
+    }
+    *reinterpret_cast<float4*>(table + e * 4) = make_float4(v[0], v[1], v[2], v[3]);
   }
 }
 
@@ -396,8 +440,8 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
 
 int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
-                                 const int32_t* mean_offsets, float* out, int64_t out_stride,
-                                 void* stream) {
+                                 const int32_t* mean_offsets, void* out, int64_t out_stride,
+                                 int out_bf16, void* stream) {
   ANNC_REQUIRE(src && out && mask && parts >= 1 && parts <= 32 && slots >= 1,
                ANNC_ERR_INVALID_ARGUMENT, "null or bad argument");
   ANNC_REQUIRE((slot_width & 3) == 0 && slot_width > 0 && (out_stride & 3) == 0 &&
@@ -408,7 +452,21 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
   long long g = (rows * slots * (slot_width / 4) + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
   sum_partials_masked_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), mean_offsets, out, out_stride);
+      src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), mean_offsets,
+      static_cast<float*>(out), out_stride, out_bf16 ? 1 : 0);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_synth_fill_rows_dev(float* table, int64_t local_rows, int64_t dim, uint64_t seed,
+                             int64_t table_id, int64_t first_row, int64_t row_step, void* stream) {
+  ANNC_REQUIRE(table && local_rows >= 0 && dim >= 4 && (dim & 3) == 0 && first_row >= 0 && row_step >= 1 &&
+                   (reinterpret_cast<uintptr_t>(table) & 15) == 0,
+               ANNC_ERR_INVALID_ARGUMENT, "synth fill: bad arguments");
+  if (local_rows == 0) return ANNC_OK;
+  synth_fill_rows_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      table, local_rows, (int)(dim / 4), seed, (unsigned long long)table_id,
+      (unsigned long long)first_row, (unsigned long long)row_step);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

@@ -233,12 +233,12 @@ class OwnerMask:
 
 def sum_partials_masked(src_ptr: int, mask: torch.Tensor, parts: int, part_stride: int, rows: int,
                         slots: int, slot_width: int, out_ptr: int, out_stride: int,
-                        mean_offsets_ptr: Optional[int] = None) -> None:
+                        mean_offsets_ptr: Optional[int] = None, out_bf16: bool = False) -> None:
     check(lib.annc_sum_partials_masked_dev(C.c_void_p(src_ptr), C.c_void_p(mask.data_ptr()),
                                            C.c_int(parts), C.c_int64(part_stride), C.c_int64(rows),
                                            C.c_int(slots), C.c_int64(slot_width),
                                            C.c_void_p(mean_offsets_ptr), C.c_void_p(out_ptr),
-                                           C.c_int64(out_stride), _stream()))
+                                           C.c_int64(out_stride), C.c_int(int(out_bf16)), _stream()))
 
 
 class BagPartition:

@@ -81,6 +81,109 @@ class ShardPlan:
         return int(sum(rc[:s]) + self.nnz[s, mine[:j]].sum())
 
 
+class RowShardedBags:
+    """Embedding bags over row-sharded tables, one process per GPU of one node, with the
+    lookups split at their source (see the module docstring, mode `row`).
+
+    Per step: prefetch(i) runs the prepass and the partition of input set i and starts the
+    barrier that tells the peers their slices are ready; run(i, out) pulls this rank's slices,
+    pools them with the bag kernel storing into the owners' receive buffers, waits for every
+    rank's kernel, and adds the parts of this rank's batch in rank order into `out`
+    (f32, or bf16 with out_bf16) as [batch, tables, dim] rows of `out_stride` elements.
+    The receive buffers alternate between steps, so a peer may start storing step i + 1 while
+    this rank still adds step i; positions and local rows are single-buffered because every
+    peer has pulled them before it joins the step's second barrier."""
+
+    def __init__(self, world: int, rank: int, device, local_tables, local_rows, table_rows, batch: int,
+                 dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2):
+        import torch
+        import torch.distributed as dist
+
+        from . import device as dev
+        self.dist, self.dev, self.torch = dist, dev, torch
+        self.world, self.rank, self.device = world, rank, device
+        T, B, D = len(local_tables), batch, dim
+        self.T, self.B, self.D, self.combiner = T, B, D, combiner
+        TB = T * B
+        nnz_all = np.asarray(nnz_all, np.int64).reshape(world, T)
+        L = (max(1, int(nnz_all.sum(axis=1).max())) + 3) // 4 * 4  # rows of rows_in stay 16-byte aligned
+        self.sets = []
+        for st in id_sets:
+            self.sets.append(dict(prepass=dev.BagPrepass(st["segs"], B), ids=st["ids"]))
+        wsb = self.sets[0]["prepass"].ws_bytes
+        self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=device)
+        self.part_bytes = part_bytes = B * T * D * 4
+        up256 = lambda n: (n + 255) // 256 * 256
+        off_pos = 2 * world * part_bytes          # after the two receive buffers [world, B, T, D]
+        off_rows = off_pos + up256((world * TB + 1) * 4)
+        self.peer = dev.PeerBuffers(off_rows + up256(L * 4), world, rank)
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        pos_of = lambda q: self.peer.ptrs[q] + off_pos
+        rows_of = lambda q: self.peer.ptrs[q] + off_rows
+        off_ptr = lambda t: self.off_ws.data_ptr() + 512 + t * (B + 1) * 4
+        my_nnz = nnz_all[rank]
+        for st in self.sets:
+            st["partition"] = dev.BagPartition(
+                [(st["ids"][t].data_ptr(), int(my_nnz[t]), int(table_rows[t]), off_ptr(t)) for t in range(T)],
+                B, world, pos_of(rank), rows_of(rank), device, id_kind=id_kind)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.pos_in = torch.zeros((world, TB + 1), **i32)
+        self.rows_in = torch.zeros((world, L), **i32)
+        srcs = [q for q in range(world) if q != rank]
+        self.pull = dev.BagPull([pos_of(q) for q in srcs], [rows_of(q) for q in srcs], rank, TB,
+                                [self.pos_in[q].data_ptr() for q in srcs],
+                                [self.rows_in[q].data_ptr() for q in srcs]) if srcs else None
+        self.launches = []
+        for buf in range(2):
+            entries = []
+            for s in range(world):
+                if s == rank:  # own lookups are read in place
+                    ids_ptr, pos_ptr = rows_of(rank), pos_of(rank) + rank * TB * 4
+                else:
+                    ids_ptr, pos_ptr = self.rows_in[s].data_ptr(), self.pos_in[s].data_ptr()
+                for t in range(T):
+                    entries.append((local_tables[t].data_ptr(), int(local_rows[t]), 1, ids_ptr, None, L,
+                                    self.peer.ptrs[s] + (buf * world + rank) * part_bytes + t * D * 4,
+                                    pos_ptr + t * B * 4))
+            self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, device, id_kind=0,
+                                               shard_count=1, shard_rank=0, exchange=True))
+        self.step = 0
+        self.launches_per_step = 2 * ((len(entries) + 55) // 56) + 8
+        self.exchange_bytes = (world - 1) * (part_bytes + TB * 4) + L * 4
+        self._work = None
+        self._partition = None
+
+    def prefetch(self, set_index: int) -> None:
+        st = self.sets[set_index]
+        st["prepass"].run(self.off_ws)
+        self._partition = st["partition"]
+        self._partition.run()
+        self._work = self.dist.all_reduce(self.flag, async_op=True)  # every rank has split its lookups
+
+    def run(self, set_index: int, out_ptr: int, out_stride: int, out_bf16: bool = False) -> None:
+        if self._work is None:
+            self.prefetch(set_index)
+        self._work.wait()
+        self._work = None
+        buf = self.step % 2
+        self.step += 1
+        if self.pull is not None:
+            self.pull.run()              # my slices of the peers' positions and local rows
+        self.launches[buf].run()         # partial sums land in their owners' memory
+        self.dist.all_reduce(self.flag)  # every rank's bag kernel has finished
+        self.dev.sum_partials_masked(
+            self.peer.local + buf * self.world * self.part_bytes, self._partition.mask, self.world,
+            self.B * self.T * self.D, self.B, self.T, self.D, out_ptr, out_stride,
+            mean_offsets_ptr=(self.off_ws.data_ptr() + 512) if self.combiner == 1 else None,
+            out_bf16=out_bf16)
+
+    def error_bits(self) -> int:
+        return self.launches[0].error_bits() | self.launches[1].error_bits()
+
+    def close(self) -> None:
+        self.peer.close()
+
+
 class ShardedDlrmPipeline:
     """Built lazily to keep torch out of ShardPlan's import path."""
 
@@ -200,57 +303,15 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             self.exchange_bytes = (sum(sc) - sc[rank]) * 8 + (T - To) * (B + 1) * 4 + (T - To) * B * D * 4
 
         def _setup_row_partitioned(self, m, plan) -> None:
-            """Row sharding with the ids split at their source.  Each rank resolves its own
-            lookups to (owner, local row), the owners pull their slices through peer-mapped
-            pointers, pool them, and store the partial sums into the source's receive buffer."""
             emb = m.emb
-            T, B, D = self.T, self.batch, self.dim
-            TB = T * B
             self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
-            L = max(1, plan.gathered_len())
-            for st in self.sets:
-                st["prepass"] = dev.BagPrepass(st["segs"], B)
-            wsb = self.sets[0]["prepass"].ws_bytes
-            self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
-            part_bytes = B * T * D * 4
-            up256 = lambda n: (n + 255) // 256 * 256
-            off_pos = 2 * world * part_bytes          # after the two receive buffers [world, B, T, D]
-            off_rows = off_pos + up256((world * TB + 1) * 4)
-            self.peer = dev.PeerBuffers(off_rows + up256(L * 4), world, rank)
-            self.flag = torch.zeros(1, dtype=torch.float32, device=self.device)
-            pos_of = lambda q: self.peer.ptrs[q] + off_pos
-            rows_of = lambda q: self.peer.ptrs[q] + off_rows
-            off_ptr = lambda t: self.off_ws.data_ptr() + 512 + t * (B + 1) * 4
-            for st in self.sets:
-                st["partition"] = dev.BagPartition(
-                    [(st["ids"][t].data_ptr(), self.nnz[t], plan.table_rows[t], off_ptr(t)) for t in range(T)],
-                    B, world, pos_of(rank), rows_of(rank), self.device)
-            i32 = dict(dtype=torch.int32, device=self.device)
-            self.pos_in = torch.zeros((world, TB + 1), **i32)
-            self.rows_in = torch.zeros((world, L), **i32)
-            srcs = [q for q in range(world) if q != rank]
-            self.pull = dev.BagPull([pos_of(q) for q in srcs], [rows_of(q) for q in srcs], rank, TB,
-                                    [self.pos_in[q].data_ptr() for q in srcs],
-                                    [self.rows_in[q].data_ptr() for q in srcs]) if srcs else None
-            self.launches = []
-            for buf in range(2):
-                entries = []
-                for s in range(world):
-                    if s == rank:  # own lookups are read in place
-                        ids_ptr, pos_ptr = rows_of(rank), pos_of(rank) + rank * TB * 4
-                    else:
-                        ids_ptr, pos_ptr = self.rows_in[s].data_ptr(), self.pos_in[s].data_ptr()
-                    for t in range(T):
-                        entries.append((self.tables[t].data_ptr(), plan.local_rows(t), 1, ids_ptr, None, L,
-                                        self.peer.ptrs[s] + (buf * world + rank) * part_bytes + t * D * 4,
-                                        pos_ptr + t * B * 4))
-                self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device, id_kind=0,
-                                                   shard_count=1, shard_rank=0, exchange=True))
-            self.launch = self.launches[0]
-            self._row_step = 0
-            self.embed_launches = 2 * ((len(entries) + 55) // 56) + 8
-            self.exchange_bytes = (world - 1) * (B * T * D * 4 + TB * 4) + L * 4
-            self._works = None
+            self.rowbags = RowShardedBags(
+                world, rank, self.device, self.tables, [plan.local_rows(t) for t in range(self.T)],
+                plan.table_rows, self.batch, self.dim, plan.nnz,
+                [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=0)
+            self.peer = self.rowbags.peer
+            self.embed_launches = self.rowbags.launches_per_step
+            self.exchange_bytes = self.rowbags.exchange_bytes
 
         def embed(self) -> None:
             plan = self.shard
@@ -258,21 +319,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "replica":
                 return DlrmPipeline.embed(self)
             if mode == "row":
-                if self._works is None:
-                    self.embed_prefetch()
-                for w in self._works:
-                    w.wait()                    # every rank has split its lookups
-                self._works = None
-                buf = self._row_step % 2
-                self._row_step += 1
-                if self.pull is not None:
-                    self.pull.run()             # my slices of the peers' positions and local rows
-                self.launch = self.launches[buf]
-                self.launch.run()               # partial sums land in their owners' memory
-                dist.all_reduce(self.flag)      # every rank's bag kernel has finished
-                dev.sum_partials_masked(self.peer.local + buf * world * B * T * D * 4,
-                                        self._partition.mask, world, B * T * D, B, T, D,
-                                        self.z.data_ptr() + D * 4, F * D)
+                self.rowbags.run(self.cur, self.z.data_ptr() + D * 4, F * D)
                 return
             if mode in ("row_gather", "row_nccl"):
                 if self._works is None:
@@ -318,10 +365,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             """Row mode: starts the gathers of ids and bag offsets; the bottom MLP runs
             while they are in flight."""
             if mode == "row":
-                self.sets[self.cur]["prepass"].run(self.off_ws)
-                self._partition = self.sets[self.cur]["partition"]
-                self._partition.run()
-                self._works = [dist.all_reduce(self.flag, async_op=True)]
+                self.rowbags.prefetch(self.cur)
                 return
             if mode not in ("row_gather", "row_nccl"):
                 return
@@ -337,7 +381,9 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def embed_error_bits(self) -> int:
             if mode == "replica":
                 return DlrmPipeline.embed_error_bits(self)
-            if mode in ("row", "row_gather"):
+            if mode == "row":
+                return self.rowbags.error_bits()
+            if mode == "row_gather":
                 return self.launches[0].error_bits() | self.launches[1].error_bits()
             return self.launch.error_bits() if self.launch is not None else 0
 

@@ -171,3 +171,60 @@ def dlrm_flops_per_sample(m: DlrmModel) -> int:
         fl += 2 * w.shape[0] * w.shape[1]
     fl += 2 * f * f * m.emb.dim
     return fl
+
+
+# ---------------------------------------------------------------- hashed tables (large recsys)
+
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64(z: np.ndarray) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        z = z + np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return z ^ (z >> np.uint64(31))
+
+
+def hashed_table_rows(seed: int, table_id: int, rows: np.ndarray, dim: int) -> np.ndarray:
+    """f32[len(rows), dim]: the values annc_synth_fill_rows_dev writes for these global rows
+    of table `table_id`, bit for bit (same integer steps, one fp32 multiply, one subtract)."""
+    rows = np.asarray(rows, dtype=np.uint64).reshape(-1, 1)
+    cols = np.arange(dim, dtype=np.uint64).reshape(1, -1)
+    with np.errstate(over="ignore"):
+        base = np.uint64(seed & _M64) ^ np.uint64((table_id * 0x9E3779B97F4A7C15) & _M64)
+        ctr = base + rows * np.uint64(0xD1B54A32D192ED03) + cols * np.uint64(0x8CB92BA72F3D8DD7)
+    u = (_splitmix64(ctr) >> np.uint64(40)).astype(np.float32)
+    scale = np.float32(0.1) * np.float32(2.0 ** -24)
+    return u * scale - np.float32(0.05)
+
+
+@dataclass
+class RecsysModel:
+    """Large row-sharded recsys configuration: `tables` hashed tables of `rows` x `dim`, mean
+    pooling, concat -> MLP (bias + ReLU, last layer sigmoid).  Weights fp32 [fan_in, fan_out]."""
+    seed: int
+    tables: int
+    rows: int
+    dim: int
+    batch: int
+    bags: List[BagInputs]
+    mlp: List[Tuple[np.ndarray, np.ndarray]]
+
+    @property
+    def nnz(self) -> int:
+        return int(sum(b.raw_ids.shape[0] for b in self.bags))
+
+
+def recsys_model(seed: int = 0, tables: int = 64, rows: int = 20_000_000, dim: int = 128,
+                 batch: int = 16384, max_bag: int = 50, zipf_a: float = 1.2,
+                 hidden=(1024, 512, 1), input_seed: int | None = None, threads: int = 8) -> RecsysModel:
+    """`batch` is this rank's share of the global batch; ranks pass their own input_seed."""
+    root = np.random.default_rng(seed)
+    r_mlp, r_in = root.spawn(2)
+    sizes = (tables * dim,) + tuple(hidden)
+    mlp = _mlp(r_mlp.spawn(2 * len(hidden)), sizes)
+    bag_rngs = (r_in if input_seed is None else np.random.default_rng(input_seed)).spawn(tables)
+    with cf.ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
+        bags = list(ex.map(lambda g: _bag_inputs(g, batch, max_bag, zipf_a), bag_rngs))
+    return RecsysModel(seed, tables, rows, dim, batch, bags, mlp)

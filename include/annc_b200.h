@@ -275,11 +275,13 @@ int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables /* host array */,
  * mask[slot * rows + r]; part p holds f32[rows, slots, slot_width] at src + p * part_stride
  * floats; zero when no bit is set.  Parts whose bit is clear are not read.  With
  * mean_offsets (i32[slots][rows + 1], the bag offsets of the prepass) the sum is multiplied by
- * 1.0f / len(bag), the reference's mean (embedding_fused_sparse_segment_reduce.cc:112-130). */
+ * 1.0f / len(bag), the reference's mean (embedding_fused_sparse_segment_reduce.cc:112-130).
+ * out is f32, or bf16 when out_bf16 != 0 (out_stride in elements of that type): the input of
+ * a BF16 MLP is then produced here, without a separate cast pass. */
 int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
-                                 const int32_t* mean_offsets, float* out, int64_t out_stride,
-                                 void* stream);
+                                 const int32_t* mean_offsets, void* out, int64_t out_stride,
+                                 int out_bf16, void* stream);
 
 /* Row sharding with the ids partitioned at their source (the exchange the multi-GPU pipeline
  * uses).  The rank that owns a batch splits the lookups of every bag by owner rank
@@ -425,6 +427,14 @@ int annc_cast_bf16_dev(const float* src, void* dst_bf16, int64_t n, void* stream
 /* Weight for the BF16 route: fp32 B[K,N] (row pitch ldb) -> bf16 [N,K], converted once. */
 int annc_bf16_weight_dev(const float* b_kn, int64_t ldb, void* b_nk_bf16, int64_t k, int64_t n,
                          void* stream);
+
+/* Benchmark utility: fills table[i, c] (f32[local_rows, dim], dim % 4 == 0) with the value a
+ * counter-based hash gives for (seed, table_id, row = first_row + i * row_step, c), uniform in
+ * [-0.05, 0.05).  Used for tables too large to generate on the host (the 655 GB row-sharded
+ * configuration): each rank fills its own shard (first_row = rank, row_step = ranks) and the
+ * CPU oracle regenerates any row with the same integer steps (annc_b200/synth.py). */
+int annc_synth_fill_rows_dev(float* table, int64_t local_rows, int64_t dim, uint64_t seed,
+                             int64_t table_id, int64_t first_row, int64_t row_step, void* stream);
 
 /* kn4 <-> [K,N] conversion on the device (layout of python/annc/optimize/data_pack.py,
  * vector 12, tiles 352 x 128, python/annc/optimize/constant_folding.py:77-88). */
