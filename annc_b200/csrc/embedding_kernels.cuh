@@ -12,7 +12,8 @@
 namespace annc {
 namespace emb {
 
-constexpr int kMaxTables = 56;          // tables per grouped launch (keeps BagParams under 4 KB)
+constexpr int kMaxTables = 120;         // tables per grouped launch: BagParams is 7.7 KB of the 32 KB
+                                        // parameter space, the per-table marks fit the 512-byte header
 constexpr int kErrRow = 1;              // row index outside its table
 constexpr int kErrSegment = 2;          // segment id outside [0, batch)
 
@@ -36,7 +37,7 @@ struct BagTableDev {
   int rows;                  // (local) table rows and lookups: both below 2^31
   int nnz;
 };
-static_assert(sizeof(BagTableDev) == 64, "BagParams must stay under the 4 KB parameter space");
+static_assert(sizeof(BagTableDev) == 64, "BagParams size is budgeted on 64-byte table entries");
 
 struct BagParams {
   BagTableDev t[kMaxTables];

@@ -148,7 +148,7 @@ class RowShardedBags:
             self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, device, id_kind=0,
                                                shard_count=1, shard_rank=0, exchange=True))
         self.step = 0
-        self.launches_per_step = 2 * ((len(entries) + 55) // 56) + 8
+        self.launches_per_step = 2 * ((len(entries) + 119) // 120) + 8
         self.exchange_bytes = (world - 1) * (part_bytes + TB * 4) + L * 4
         self._work = None
         self._partition = None
@@ -267,7 +267,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                             B, world, self.device)
                 self.launch = self.launches[0]
                 self._row_step = 0
-                self.embed_launches = 2 * ((len(entries) + 55) // 56) + 2
+                self.embed_launches = 2 * ((len(entries) + 119) // 120) + 2
                 self.exchange_bytes = (world - 1) * (B * T * D * 4 + L * 8 + wsb)
                 self._works = None
                 return
@@ -299,7 +299,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                                     self.pooled.data_ptr() + ((s * B) * To + j) * D * 4,
                                     self.off_r.data_ptr() + ((s * To + j) * (B + 1)) * 4))
             self.launch = dev.BagLaunch(entries, D, B, 2, max(To, 1) * D, self.device) if entries else None
-            self.embed_launches = 3 * ((len(entries) + 63) // 64) + world
+            self.embed_launches = 3 * ((len(entries) + 119) // 120) + world
             self.exchange_bytes = (sum(sc) - sc[rank]) * 8 + (T - To) * (B + 1) * 4 + (T - To) * B * D * 4
 
         def _setup_row_partitioned(self, m, plan) -> None:
