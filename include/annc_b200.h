@@ -90,6 +90,21 @@ void* annc_lookup_custom_call(const char* target_name);
  * rhs_is_parameter selects the layout_matmul matcher (gemm_rewriter.cc:13-56). */
 const char* annc_select_gemm_target(int pattern, int rhs_is_parameter);
 
+/* KERNEL_MAP_FILE of the kernel selector (README_kernel_selector.md:20-62; parser and lookup
+ * of annc/service/cpu/xla/kernel_selector_ops_rewriter.cc:50-263): lines
+ * `[gemm](m,n,k) -> symbol` with numbers, `*` and ranges `a:b` / `a:*`; kernels gemv (2 sizes),
+ * gemm (3), batch3d (4), batch4d (5), argmax (3).  Load replaces the current table (path NULL =
+ * the KERNEL_MAP_FILE variable); bad_lines (may be NULL) counts the lines the reference would
+ * report and skip.  Lookup returns the symbol of the first matching entry in the reference's
+ * order (valid until the thread's next lookup) or NULL; resolve returns that symbol's address
+ * in this library (NULL if it is not one of ours). */
+int annc_kernel_map_load(const char* path, int* bad_lines);
+int annc_kernel_map_load_text(const char* text, int* bad_lines);
+int annc_kernel_map_size(void);
+void annc_kernel_map_clear(void);
+const char* annc_kernel_map_lookup(const char* kernel, const int* sizes, int num_sizes);
+void* annc_kernel_map_resolve(const char* kernel, const int* sizes, int num_sizes);
+
 /* ---------------------------------------------------------------- tensors */
 
 enum { ANNC_F32 = 1, ANNC_I32 = 3, ANNC_I64 = 9, ANNC_BOOL = 10, ANNC_U64 = 23 };

@@ -533,3 +533,75 @@ def sparse_select(a, b, greater, equal1, equal2):
     r1 = np.where(b == equal1, np.float32(1), g)
     r2 = np.where(b == equal2, np.float32(1), r1).astype(np.float32)
     return a.astype(np.float32).reshape(-1, 1), r2.reshape(-1, 1), np.stack([r2, np.ones_like(r2)], 1)
+
+
+# ---------------------------------------------------------------- KERNEL_MAP_FILE
+# Restatement of the kernel selector's map parser and lookup
+# (annc/service/cpu/xla/kernel_selector_ops_rewriter.cc:50-104 IntervalMap, :124-195 parseInt /
+# parseRange / parseLine, :201-259 fill_map_from_file).
+
+_KMAP_TYPES = {"gemv": (0, 2), "gemm": (1, 3), "batch3d": (2, 4), "batch4d": (3, 5), "argmax": (4, 3)}
+_KMAP_ANY = (0, 2 ** 31 - 1)
+
+
+def kernel_map_parse(text: str):
+    """Returns (entries, bad_lines); entries is a dict {(type_index, ranges): symbol}."""
+    import re
+    elem = r"(?:\d+|\*|\d+:(?:\d+|\*))"
+    pat = re.compile(r"^\[(.+)\]\(((?:" + elem + r",)*" + elem + r")\)->(.+)$", re.S)
+    entries, bad = {}, 0
+    for line in text.split("\n")[:-1] if text.endswith("\n") else text.split("\n"):
+        if line.endswith("\r"):
+            line = line[:-1]
+        t = "".join(ch for ch in line if ch not in " \t\n\v\f\r")
+        m = pat.match(t)
+        if not m:
+            bad += 1
+            continue
+
+        def num(s):
+            if s == "*":
+                return _KMAP_ANY[1]
+            v = int(s)
+            return v if v <= _KMAP_ANY[1] else -1
+
+        ranges, ok = [], True
+        for tok in m.group(2).split(","):
+            if tok == "*":
+                r = _KMAP_ANY
+            elif ":" in tok:
+                a, b = tok.split(":")
+                r = (num(a), num(b))
+            else:
+                r = (num(tok), num(tok))
+            if r[0] == -1 or r[1] == -1:
+                ok = False
+                break
+            ranges.append(r)
+        if not ok:
+            bad += 1
+            continue
+        if m.group(1) not in _KMAP_TYPES:
+            bad += 1
+            break
+        ty, rank = _KMAP_TYPES[m.group(1)]
+        if len(ranges) == 1 and ranges[0] == _KMAP_ANY:
+            ranges = [_KMAP_ANY] * rank
+        if len(ranges) != rank:
+            bad += 1
+            continue
+        entries[(ty, tuple(ranges))] = m.group(3)
+    return entries, bad
+
+
+def kernel_map_lookup(entries, kernel: str, sizes):
+    """First entry, in std::map key order, whose ranges contain the sizes; None otherwise."""
+    if kernel not in _KMAP_TYPES:
+        return None
+    ty = _KMAP_TYPES[kernel][0]
+    for key in sorted(entries):
+        if key[0] != ty or len(key[1]) != len(sizes):
+            continue
+        if all(lo <= s <= hi for s, (lo, hi) in zip(sizes, key[1])):
+            return entries[key]
+    return None

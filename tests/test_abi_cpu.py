@@ -132,3 +132,67 @@ def test_no_gpu_means_loud_failure(annc):
         ops.kp_fused_sparse_dynamic_stitch(np.array([0, 1], np.int64),
                                            [np.ones((2, 2), np.float32), np.ones((2, 2), np.float32)])
     assert e.value.code == 100  # ANNC_ERR_CUDA: no fallback
+
+
+# ---------------------------------------------------------------- KERNEL_MAP_FILE
+
+KMAP_SAMPLE = "(6656,8,8) -> __xla_cpu_runtime_KernelSelectorGEMM\n"  # the reference's own gemm_map.txt line: no [kernel], rejected
+
+
+def _kmap_lookup(annc, kernel, sizes):
+    import ctypes as C
+    annc.lib.annc_kernel_map_lookup.restype = C.c_char_p
+    arr = (C.c_int * len(sizes))(*sizes)
+    r = annc.lib.annc_kernel_map_lookup(kernel.encode(), arr, len(sizes))
+    return r.decode() if r else None
+
+
+def test_kernel_map_matches_reference_rules(annc, tmp_path):
+    import ctypes as C
+    text = ("[gemm](6656, 8, 8) -> __xla_cpu_runtime_KernelSelectorGEMMSequential\r\n"
+            "[gemm](128:512, 1024, 416:*) -> __xla_cpu_runtime_KernelSelectorGEMMParallel\n"
+            "[gemv](*) -> __xla_cpu_runtime_KernelSelectorGEMV\n"
+            "[batch3d](512,26,4,4:26) -> __xla_cpu_runtime_KernelSelectorBatch3DMLIR\n"
+            "[batch3d](1,2,3) -> wrong_rank\n"
+            "[argmax] (1:*, *, 5) -> __xla_cpu_runtime_ArgMax3DParallel\n"
+            "gemm(1,2,3) -> no_brackets\n"
+            "[gemm](99999999999,1,1) -> overflow\n"
+            + KMAP_SAMPLE +
+            "[conv](1,2) -> unknown_kernel_stops_the_load\n"
+            "[gemm](1,1,1) -> never_read\n")
+    want, want_bad = oracle.kernel_map_parse(text)
+    bad = C.c_int(-1)
+    assert annc.lib.annc_kernel_map_load_text(text.encode(), C.byref(bad)) == 0
+    assert bad.value == want_bad == 5
+    assert annc.lib.annc_kernel_map_size() == len(want) == 5
+    probes = [("gemm", [6656, 8, 8]), ("gemm", [128, 1024, 416]), ("gemm", [512, 1024, 9999]),
+              ("gemm", [513, 1024, 416]), ("gemm", [1, 1, 1]), ("gemv", [7, 12345]), ("gemv", [7]),
+              ("batch3d", [512, 26, 4, 4]), ("batch3d", [512, 26, 4, 27]), ("batch3d", [1, 2, 3]),
+              ("argmax", [1, 0, 5]), ("argmax", [0, 0, 5]), ("batch4d", [1, 1, 1, 1, 1]), ("conv", [1, 2])]
+    for kernel, sizes in probes:
+        assert _kmap_lookup(annc, kernel, sizes) == oracle.kernel_map_lookup(want, kernel, sizes), (kernel, sizes)
+    assert _kmap_lookup(annc, "gemm", [6656, 8, 8]) == "__xla_cpu_runtime_KernelSelectorGEMMSequential"
+    # from a file, through the environment variable's rule, and the fallback-first order of the
+    # reference's map: a `(*)` entry sorts before every specific entry and shadows it
+    f = tmp_path / "map.txt"
+    f.write_text("[gemm](6656,8,8) -> specific\n[gemm](*) -> fallback\n")
+    assert annc.lib.annc_kernel_map_load(str(f).encode(), None) == 0
+    w2, _ = oracle.kernel_map_parse(f.read_text())
+    assert _kmap_lookup(annc, "gemm", [6656, 8, 8]) == oracle.kernel_map_lookup(w2, "gemm", [6656, 8, 8]) == "fallback"
+    assert annc.lib.annc_kernel_map_load(b"/nonexistent/map", None) != 0
+    assert annc.lib.annc_kernel_map_size() == 2  # an unreadable file leaves the table as it was
+    annc.lib.annc_kernel_map_clear()
+
+
+def test_kernel_map_resolves_library_symbols(annc):
+    import ctypes as C
+    annc.lib.annc_kernel_map_resolve.restype = C.c_void_p
+    annc.lib.annc_kernel_map_load_text(b"[gemm](*) -> __xla_cpu_runtime_KernelSelectorGEMMSequential\n"
+                                       b"[gemv](*) -> not_a_symbol_of_this_library\n", None)
+    arr = (C.c_int * 3)(128, 256, 512)
+    addr = annc.lib.annc_kernel_map_resolve(b"gemm", arr, 3)
+    direct = C.cast(annc.lib.__xla_cpu_runtime_KernelSelectorGEMMSequential, C.c_void_p).value
+    assert addr == direct
+    arr2 = (C.c_int * 2)(1, 2)
+    assert annc.lib.annc_kernel_map_resolve(b"gemv", arr2, 2) is None
+    annc.lib.annc_kernel_map_clear()
