@@ -9,11 +9,13 @@
 // Rows R..127 of a stage are never written; whatever they hold only reaches accumulator
 // rows and columns that are not read.
 //
-// Persistent CTAs (one per SM): warp 0 TMA producer over a 4-stage ring, warp 1 MMA
-// issuer with two TMEM accumulators in ping-pong, warps 2-5 epilogue: tcgen05.ld of the
-// needed column chunks into a padded shared-memory copy of the accumulator, then the
-// four warps together write the tile's output rows contiguously (row 0 of every sample
-// comes from global memory unrounded, the products are TF32 x TF32 with fp32 sums).
+// Persistent CTAs (one per SM): warp 0 TMA producer over a 2-stage ring, warp 1 MMA
+// issuer with two TMEM accumulators in ping-pong, warps 2-9 two epilogue groups of four
+// warps, group g taking the tiles that use accumulator g: tcgen05.ld of the needed column
+// chunks into the group's padded shared-memory copy of the accumulator, then the group's four
+// warps together write the tile's output rows contiguously (row 0 of every sample comes
+// from global memory unrounded, the products are TF32 x TF32 with fp32 sums).  The epilogue
+// is the longest stage of a tile, so two of them run side by side.
 // The kernel is bound by HBM (F*64*4 bytes read and (64 + F(F-1)/2)*4 written per sample).
 // All mbarrier waits are bounded (tc_ptx.cuh).
 #include <cstring>
@@ -28,14 +30,15 @@ namespace {
 using namespace annc::tc;
 
 constexpr int ID = 64;              // embedding dim
-constexpr int I_STAGES = 4;
+constexpr int I_STAGES = 2;
 constexpr int I_BOX = 128 * 128;    // bytes reserved per 32-float half (128 rows x 128 B)
 constexpr int I_STAGE = 2 * I_BOX;
 constexpr int I_LD = 132;           // padded accumulator row in shared memory (floats)
-constexpr int I_THREADS = 192;
+constexpr int I_THREADS = 320;     // producer, MMA issuer, two epilogue groups of 128
 // Row-0 floats each epilogue thread carries per tile: samples_per_tile * 64 / 128, rounded up
 // to the template instance (2 covers F >= 26, the DLRM case; 32 covers F = 2).
-constexpr size_t I_SMEM = 1024 + (size_t)I_STAGES * I_STAGE + 128 * I_LD * 4 + 1024 + 256;
+constexpr int I_DSM = 128 * I_LD * 4;  // one group's accumulator copy
+constexpr size_t I_SMEM = 1024 + (size_t)I_STAGES * I_STAGE + 2 * I_DSM + 1024 + 256;
 
 __device__ int g_inter_error = 0;
 
@@ -50,8 +53,8 @@ struct InterParams {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void epi_sync() {  // the 128 epilogue threads only
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+__device__ __forceinline__ void epi_sync(int group) {  // the 128 threads of one epilogue group
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
 }
 
 template <int ROW0_PER_THREAD>
@@ -61,16 +64,16 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  float* dsm = reinterpret_cast<float*>(gen + I_STAGES * I_STAGE);
-  uint8_t* pair_i = gen + I_STAGES * I_STAGE + 128 * I_LD * 4;
+  float* dsm_all = reinterpret_cast<float*>(gen + I_STAGES * I_STAGE);
+  uint8_t* pair_i = gen + I_STAGES * I_STAGE + 2 * I_DSM;
   uint8_t* pair_j = pair_i + 512;
-  const uint32_t bars = base + I_STAGES * I_STAGE + 128 * I_LD * 4 + 1024;
+  const uint32_t bars = base + I_STAGES * I_STAGE + 2 * I_DSM + 1024;
   const uint32_t bar_full = bars, bar_empty = bars + 8 * I_STAGES;
   const uint32_t bar_tfull = bars + 16 * I_STAGES, bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + I_STAGES * I_STAGE + 128 * I_LD * 4 +
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + I_STAGES * I_STAGE + 2 * I_DSM +
                                                     1024 + 16 * I_STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_fail = reinterpret_cast<volatile int*>(tmem_slot + 2);  // epilogue warps only
+  volatile int* epi_fail_all = reinterpret_cast<volatile int*>(tmem_slot + 2);  // one word per group
 
   if (*reinterpret_cast<volatile int*>(&g_inter_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,7 +88,8 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       mbar_init(bar_tempty + 8 * b, 4);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
-    *epi_fail = 0;
+    epi_fail_all[0] = 0;
+    epi_fail_all[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int e = threadIdx.x; e < p.tri; e += I_THREADS) {  // pair e -> (i, j), j < i, row-major
@@ -140,7 +144,10 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       }
     }
   } else {
-    const int q = warp & 3, te = threadIdx.x - 64;
+    const int group = (warp - 2) >> 2;                // accumulator and tiles of this group
+    const int q = warp & 3, te = (threadIdx.x - 64) & 127;
+    float* dsm = dsm_all + group * (I_DSM / 4);
+    volatile int* epi_fail = epi_fail_all + group;
     const int row_lo = 32 * q;
     // columns this warp's rows need: the diagonal blocks of the samples they belong to
     int c_lo = 0, c_hi = 0;
@@ -149,9 +156,10 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       c_lo = (row_lo / p.F) * p.F;
       c_hi = (row_hi / p.F + 1) * p.F;
     }
-    long long li = 0;
-    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++li) {
-      const int buf = (int)(li & 1);
+    long long li = group;
+    for (long long t = blockIdx.x + (long long)group * gridDim.x; t < p.tiles;
+         t += 2LL * gridDim.x, li += 2) {
+      const int buf = group;
       const uint32_t tph = (uint32_t)(li >> 1) & 1u;
       const long long b0 = t * p.spt;
       float row0[ROW0_PER_THREAD];
@@ -165,7 +173,7 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * buf, tph, abort_flag,
                                                         &g_inter_error)) != 0;
       if (!ok) *epi_fail = 1;
-      epi_sync();
+      epi_sync(group);
       if (*epi_fail) break;  // written before the barrier by epilogue warps only: same answer for all
       tc_fence_after();
 #pragma unroll 1
@@ -184,7 +192,7 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);  // accumulator may be overwritten
-      epi_sync();
+      epi_sync(group);
       // Output rows of the tile's samples.  Triangle: pair index outer (its (i, j) is read
       // once), sample inner; for one sample consecutive threads write consecutive floats.
       for (int pe = te; pe < p.tri; pe += 128) {
@@ -207,7 +215,7 @@ dot_interaction_tc_kernel(const __grid_constant__ CUtensorMap tmap, InterParams 
         const int s = e / pad, col = ID + p.tri + (e - s * pad);
         if (b0 + s < p.batch) p.out[(b0 + s) * p.out_stride + col] = 0.f;
       }
-      epi_sync();  // dsm is rewritten by the next tile
+      epi_sync(group);  // dsm is rewritten by the next tile
     }
   }
   tc_fence_before();

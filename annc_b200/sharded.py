@@ -81,6 +81,23 @@ class ShardPlan:
         return int(sum(rc[:s]) + self.nnz[s, mine[:j]].sum())
 
 
+def partition_lookups(raw_ids, seg_ids, table_rows: int, batch: int, shards: int):
+    """Host statement of what annc_embed_bag_partition_dev computes for one table (the GPU
+    tests compare the kernel with it; the gloo CPU test runs the exchange protocol on it):
+    bucket = uint64(id) % table_rows, owner = bucket % shards, local row = bucket // shards.
+    Returns counts int64[shards, batch] and, per owner, the int32 local rows in lookup order
+    (segment ids are sorted, so that is bag by bag)."""
+    bucket = (np.asarray(raw_ids).view(np.uint64) % np.uint64(table_rows)).astype(np.int64)
+    owner, local = bucket % shards, bucket // shards
+    counts = np.zeros((shards, batch), np.int64)
+    rows = []
+    for g in range(shards):
+        sel = owner == g
+        np.add.at(counts[g], np.asarray(seg_ids)[sel], 1)
+        rows.append(local[sel].astype(np.int32))
+    return counts, rows
+
+
 class RowShardedBags:
     """Embedding bags over row-sharded tables, one process per GPU of one node, with the
     lookups split at their source (see the module docstring, mode `row`).

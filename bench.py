@@ -373,7 +373,10 @@ def run_gpu(args):
                 "dtype": "tf32" if args.workload == "dlrm" else "bf16", "data": "synthetic",
                 "impl": "annc_b200", "config": workload_config(args, world),
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
-                        "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes},
+                        "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
+                        # the end-to-end step is bound by the host-to-device copy of the ids and
+                        # index matrices (the operands' own format): GB/s this rank's copies reach
+                        "h2d_gbs": pipe.h2d_bytes / (ms_e2e / 1e3) / 1e9},
                 "gpu_launches": pipe.launches_per_step * args.steps,
                 "gemm_kernels": sorted(set(pipe.kernel_names)),
                 "roofline": roofline, "clocks": sampler.summary()}
