@@ -14,8 +14,11 @@
 //   warp 1   allocates tensor memory for the pair; in the leader one thread issues the MMAs
 //            (UMMA 256 x 256 x {8,16}), commits to the "empty" barrier of both CTAs and, after
 //            the last k-step of a tile, to the "accumulator full" barrier of both CTAs
-//   warps 2-5  epilogue: tcgen05.ld of the CTA's 128 accumulator rows, scale / addend / bias /
-//            activation or row softmax, stores; then release the accumulator to the leader
+//   warps 2-9  epilogue, two warps per 32 accumulator rows (128 columns each): tcgen05.ld of a
+//            32 x 32 chunk (the next chunk's load already in flight), transpose through a
+//            swizzled shared-memory tile, then scale / addend / bias / activation and stores
+//            in whole 128-byte lines; or a thread-per-row softmax.  Each warp then releases
+//            the accumulator to the leader
 //
 // The kernel is persistent (one pair per two SMs, tiles taken round robin) and the accumulator
 // is double-buffered in the 512 tensor-memory columns, so the epilogue of tile i runs under
@@ -48,9 +51,11 @@ constexpr int P_A_BYTES = 16384;  // 128 rows x 128 bytes
 constexpr int P_B_BYTES = 16384;  // 128 columns x 128 bytes
 constexpr int P_STAGE = P_A_BYTES + P_B_BYTES;
 constexpr int P_STAGES = 6;
-constexpr int P_THREADS = 192;
+constexpr int P_THREADS = 320;      // producer, MMA issuer, eight epilogue warps
 constexpr int P_TMEM_COLS = 512;
-constexpr size_t P_SMEM = 1024 + (size_t)P_STAGES * P_STAGE + 256;
+constexpr int P_EPI_WARPS = 8;                       // two per TMEM lane quadrant, 128 columns each
+constexpr int P_STG_BYTES = P_EPI_WARPS * 32 * 32 * 4;  // one swizzled 32 x 32 chunk per epilogue warp
+constexpr size_t P_SMEM = 1024 + (size_t)P_STAGES * P_STAGE + 256 + P_STG_BYTES;
 
 struct PairParams {
   int M, N, K;
@@ -77,9 +82,9 @@ __device__ __forceinline__ float act_apply(float v, int act) {
   return v;
 }
 
-// Values of one 32-column chunk of this thread's row before the activation:
-// alpha * acc (+ beta * C) (+ addend) (+ bias).  Columns at or past N come out as -inf-safe
-// zeros; the caller masks them.
+// Per-row form of the epilogue (the softmax needs whole rows in one thread): values of one
+// 32-column chunk of this thread's row before the activation,
+// alpha * acc (+ beta * C) (+ addend) (+ bias).
 __device__ __forceinline__ void chunk_values(const PairParams& p, const uint32_t (&r)[32], float (&v)[32],
                                              long long grow, int col0, long long bz, bool row_ok) {
 #pragma unroll
@@ -100,19 +105,9 @@ __device__ __forceinline__ void chunk_values(const PairParams& p, const uint32_t
   }
   if (p.addend) {
     const float* a = p.addend + bz * p.stride_addend + grow * p.ld_addend + col0;
-    const bool vec = ((p.ld_addend & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0) &&
-                     ((p.stride_addend & 3) == 0) && col0 + 31 < p.N;
-    if (vec) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 x = __ldg(reinterpret_cast<const float4*>(a + j));
-        v[j] += x.x; v[j + 1] += x.y; v[j + 2] += x.z; v[j + 3] += x.w;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) v[j] += __ldg(a + j);
-    }
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) v[j] += __ldg(a + j);
   }
   if (p.bias) {
 #pragma unroll
@@ -121,49 +116,130 @@ __device__ __forceinline__ void chunk_values(const PairParams& p, const uint32_t
   }
 }
 
-__device__ __forceinline__ void chunk_store(const PairParams& p, const float (&v)[32], long long grow,
-                                            int col0, long long bz) {
-  if (p.c_bf16) {
-    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
-    const bool vec = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                     ((p.stride_c & 7) == 0) && col0 + 31 < p.N;
-    if (vec) {
+// Staging tile of one epilogue warp: 32 rows x 32 floats, the 16-byte granule g of row r
+// stored at granule g ^ (r & 7), so that both the row-wise writes (lane = row) and the
+// reads of four rows x 128 bytes are free of bank conflicts beyond the 512 bytes they move.
+__device__ __forceinline__ float* stg_at(float* stg, int row, int granule) {
+  return stg + row * 32 + ((granule ^ (row & 7)) << 2);
+}
+
+// Coalesced half of the epilogue.  The warp has put a 32-row x 32-column chunk into its
+// staging tile (row = TMEM lane); here lane l takes columns 4 (l % 8) .. + 3 of rows l / 8 + 4 i,
+// so one instruction covers four rows with 128 contiguous bytes each: C and the addend are
+// read and C is written in whole lines, all eight loads of a lane in flight together.
+// `finalize` adds beta * C, addend, bias (bias4: this lane's four columns, loaded by the
+// caller before the accumulator was ready) and the activation; the softmax route stages
+// finished values and only stores them.
+__device__ __forceinline__ void chunk_store_staged(const PairParams& p, float* stg, int lane,
+                                                   long long row0, int col0, long long bz, bool finalize,
+                                                   const float (&bias4)[4]) {
+  const int g = lane & 7;
+  const int c = col0 + g * 4;
+  if (c >= p.N) return;
+  const bool full4 = c + 3 < p.N;
+  const bool c_vec = full4 && ((p.ldc & 3) == 0) && ((p.stride_c & 3) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+  const bool a_vec = full4 && ((p.ld_addend & 3) == 0) && ((p.stride_addend & 3) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+  const bool use_beta = finalize && p.beta != 0.f;
+  const bool use_add = finalize && p.addend != nullptr;
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint4 o;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-        o.x = *reinterpret_cast<uint32_t*>(&t0);
-        o.y = *reinterpret_cast<uint32_t*>(&t1);
-        o.z = *reinterpret_cast<uint32_t*>(&t2);
-        o.w = *reinterpret_cast<uint32_t*>(&t3);
-        *reinterpret_cast<uint4*>(c + j) = o;
+  for (int i0 = 0; i0 < 8; i0 += 4) {  // two batches of four rows: four loads of each kind in flight
+  float v[4][4];
+  float4 ld_c[4], ld_a[4];
+#pragma unroll
+  for (int ii = 0; ii < 4; ++ii) {
+    const int i = ii, rl = (lane >> 3) + 4 * (i0 + ii);
+    const long long grow = row0 + rl;
+    const float4 s4 = *reinterpret_cast<const float4*>(stg_at(stg, rl, g));
+    v[i][0] = s4.x; v[i][1] = s4.y; v[i][2] = s4.z; v[i][3] = s4.w;
+    ld_c[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ld_a[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (grow < p.M) {
+      const long long coff = bz * p.stride_c + grow * p.ldc + c;
+      if (use_beta) {
+        if (p.c_bf16) {
+          const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.C) + coff;
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (c + e < p.N) t[e] = __bfloat162float(cp[e]);
+          ld_c[i] = make_float4(t[0], t[1], t[2], t[3]);
+        } else if (c_vec) {
+          ld_c[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.C) + coff);
+        } else {
+          const float* cp = static_cast<const float*>(p.C) + coff;
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (c + e < p.N) t[e] = cp[e];
+          ld_c[i] = make_float4(t[0], t[1], t[2], t[3]);
+        }
+      }
+      if (use_add) {
+        const float* ap = p.addend + bz * p.stride_addend + grow * p.ld_addend + c;
+        if (a_vec) {
+          ld_a[i] = __ldg(reinterpret_cast<const float4*>(ap));
+        } else {
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (c + e < p.N) t[e] = __ldg(ap + e);
+          ld_a[i] = make_float4(t[0], t[1], t[2], t[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < 4; ++ii) {
+    const int i = ii, rl = (lane >> 3) + 4 * (i0 + ii);
+    const long long grow = row0 + rl;
+    if (grow >= p.M) continue;
+    const long long coff = bz * p.stride_c + grow * p.ldc + c;
+    if (finalize) {
+      v[i][0] = act_apply(v[i][0] + p.beta * ld_c[i].x + ld_a[i].x + bias4[0], p.act);
+      v[i][1] = act_apply(v[i][1] + p.beta * ld_c[i].y + ld_a[i].y + bias4[1], p.act);
+      v[i][2] = act_apply(v[i][2] + p.beta * ld_c[i].z + ld_a[i].z + bias4[2], p.act);
+      v[i][3] = act_apply(v[i][3] + p.beta * ld_c[i].w + ld_a[i].w + bias4[3], p.act);
+    }
+    if (p.c_bf16) {
+      __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + coff;
+      if (full4 && ((p.ldc & 3) == 0) && ((p.stride_c & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 7) == 0)) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[i][0], v[i][1]), hi = __floats2bfloat162_rn(v[i][2], v[i][3]);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(cp) = o;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c + e < p.N) cp[e] = __float2bfloat16_rn(v[i][e]);
       }
     } else {
+      float* cp = static_cast<float*>(p.C) + coff;
+      if (c_vec) {
+        *reinterpret_cast<float4*>(cp) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) c[j] = __float2bfloat16_rn(v[j]);
+        for (int e = 0; e < 4; ++e)
+          if (c + e < p.N) cp[e] = v[i][e];
+      }
     }
-    return;
   }
-  float* c = static_cast<float*>(p.C) + bz * p.stride_c + grow * p.ldc + col0;
-  const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                   ((p.stride_c & 3) == 0) && col0 + 31 < p.N;
-  if (vec) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4)
-      *reinterpret_cast<float4*>(c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < p.N) c[j] = v[j];
   }
 }
 
+// Row `lane` of the warp's staging tile <- 32 accumulator values scaled by alpha.
+__device__ __forceinline__ void stage_row(float* stg, int lane, const uint32_t (&r)[32], float alpha) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<float4*>(stg_at(stg, lane, j)) =
+        make_float4(alpha * __uint_as_float(r[4 * j]), alpha * __uint_as_float(r[4 * j + 1]),
+                    alpha * __uint_as_float(r[4 * j + 2]), alpha * __uint_as_float(r[4 * j + 3]));
+}
+
 // DT 0: TF32 (fp32 elements, 32 per 128-byte k-step, UMMA K = 8); DT 1: BF16 (64, K = 16).
-template <int DT>
+template <int DT, bool SOFTMAX>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, PairParams p) {
@@ -177,6 +253,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t bar_tfull = bars + 16 * P_STAGES, bar_tempty = bar_tfull + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + P_STAGES * P_STAGE + 16 * P_STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* staging = reinterpret_cast<float*>(gen_base + P_STAGES * P_STAGE + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -191,7 +268,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);   // one commit
-      mbar_init(bar_tempty + 8 * a, 8);  // four epilogue warps of each CTA
+      mbar_init(bar_tempty + 8 * a, 2 * P_EPI_WARPS);  // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -278,8 +355,10 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     } else {
-      // ---------------- epilogue (both CTAs): warp q owns TMEM lanes 32 q .. 32 q + 31
-      const int q = warp & 3;
+      // ---------------- epilogue (both CTAs): eight warps; warp (q, half) owns TMEM lanes
+      // 32 q .. 32 q + 31 and accumulator columns 128 half .. 128 half + 127 (four chunks of 32)
+      const int q = warp & 3, half = (warp - 2) >> 2;
+      float* stg = staging + (warp - 2) * (32 * 32);
       uint32_t tcount = 0;
       bool ok = true;
       for (long long tile = pair; tile < p.tiles && ok; tile += pairs, ++tcount) {
@@ -287,29 +366,58 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const long long bz = tile / ((long long)p.tiles_m * p.tiles_n);
         const int t2 = (int)(tile - bz * p.tiles_m * p.tiles_n);
         const int tn = t2 / p.tiles_m, tm = t2 - tn * p.tiles_m;
-        const long long grow = (long long)tm * (2 * PM) + rank * PM + q * 32 + lane;
+        const long long row0 = (long long)tm * (2 * PM) + rank * PM + q * 32;  // first row of this warp
+        const long long grow = row0 + lane;
         const bool row_ok = grow < p.M;
-        const int nb = tn * PN;
+        constexpr int WCOLS = PN / (P_EPI_WARPS / 4);  // columns per epilogue warp (128)
+        const int nb = tn * PN + half * WCOLS;  // first column of this warp
+        // Bias of the warp's 128 columns, four per lane, fetched once per tile while the MMAs
+        // still run: a load per chunk would put an L2 round trip on every chunk's critical path.
+        float4 bias_w = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!SOFTMAX && p.bias) {
+          const int c = nb + lane * 4;
+          if (c + 3 < p.N && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+            bias_w = __ldg(reinterpret_cast<const float4*>(p.bias + c));
+          } else {
+            if (c < p.N) bias_w.x = __ldg(p.bias + c);
+            if (c + 1 < p.N) bias_w.y = __ldg(p.bias + c + 1);
+            if (c + 2 < p.N) bias_w.z = __ldg(p.bias + c + 2);
+            if (c + 3 < p.N) bias_w.w = __ldg(p.bias + c + 3);
+          }
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.error_word)) != 0;
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)PN;
-        if (!p.softmax) {
+        if (!SOFTMAX) {
+          // chunk i + 1 is read from tensor memory (into the registers staging has just
+          // freed) while chunk i goes from the staging tile to global memory
+          uint32_t ra[32];
+          const uint32_t tcol = taddr + (uint32_t)(half * WCOLS);
+          if (nb < p.N) tmem_ld32(tcol, ra);
+          // not unrolled: the body is large, and unrolled copies of it thrash the instruction cache
 #pragma unroll 1
-          for (int c0 = 0; c0 < PN && nb + c0 < p.N; c0 += 32) {
-            uint32_t r[32];
-            float v[32];
-            tmem_ld32(taddr + (uint32_t)c0, r);
-            tmem_ld_wait();
-            chunk_values(p, r, v, grow, nb + c0, bz, row_ok);
-            if (row_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = act_apply(v[j], p.act);
-              chunk_store(p, v, grow, nb + c0, bz);
+          for (int i = 0; i < WCOLS / 32; ++i) {
+            const int c0 = nb + 32 * i;
+            if (c0 < p.N) {  // warp-uniform
+              float bias4[4];  // this lane's columns of the chunk, from the lane that fetched them
+              const int src = 8 * i + (lane & 7);
+              bias4[0] = __shfl_sync(0xffffffffu, bias_w.x, src);
+              bias4[1] = __shfl_sync(0xffffffffu, bias_w.y, src);
+              bias4[2] = __shfl_sync(0xffffffffu, bias_w.z, src);
+              bias4[3] = __shfl_sync(0xffffffffu, bias_w.w, src);
+              tmem_ld_wait();
+              stage_row(stg, lane, ra, p.alpha);
+              if (i + 1 < WCOLS / 32 && c0 + 32 < p.N) tmem_ld32(tcol + 32u * (i + 1), ra);
+              __syncwarp();
+              chunk_store_staged(p, stg, lane, row0, c0, bz, true, bias4);
+              __syncwarp();
             }
           }
-        } else {
-          // three passes over the row in tensor memory: max, sum of exp, normalised store
+        } else if (half == 0) {
+          // row softmax: one thread per row over all N <= 256 columns, three passes over the
+          // row in tensor memory: max, sum of exp, normalised store (warps of half 1 idle)
+          const float no_bias[4] = {0.f, 0.f, 0.f, 0.f};
           float mx = -INFINITY, sum = 0.f;
 #pragma unroll 1
           for (int pass = 0; pass < 3; ++pass) {
@@ -330,10 +438,15 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                   if (c0 + j < p.N) sum += expf(v[j] - mx);
-              } else if (row_ok) {
+              } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __fdiv_rn(expf(v[j] - mx), sum);
-                chunk_store(p, v, grow, c0, bz);
+                for (int j = 0; j < 8; ++j)
+                  *reinterpret_cast<float4*>(stg_at(stg, lane, j)) =
+                      make_float4(__fdiv_rn(expf(v[4 * j] - mx), sum), __fdiv_rn(expf(v[4 * j + 1] - mx), sum),
+                                  __fdiv_rn(expf(v[4 * j + 2] - mx), sum), __fdiv_rn(expf(v[4 * j + 3] - mx), sum));
+                __syncwarp();
+                chunk_store_staged(p, stg, lane, row0, c0, bz, false, no_bias);
+                __syncwarp();
               }
             }
           }
@@ -407,7 +520,14 @@ int run_pair(const annc_gemm_desc& d, int math, cudaStream_t s) {
   if (!pair_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 pair gemm: unsupported shape");
   const bool bf16 = math == ANNC_MATH_BF16;
   static int max_pairs[2] = {0, 0};
-  auto kern = bf16 ? gemm_pair_tcgen05_kernel<1> : gemm_pair_tcgen05_kernel<0>;
+  const bool softmax = (d.io_flags & ANNC_IO_SOFTMAX) != 0;
+  auto kern = bf16 ? (softmax ? gemm_pair_tcgen05_kernel<1, true> : gemm_pair_tcgen05_kernel<1, false>)
+                   : (softmax ? gemm_pair_tcgen05_kernel<0, true> : gemm_pair_tcgen05_kernel<0, false>);
+  static bool attr_done[2][2] = {{false, false}, {false, false}};
+  if (!attr_done[bf16][softmax]) {
+    ANNC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM));
+    attr_done[bf16][softmax] = true;
+  }
   if (max_pairs[bf16] == 0) {
     ANNC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM));
     cudaLaunchConfig_t q;

@@ -81,6 +81,10 @@ class DlrmPipeline:
         self.out = self.acts_t[-1]
         self.kernel_names: List[str] = []
         self.launches_per_step = 0
+        # The bottom MLP does not depend on the embeddings: it runs on a second stream beside the
+        # prepass and the bag kernel (which is bound by gather latency, not by bandwidth) and
+        # joins before the interaction.
+        self.side_stream = torch.cuda.Stream(device=device)
         self.embed_launches = 3  # prepass + bag + atomic route
         self._setup_embedding(model)
 
@@ -116,15 +120,19 @@ class DlrmPipeline:
         B, F, D = self.batch, self.F, self.dim
         x = self.dense
         nb = len(self.bottom)
+        main = torch.cuda.current_stream()
+        self.side_stream.wait_stream(main)  # this step's inputs, and the previous step's readers of z
+        with torch.cuda.stream(self.side_stream):
+            for i, (w, b) in enumerate(self.bottom):
+                last = i == nb - 1
+                y = self.z if last else self.acts_b[i]
+                names.append(dev.gemm(x, w, y, m=B, n=w.shape[1], k=w.shape[0], bias=b,
+                                      activation=ACT_RELU, ldc=(F * D if last else None),
+                                      math=self.math))
+                x = y
         self.embed_prefetch()
-        for i, (w, b) in enumerate(self.bottom):
-            last = i == nb - 1
-            y = self.z if last else self.acts_b[i]
-            names.append(dev.gemm(x, w, y, m=B, n=w.shape[1], k=w.shape[0], bias=b,
-                                  activation=ACT_RELU, ldc=(F * D if last else None),
-                                  math=self.math))
-            x = y
         self.embed()
+        main.wait_stream(self.side_stream)
         dev.dot_interaction(self.z, self.inter_buf, self.math)
         x = self.inter_buf
         nt = len(self.top)

@@ -11,6 +11,10 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
+import os
+
+os.environ["ANNC_GEMM_ROUTE"] = "pair"  # read once by the library: this module runs in its own process
+
 import torch
 import annc_b200  # noqa: F401,E402  (no fallback: a missing library fails the collection)
 from annc_b200 import device  # noqa: E402
