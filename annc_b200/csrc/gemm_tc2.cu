@@ -76,6 +76,23 @@ struct PairParams {
   int* error_word;
 };
 
+// Tile order: bands of P_BAND row tiles; inside a band the column tile advances slowest and the
+// row tile fastest, so the ~74 tiles in flight at any time cover about 8 row tiles x 9 column
+// tiles: every A and B panel they stream is shared through L2 by several pairs instead of
+// being fetched from DRAM once per column (or row) tile.
+constexpr int P_BAND = 8;
+__device__ __forceinline__ void tile_coords(const PairParams& p, long long tile, long long* bz, int* tm,
+                                            int* tn) {
+  const long long per_batch = (long long)p.tiles_m * p.tiles_n;
+  *bz = tile / per_batch;
+  const int t2 = (int)(tile - *bz * per_batch);
+  const int band = t2 / (P_BAND * p.tiles_n);
+  const int rem = t2 - band * (P_BAND * p.tiles_n);
+  const int rows = min(P_BAND, p.tiles_m - band * P_BAND);
+  *tn = rem / rows;
+  *tm = band * P_BAND + (rem - *tn * rows);
+}
+
 __device__ __forceinline__ float act_apply(float v, int act) {
   if (act == ANNC_ACT_RELU) return fmaxf(v, 0.0f);
   if (act == ANNC_ACT_SIGMOID) return __fdiv_rn(1.0f, 1.0f + expf(-v));
@@ -288,9 +305,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t kit = 0;
         bool ok = true;
         for (long long tile = pair; tile < p.tiles && ok; tile += pairs) {
-          const long long bz = tile / ((long long)p.tiles_m * p.tiles_n);
-          const int t2 = (int)(tile - bz * p.tiles_m * p.tiles_n);
-          const int tn = t2 / p.tiles_m, tm = t2 - tn * p.tiles_m;
+          long long bz;
+          int tm, tn;
+          tile_coords(p, tile, &bz, &tm, &tn);
           const int m0 = tm * (2 * PM) + (int)rank * PM;
           const int n0 = tn * PN + (int)rank * (PN / 2);
           for (int kt = 0; kt < KT; ++kt, ++kit) {
@@ -363,9 +380,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (long long tile = pair; tile < p.tiles && ok; tile += pairs, ++tcount) {
         const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
-        const long long bz = tile / ((long long)p.tiles_m * p.tiles_n);
-        const int t2 = (int)(tile - bz * p.tiles_m * p.tiles_n);
-        const int tn = t2 / p.tiles_m, tm = t2 - tn * p.tiles_m;
+        long long bz;
+        int tm, tn;
+        tile_coords(p, tile, &bz, &tm, &tn);
         const long long row0 = (long long)tm * (2 * PM) + rank * PM + q * 32;  // first row of this warp
         const long long grow = row0 + lane;
         const bool row_ok = grow < p.M;
