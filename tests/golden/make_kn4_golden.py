@@ -1,7 +1,7 @@
 """Generates tests/golden/kn4_golden.npz by running the reference's own packer.
 
 Run in a container that has the reference tree:
-    python tests/golden/make_kn4_golden.py /root/reference
+    python tests/golden/make_kn4_golden.py <path of the ANNC checkout>
 It loads python/annc/optimize/data_pack.py from that tree as a stand-alone module
 (numpy only) and packs B = arange(K*N) with FormageChange(12).run(kn -> kn4,
 tiles (0,352),(1,128)) exactly as python/annc/optimize/constant_folding.py:77-88
