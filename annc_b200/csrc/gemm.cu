@@ -99,6 +99,25 @@ kn4_unpack_chunks_kernel(const float* __restrict__ src, float* __restrict__ dst,
   }
 }
 
+// kn4 -> [N,K] (the K-major layout the TMA route likes best): a block moves a 32 (k) x 32 (n)
+// tile through shared memory, reading the packed buffer along n and writing rows of k.
+__global__ void __launch_bounds__(256)
+kn4_unpack_transposed_kernel(const float* __restrict__ src, float* __restrict__ dst, long long K,
+                             long long N) {
+  __shared__ float tile[32][33];
+  const long long n0 = (long long)blockIdx.x * 32, k0 = (long long)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const long long k = k0 + r, n = n0 + tx;
+    tile[r][tx] = (k < K && n < N) ? src[kn4::offset(K, N, k, n)] : 0.f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const long long n = n0 + r, k = k0 + tx;
+    if (n < N && k < K) dst[n * K + k] = tile[tx][r];
+  }
+}
+
 __global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                  long long n) {
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -135,6 +154,19 @@ static bool unpack_kn4_into_workspace(const annc_gemm_desc& d, cudaStream_t s, a
   plain->ldb = d.n;
   plain->workspace = nullptr;
   plain->workspace_bytes = 0;
+  // Re-laid as [N,K] the weight takes the K-major TMA route of the CTA-pair kernel (one 16 KB
+  // box per stage), the fastest one; [K,N] is the fallback when K rows would not be 16-byte pitched.
+  if ((d.k & 3) == 0 && (d.k + 31) / 32 <= 65535) {
+    annc_gemm_desc t = *plain;
+    t.trans_b = 1;
+    t.ldb = d.k;
+    if (pair_supported(t, ANNC_MATH_TF32) && use_pair(t, ANNC_MATH_TF32)) {
+      dim3 grid((unsigned)((d.n + 31) / 32), (unsigned)((d.k + 31) / 32));
+      kn4_unpack_transposed_kernel<<<grid, 256, 0, s>>>(d.b, static_cast<float*>(d.workspace), d.k, d.n);
+      *plain = t;
+      return true;
+    }
+  }
   if (!tc_supported(*plain, ANNC_MATH_TF32)) return false;
   dim3 grid((unsigned)((d.n / 4 + 255) / 256), (unsigned)(d.k < 1024 ? d.k : 1024));
   kn4_unpack_chunks_kernel<<<grid, 256, 0, s>>>(d.b, static_cast<float*>(d.workspace), (int)d.k,

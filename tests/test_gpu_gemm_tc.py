@@ -140,3 +140,19 @@ def test_kn4_with_workspace_matches_direct_route():
     assert torch.equal(ws, _dev(w))
     assert torch.equal(c_ws, c_plain)
     assert nerr(c_direct, a @ w) <= TF32_TOL and nerr(c_ws, a @ w) <= TF32_TOL
+
+
+def test_kn4_with_workspace_takes_the_k_major_route_for_long_k():
+    """K >= 1024 and K % 4 == 0: the packed weight is re-laid as [N,K] and the CTA-pair kernel
+    runs its K-major TMA route; the workspace then holds the transposed weight."""
+    m, n, k = 1024, 520, 1032
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+    packed = _dev(oracle.kn4_pack(w))
+    ws = torch.zeros((n, k), device="cuda")
+    c = torch.full((m, n), float("nan"), device="cuda")
+    device.gemm(_dev(a), packed, c, m=m, n=n, k=k, b_format=B_KN4, workspace=ws)
+    assert not device.gemm_timed_out()
+    assert torch.equal(ws, _dev(w).t().contiguous())
+    assert nerr(c, a @ w) <= TF32_TOL
