@@ -75,6 +75,7 @@ def _load() -> C.CDLL:
     lib.annc_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
     lib.annc_peer_buffer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     lib.annc_peer_buffer_close.argtypes = [C.c_void_p]
+    lib.annc_peer_copy_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.annc_peer_buffer_destroy.argtypes = [C.c_void_p]
     lib.annc_embed_bag_owner_mask_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int,
                                                   C.c_void_p, C.c_void_p]

@@ -40,6 +40,13 @@ int annc_peer_buffer_open(const void* handle64, void** dev_ptr) {
   return ANNC_OK;
 }
 
+int annc_peer_copy_dev(void* dst, const void* src, size_t bytes, void* stream) {
+  if (bytes == 0) return ANNC_OK;
+  ANNC_REQUIRE(dst && src, ANNC_ERR_INVALID_ARGUMENT, "null copy argument");
+  ANNC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return ANNC_OK;
+}
+
 int annc_peer_buffer_close(void* dev_ptr) {
   if (dev_ptr) ANNC_CUDA(cudaIpcCloseMemHandle(dev_ptr));
   return ANNC_OK;

@@ -213,6 +213,15 @@ def sum_partials_ptr(src_ptr: int, parts: int, part_stride: int, rows: int, widt
                                     C.c_void_p(out_ptr), C.c_int64(out_stride), _stream()))
 
 
+def peer_copy(dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+    """annc_peer_copy_dev on the current stream (raw pointers: either may be a peer mapping)."""
+    check(lib.annc_peer_copy_dev(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), C.c_size_t(nbytes), _stream()))
+
+
+def cast_bf16_ptr(src_ptr: int, dst_ptr: int, n: int) -> None:
+    check(lib.annc_cast_bf16_dev(C.c_void_p(src_ptr), C.c_void_p(dst_ptr), C.c_int64(n), _stream()))
+
+
 class OwnerMask:
     """annc_embed_bag_owner_mask_dev over fixed id / offset buffers: which ranks hold a part
     of each bag of this rank's batch.  entries: (ids_ptr, nnz, num_buckets, offsets_ptr)."""
@@ -340,7 +349,10 @@ class BagPrepass:
         self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
 
     def run(self, ws: torch.Tensor) -> None:
+        self.run_ptr(ws.data_ptr())
+
+    def run_ptr(self, ws_ptr: int) -> None:
         check(lib.annc_embed_bag_prepass_dev(self.desc, C.c_int(self.n), C.c_int64(self.ncols),
                                              C.c_int32(self.col), C.c_int64(self.batch),
-                                             C.c_void_p(ws.data_ptr()), C.c_size_t(self.ws_bytes),
+                                             C.c_void_p(ws_ptr), C.c_size_t(self.ws_bytes),
                                              _stream()))

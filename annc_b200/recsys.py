@@ -19,26 +19,39 @@ import torch.distributed as dist
 from . import device as dev
 from ._lib import (ACT_RELU, ACT_SIGMOID, IO_A_BF16, IO_B_BF16, IO_C_BF16, MATH_BF16, MATH_FP32, check,
                    lib)
-from .sharded import RowShardedBags
+from .sharded import RowShardedBags, ShardPlan, TableShardedBags
 from .synth import RecsysModel
 
 
 class RecsysPipeline:
-    def __init__(self, model: RecsysModel, device: torch.device, keep_host_inputs: bool = False):
+    def __init__(self, model: RecsysModel, device: torch.device, keep_host_inputs: bool = False,
+                 shard: str = "row"):
+        """shard: "row" (mod rule, partial sums stored into the sample owner's memory) or "table"
+        (whole tables per rank, finished pooled vectors stored into the sample owner's memory)."""
+        assert shard in ("row", "table")
         world, rank = dist.get_world_size(), dist.get_rank()
-        self.world, self.rank, self.device = world, rank, device
+        self.world, self.rank, self.device, self.shard = world, rank, device, shard
         self.model = model
         T, R, D, B = model.tables, model.rows, model.dim, model.batch
         self.T, self.D, self.batch = T, D, B
-        self.local_rows = len(range(rank, R, world))
-        # one allocation for all local shards: [T, local_rows, D]
-        self.table_mem = torch.empty((T, max(self.local_rows, 1), D), dtype=torch.float32, device=device)
         s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        for t in range(T):
-            check(lib.annc_synth_fill_rows_dev(C.c_void_p(self.table_mem[t].data_ptr()),
-                                               C.c_int64(self.local_rows), C.c_int64(D),
-                                               C.c_uint64(model.seed), C.c_int64(t), C.c_int64(rank),
-                                               C.c_int64(world), s))
+        if shard == "row":
+            self.local_rows = len(range(rank, R, world))
+            # one allocation for all local shards: [T, local_rows, D]
+            self.table_mem = torch.empty((T, max(self.local_rows, 1), D), dtype=torch.float32, device=device)
+            for t in range(T):
+                check(lib.annc_synth_fill_rows_dev(C.c_void_p(self.table_mem[t].data_ptr()),
+                                                   C.c_int64(self.local_rows), C.c_int64(D),
+                                                   C.c_uint64(model.seed), C.c_int64(t), C.c_int64(rank),
+                                                   C.c_int64(world), s))
+        else:
+            self.owned = [int(t) for t in np.array_split(np.arange(T), world)[rank]]
+            self.local_rows = R
+            self.table_mem = torch.empty((max(len(self.owned), 1), R, D), dtype=torch.float32, device=device)
+            for j, t in enumerate(self.owned):
+                check(lib.annc_synth_fill_rows_dev(C.c_void_p(self.table_mem[j].data_ptr()), C.c_int64(R),
+                                                   C.c_int64(D), C.c_uint64(model.seed), C.c_int64(t),
+                                                   C.c_int64(0), C.c_int64(1), s))
         up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
         nnz = [int(b.raw_ids.shape[0]) for b in model.bags]
         self.nnz, self.nnz_total = nnz, int(sum(nnz))
@@ -62,9 +75,17 @@ class RecsysPipeline:
         self._step = 0
         nnz_all = [None] * world
         dist.all_gather_object(nnz_all, nnz)
-        self.bags = RowShardedBags(world, rank, device, [self.table_mem[t] for t in range(T)],
-                                   [self.local_rows] * T, [R] * T, B, D, np.array(nnz_all),
-                                   [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=1)
+        if shard == "row":
+            self.bags = RowShardedBags(world, rank, device, [self.table_mem[t] for t in range(T)],
+                                       [self.local_rows] * T, [R] * T, B, D, np.array(nnz_all),
+                                       [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=1)
+        else:
+            plan = ShardPlan("table", world, rank, [R] * T, np.array(nnz_all))
+            assert plan.owned[rank] == self.owned
+            self.bags = TableShardedBags(world, rank, device, plan,
+                                         [self.table_mem[j] for j in range(len(self.owned))], B, D,
+                                         [dict(ids_all=st["ids_all"], segs=st["segs"]) for st in self.sets],
+                                         combiner=1)
         # MLP: bf16 weights [N,K] converted once; the last layer (n = 1) stays fp32
         self.layers = []
         for i, (w, b) in enumerate(model.mlp):
@@ -83,7 +104,11 @@ class RecsysPipeline:
     def forward(self, set_index: int = 0) -> torch.Tensor:
         B = self.batch
         self.bags.prefetch(set_index)
-        self.bags.run(set_index, self.x0.data_ptr(), self.T * self.D, out_bf16=True)
+        if self.shard == "row":
+            self.bags.run(set_index, self.x0.data_ptr(), self.T * self.D, out_bf16=True)
+        else:  # the owners have stored finished fp32 means; one pass makes the MLP's bf16 input
+            pooled = self.bags.run(set_index)
+            dev.cast_bf16_ptr(pooled, self.x0.data_ptr(), B * self.T * self.D)
         x = self.x0
         names = []
         n_layers = len(self.layers)

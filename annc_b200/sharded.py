@@ -201,6 +201,111 @@ class RowShardedBags:
         self.peer.close()
 
 
+class TableShardedBags:
+    """Embedding bags over table-wise sharded tables (contiguous blocks of whole tables per
+    rank), one process per GPU of one node, with the exchange fused into the bag kernel's
+    stores: each owner fetches the raw ids and bag offsets of its tables from every source
+    (device-to-device copies through peer-mapped pointers, sizes known on the host), pools
+    whole bags — so sums keep the reference's order and are bit-exact — and stores every
+    finished pooled vector straight into the source rank's [batch, tables, dim] buffer.
+    Nothing is added afterwards and no all-to-all runs; 1/G of the bytes of row sharding
+    cross NVLink.  Two one-element all-reduces order the steps.
+
+    local_tables: the tables this rank owns (plan.owned[rank]), full size.  run() leaves this
+    rank's pooled vectors, fp32, in `self.out` ([batch, tables, dim], inside the peer buffer)."""
+
+    def __init__(self, world: int, rank: int, device, plan: ShardPlan, local_tables, batch: int, dim: int,
+                 id_sets, combiner: int = 0, id_kind: int = 2):
+        import torch
+        import torch.distributed as dist
+
+        from . import device as dev
+        self.dist, self.dev, self.torch = dist, dev, torch
+        self.world, self.rank, self.plan = world, rank, plan
+        T, B, D = plan.T, batch, dim
+        self.T, self.B, self.D = T, B, D
+        nnz = plan.nnz                      # [world, T]
+        mine = plan.owned[rank]
+        self.sets = [dict(prepass=dev.BagPrepass(st["segs"], B), ids_all=st["ids_all"]) for st in id_sets]
+        wsb = self.sets[0]["prepass"].ws_bytes
+        up256 = lambda n: (n + 255) // 256 * 256
+        Lmax = int(nnz.sum(axis=1).max())
+        out_bytes = B * T * D * 4
+        off_ids = 2 * out_bytes                 # two output buffers, then this rank's ids, then its offsets
+        off_off = off_ids + up256(max(1, Lmax) * 8)
+        self.peer = dev.PeerBuffers(off_off + up256(wsb), world, rank)
+        self.out_bytes, self._off_ids, self._off_off = out_bytes, off_ids, off_off
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.my_nnz_total = int(nnz[rank].sum())
+        # what this rank fetches: for every source s, the ids and offsets of the owned tables
+        To = len(mine)
+        counts = [int(nnz[s, mine].sum()) for s in range(world)]
+        self.ids_in = torch.zeros(max(1, sum(counts)), dtype=torch.int64, device=device)
+        self.off_in = torch.zeros(max(1, world * To * (B + 1)), dtype=torch.int32, device=device)
+        self.copies = []
+        pos = 0
+        for s in range(world):
+            if To == 0:
+                break
+            first = mine[0]
+            src_ids = self.peer.ptrs[s] + off_ids + int(nnz[s, :first].sum()) * 8
+            self.copies.append((self.ids_in.data_ptr() + pos * 8, src_ids, counts[s] * 8))
+            src_off = self.peer.ptrs[s] + off_off + 512 + first * (B + 1) * 4
+            self.copies.append((self.off_in.data_ptr() + s * To * (B + 1) * 4, src_off, To * (B + 1) * 4))
+            pos += counts[s]
+        self.launches = []
+        for buf in range(2):
+            entries = []
+            pos = 0
+            for s in range(world):
+                for j, t in enumerate(mine):
+                    entries.append((local_tables[j].data_ptr(), plan.table_rows[t], plan.table_rows[t],
+                                    self.ids_in.data_ptr() + pos * 8, None, int(nnz[s, t]),
+                                    self.peer.ptrs[s] + buf * out_bytes + t * D * 4,
+                                    self.off_in.data_ptr() + ((s * To + j) * (B + 1)) * 4))
+                    pos += int(nnz[s, t])
+            self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, device, id_kind=id_kind,
+                                               combiner=combiner) if entries else None)
+        self.step = 0
+        self.out_ptr = self.peer.local
+        self.launches_per_step = 3 * ((world * max(To, 1) + 119) // 120) + 2 * world + 4
+        self.exchange_bytes = (sum(counts) - counts[rank]) * 8 + (world - 1) * To * B * D * 4
+        self._work = None
+
+    def prefetch(self, set_index: int) -> None:
+        st = self.sets[set_index]
+        # this rank's ids and bag offsets into the part of its buffer the owners read
+        self.dev.peer_copy(self.peer.local + self._off_ids, st["ids_all"].data_ptr(), self.my_nnz_total * 8)
+        ws = self.peer.local + self._off_off
+        st["prepass"].run_ptr(ws)
+        self._work = self.dist.all_reduce(self.flag, async_op=True)
+
+    def run(self, set_index: int) -> int:
+        """Returns the device address of this step's fp32 [batch, tables, dim] pooled vectors."""
+        if self._work is None:
+            self.prefetch(set_index)
+        self._work.wait()
+        self._work = None
+        buf = self.step % 2
+        self.step += 1
+        for dst, src, nbytes in self.copies:
+            self.dev.peer_copy(dst, src, nbytes)
+        if self.launches[buf] is not None:
+            self.launches[buf].run()     # pooled vectors land in their sources' memory
+        self.dist.all_reduce(self.flag)  # every owner's bag kernel has finished
+        return self.peer.local + buf * self.out_bytes
+
+    def error_bits(self) -> int:
+        bits = 0
+        for l in self.launches:
+            if l is not None:
+                bits |= l.error_bits()
+        return bits
+
+    def close(self) -> None:
+        self.peer.close()
+
+
 class ShardedDlrmPipeline:
     """Built lazily to keep torch out of ShardPlan's import path."""
 

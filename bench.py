@@ -79,8 +79,10 @@ def workload_config(args, world):
                 "global_batch": args.batch * world, "per_gpu_batch": args.batch, "tables": args.tables,
                 "dim": 128, "rows": rows, "bag": "U{1..50}, Zipf 1.2, mean",
                 "table_bytes_total": args.tables * rows * 512,
-                "parallelism": "row-sharded tables (mod rule) over %d GPU(s), lookups split at their "
-                               "source, partial sums stored into the owner's memory; dp MLP" % world,
+                "parallelism": ("table-wise sharded tables over %d GPU(s), pooled vectors stored into the "
+                                "sample owner's memory; dp MLP" % world) if args.shard == "table" else
+                               ("row-sharded tables (mod rule) over %d GPU(s), lookups split at their "
+                                "source, partial sums stored into the owner's memory; dp MLP" % world),
                 "l2": "inputs larger than L2 (table shard %.1f GB per GPU)" % (args.tables * int(args.rows_per_gpu) * 512 / 1e9)}
     return {"workload": "dlrm_style_fp32w_tf32math_batch%d_26tables_dim64_zipf1.05" % args.batch,
             "global_batch": args.batch * world, "per_gpu_batch": args.batch,
@@ -261,15 +263,18 @@ def run_gpu(args):
         if world == 1:  # the row-sharded step uses torch.distributed for its barriers at every N
             dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29000 + os.getpid() % 2000),
                                     rank=0, world_size=1, device_id=devi)
-        args.shard = "row"
+        args.shard = "table" if args.shard == "table" else "row"
         model = synth.recsys_model(seed=args.seed, tables=args.tables, rows=int(args.rows_per_gpu) * world,
                                    batch=args.batch, input_seed=1000 + rank)
-        pipe = RecsysPipeline(model, devi, keep_host_inputs=True)
+        pipe = RecsysPipeline(model, devi, keep_host_inputs=True, shard=args.shard)
         nnz = model.nnz
         # the bag kernel of the partitioned step reads an int32 local row per lookup and two
         # int32 positions per bag, and writes one fp32 part per bag
         emb_bytes = nnz * (4 * 128 + 4) + args.tables * args.batch * (4 * 128 + 8)
         bag_kernel = "bag_reduce_kernel<32,1> (gather + segment sum of the partitioned step, %d tables)" % args.tables
+        if args.shard == "table":  # whole bags: raw 8-byte ids hashed in the kernel, mean applied there
+            emb_bytes = nnz * (4 * 128 + 8) + args.tables * args.batch * (4 * 128 + 8)
+            bag_kernel = "bag_reduce_kernel<32,1> (hash-bucket + gather + segment mean, %d tables)" % args.tables
     else:
         model = synth.dlrm_model(seed=args.seed, batch=args.batch, max_rows=args.max_rows,
                                  input_seed=(1000 + rank) if world > 1 else None)

@@ -349,6 +349,9 @@ int annc_copy_rows_dev(float* dst, int64_t dst_stride, const float* src, int64_t
  * servers) by one kernel.  Peers close their mapping before the owner destroys the buffer. */
 int annc_peer_buffer_create(size_t bytes, void** dev_ptr, void* handle64);
 int annc_peer_buffer_open(const void* handle64, void** dev_ptr);
+/* Asynchronous device-to-device copy on `stream`; either side may be a mapped peer buffer (the
+ * owner of whole tables fetches the ids and bag offsets of its tables from every source). */
+int annc_peer_copy_dev(void* dst, const void* src, size_t bytes, void* stream);
 int annc_peer_buffer_close(void* dev_ptr);
 int annc_peer_buffer_destroy(void* dev_ptr);
 

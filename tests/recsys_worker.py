@@ -19,6 +19,7 @@ from oracle import oracle  # noqa: E402
 
 
 def main():
+    shard = sys.argv[1] if len(sys.argv) > 1 else "row"
     rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     world = int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(local)
@@ -26,7 +27,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     model = synth.recsys_model(seed=3, tables=5, rows=50_001, dim=128, batch=512, max_bag=50,
                                zipf_a=1.2, hidden=(256, 128, 1), input_seed=200 + rank, threads=2)
-    pipe = RecsysPipeline(model, dev)
+    pipe = RecsysPipeline(model, dev, shard=shard)
     got = pipe.forward().cpu().numpy()
     assert pipe.embed_error_bits() == 0
     again = pipe.forward().cpu().numpy()  # second receive buffer
@@ -34,9 +35,14 @@ def main():
     T, R, D, B = model.tables, model.rows, model.dim, model.batch
     # 1. the device-filled shard equals the numpy restatement of the hash
     probe = np.array([0, 1, 7, pipe.local_rows - 1])
-    for t in (0, T - 1):
-        want_rows = synth.hashed_table_rows(model.seed, t, rank + world * probe, D)
-        np.testing.assert_array_equal(pipe.table_mem[t][torch.from_numpy(probe).to(dev)].cpu().numpy(), want_rows)
+    if shard == "row":
+        for t in (0, T - 1):
+            want_rows = synth.hashed_table_rows(model.seed, t, rank + world * probe, D)
+            np.testing.assert_array_equal(pipe.table_mem[t][torch.from_numpy(probe).to(dev)].cpu().numpy(), want_rows)
+    else:
+        for j, t in enumerate(pipe.owned):
+            want_rows = synth.hashed_table_rows(model.seed, t, probe, D)
+            np.testing.assert_array_equal(pipe.table_mem[j][torch.from_numpy(probe).to(dev)].cpu().numpy(), want_rows)
     # 2. pooled means
     pooled = np.zeros((B, T, D), np.float32)
     for t, bag in enumerate(model.bags):
@@ -59,7 +65,7 @@ def main():
     dist.barrier()
     pipe.close()
     dist.destroy_process_group()
-    print(f"rank {rank} recsys ok err {err:.2e}")
+    print(f"rank {rank} recsys {shard} ok err {err:.2e}")
 
 
 if __name__ == "__main__":
