@@ -13,7 +13,7 @@ ANNC_F32, ANNC_I32, ANNC_I64, ANNC_BOOL, ANNC_U64 = 1, 3, 9, 10, 23
 ACT_NONE, ACT_RELU, ACT_SIGMOID = 0, 1, 2
 B_PLAIN, B_KN4 = 0, 1
 MATH_AUTO, MATH_FP32, MATH_TF32, MATH_BF16 = 0, 1, 2, 3
-IO_A_BF16, IO_B_BF16, IO_C_BF16, IO_SOFTMAX = 1, 2, 4, 8
+IO_A_BF16, IO_B_BF16, IO_C_BF16, IO_SOFTMAX, IO_PAIR = 1, 2, 4, 8, 16
 
 
 class AnncError(RuntimeError):

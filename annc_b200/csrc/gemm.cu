@@ -43,7 +43,7 @@ static int forced_route() {
 // whose two resident CTAs per SM and staged, coalesced epilogue stream C faster.
 static bool use_pair(const annc_gemm_desc& d, int math) {
   if (!pair_supported(d, math)) return false;
-  if (math == ANNC_MATH_BF16 || (d.io_flags & ANNC_IO_SOFTMAX)) return true;
+  if (math == ANNC_MATH_BF16 || (d.io_flags & (ANNC_IO_SOFTMAX | ANNC_IO_PAIR))) return true;
   if (!tc_supported(d, math)) return true;
   const int f = forced_route();
   if (f) return f == 2;

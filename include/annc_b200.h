@@ -409,7 +409,8 @@ enum { ANNC_MATH_AUTO = 0, ANNC_MATH_FP32 = 1, ANNC_MATH_TF32 = 2, ANNC_MATH_BF1
  * data: A [M,K], B [N,K] (trans_b = 1), lda / ldb / stride_a / stride_b in elements.
  * ANNC_IO_SOFTMAX applies a row softmax over the n <= 256 columns after bias and activation
  * (batch_matmul followed by the XNNPACK softmax, in one kernel). */
-enum { ANNC_IO_A_BF16 = 1, ANNC_IO_B_BF16 = 2, ANNC_IO_C_BF16 = 4, ANNC_IO_SOFTMAX = 8 };
+enum { ANNC_IO_A_BF16 = 1, ANNC_IO_B_BF16 = 2, ANNC_IO_C_BF16 = 4, ANNC_IO_SOFTMAX = 8,
+       ANNC_IO_PAIR = 16 /* ask for the CTA-pair kernel whatever the shape heuristic says */ };
 
 typedef struct annc_gemm_desc {
   int32_t trans_a, trans_b;

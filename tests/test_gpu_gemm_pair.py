@@ -11,15 +11,11 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-import os
-
-os.environ["ANNC_GEMM_ROUTE"] = "pair"  # read once by the library: this module runs in its own process
-
 import torch
 import annc_b200  # noqa: F401,E402  (no fallback: a missing library fails the collection)
 from annc_b200 import device  # noqa: E402
 from annc_b200._lib import (ACT_NONE, ACT_RELU, ACT_SIGMOID, IO_A_BF16, IO_B_BF16, IO_C_BF16,  # noqa: E402
-                            IO_SOFTMAX, MATH_BF16, MATH_TF32)
+                            IO_PAIR, IO_SOFTMAX, MATH_BF16, MATH_TF32)
 
 
 def _dev(a):
@@ -43,9 +39,9 @@ def test_pair_tf32(m, n, k, bsrc):
     want = oracle.matmul(a, b)
     c = torch.full((m, n), float("nan"), device="cuda")
     if bsrc == "nk":
-        name = device.gemm(_dev(a), _dev(b.T), c, m=m, n=n, k=k, trans_b=True, math=MATH_TF32)
+        name = device.gemm(_dev(a), _dev(b.T), c, m=m, n=n, k=k, trans_b=True, math=MATH_TF32, io_flags=IO_PAIR)
     else:
-        name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, math=MATH_TF32)
+        name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, math=MATH_TF32, io_flags=IO_PAIR)
     assert name == "tcgen05_pair_tf32"
     assert not device.gemm_timed_out()
     assert nerr(c, want) <= 2e-3
@@ -75,7 +71,7 @@ def test_pair_epilogues(act, with_addend, with_bias, alpha, beta):
     c = _dev(c0)
     name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, alpha=alpha, beta=beta,
                        addend=_dev(add) if with_addend else None, bias=_dev(bias) if with_bias else None,
-                       activation=act, math=MATH_TF32)
+                       activation=act, math=MATH_TF32, io_flags=IO_PAIR)
     assert name == "tcgen05_pair_tf32" and not device.gemm_timed_out()
     assert np.abs(c.cpu().numpy() - want).max() <= 2e-3 * np.abs(pre).max()
 
@@ -88,7 +84,7 @@ def test_pair_strided_batch_and_pitched_output():
     want = np.matmul(a, b)
     c = torch.full((bsz, m, n + 8), 9.0, device="cuda")
     name = device.gemm(_dev(a), _dev(b), c, m=m, n=n, k=k, batch=bsz, stride_a=m * k, stride_b=k * n,
-                       stride_c=m * (n + 8), ldc=n + 8, math=MATH_TF32)
+                       stride_c=m * (n + 8), ldc=n + 8, math=MATH_TF32, io_flags=IO_PAIR)
     assert name == "tcgen05_pair_tf32" and not device.gemm_timed_out()
     got = c.cpu().numpy()
     assert (got[:, :, n:] == 9.0).all()
@@ -124,7 +120,7 @@ def test_pair_batch_matmul_softmax(n):
     logits = torch.empty((bsz, m, n), device="cuda")
     probs = torch.full((bsz, m, n), float("nan"), device="cuda")
     kw = dict(m=m, n=n, k=k, batch=bsz, stride_a=m * k, stride_b=k * n, stride_c=m * n, math=MATH_TF32)
-    device.gemm(_dev(q), _dev(kt), logits, **kw)
+    device.gemm(_dev(q), _dev(kt), logits, io_flags=IO_PAIR, **kw)
     name = device.gemm(_dev(q), _dev(kt), probs, io_flags=IO_SOFTMAX, **kw)
     assert name == "tcgen05_pair_tf32" and not device.gemm_timed_out()
     own = oracle.softmax(logits.cpu().numpy().reshape(-1, n)).reshape(bsz, m, n)
