@@ -35,6 +35,16 @@ int cuda_fail(cudaError_t e, const char* what);
     if (!(cond)) return ::annc::fail(code, "%s", msg); \
   } while (0)
 
+// Index of the current device, clamped to the size of the per-device caches below.  Function
+// attributes, occupancy figures and symbol addresses belong to one device: code that caches them
+// keeps one slot per device so that a process driving several GPUs sets each of them up.
+constexpr int kMaxDevices = 64;
+inline int device_slot() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0) d = 0;
+  return d < kMaxDevices ? d : kMaxDevices - 1;
+}
+
 cudaStream_t current_stream();
 // Events set with annc_embed_bag_set_timing_events on this thread (may be null).
 void timing_events(cudaEvent_t* start, cudaEvent_t* stop);

@@ -392,7 +392,8 @@ bool tc_supported(const annc_gemm_desc& d, int math) {
 
 int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   if (!tc_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 gemm: unsupported shape");
-  static bool attr_set = false;
+  static bool attr_set_dev[kMaxDevices] = {};
+  bool& attr_set = attr_set_dev[device_slot()];
   if (!attr_set) {
     ANNC_CUDA(cudaFuncSetAttribute(gemm_tf32_tcgen05_kernel<3>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(3)));
@@ -447,10 +448,12 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
 }
 
 int* gemm_error_word() {
-  static int* addr = []() -> int* {
+  static int* addr_dev[kMaxDevices] = {};
+  int*& addr = addr_dev[device_slot()];
+  if (!addr) {
     void* p = nullptr;
-    return cudaGetSymbolAddress(&p, g_gemm_error) == cudaSuccess ? static_cast<int*>(p) : nullptr;
-  }();
+    if (cudaGetSymbolAddress(&p, g_gemm_error) == cudaSuccess) addr = static_cast<int*>(p);
+  }
   return addr;
 }
 

@@ -536,11 +536,13 @@ bool pair_supported(const annc_gemm_desc& d, int math) {
 int run_pair(const annc_gemm_desc& d, int math, cudaStream_t s) {
   if (!pair_supported(d, math)) return fail(ANNC_ERR_UNSUPPORTED, "tcgen05 pair gemm: unsupported shape");
   const bool bf16 = math == ANNC_MATH_BF16;
-  static int max_pairs[2] = {0, 0};
+  static int max_pairs_dev[kMaxDevices][2] = {};
+  int (&max_pairs)[2] = max_pairs_dev[device_slot()];
   const bool softmax = (d.io_flags & ANNC_IO_SOFTMAX) != 0;
   auto kern = bf16 ? (softmax ? gemm_pair_tcgen05_kernel<1, true> : gemm_pair_tcgen05_kernel<1, false>)
                    : (softmax ? gemm_pair_tcgen05_kernel<0, true> : gemm_pair_tcgen05_kernel<0, false>);
-  static bool attr_done[2][2] = {{false, false}, {false, false}};
+  static bool attr_done_dev[kMaxDevices][2][2] = {};
+  bool (&attr_done)[2][2] = attr_done_dev[device_slot()];
   if (!attr_done[bf16][softmax]) {
     ANNC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM));
     attr_done[bf16][softmax] = true;

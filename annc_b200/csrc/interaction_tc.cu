@@ -236,7 +236,8 @@ int dot_interaction_tc(const float* z, int64_t batch, int F, int dim, int64_t z_
       (reinterpret_cast<uintptr_t>(z) & 15) != 0 || batch * F >= (1LL << 31) ||
       out_stride >= (1 << 20))
     return ANNC_ERR_UNSUPPORTED;
-  static bool attr_set = false;
+  static bool attr_set_dev[kMaxDevices] = {};
+  bool& attr_set = attr_set_dev[device_slot()];
   if (!attr_set) {
     ANNC_CUDA(cudaFuncSetAttribute(dot_interaction_tc_kernel<2>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I_SMEM));
