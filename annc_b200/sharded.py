@@ -18,8 +18,11 @@ Three partitionings of the tables, the MLPs always run on the rank's own batch s
   row_nccl the all-gathered ids with the exchange as a separate step: partial sums are
            written locally, then go through an NCCL all-to-all (the baseline the fused
            step is measured against).
-  table    whole tables per rank (contiguous blocks); ids travel to the owners by
-           all-to-all, finished pooled vectors come back by all-to-all, no add.
+  table    whole tables per rank (contiguous blocks); the owners fetch the ids and bag offsets
+           of their tables through peer-mapped pointers and the bag kernel stores finished
+           pooled vectors into the sample owner's memory (TableShardedBags); no add.
+  table_nccl  the same partitioning with NCCL: ids travel to the owners by all-to-all,
+           finished pooled vectors come back by all-to-all.
   replica  every rank holds every table; no exchange (scaling ceiling when tables fit).
 
 ShardPlan is pure numpy so that the partitioning logic is testable on CPU ranks.
@@ -35,7 +38,7 @@ class ShardPlan:
     """Sizes and offsets of the exchange.  nnz[s][t] = lookups of rank s in table t."""
 
     def __init__(self, mode: str, world: int, rank: int, table_rows: List[int], nnz: np.ndarray):
-        assert mode in ("row", "row_gather", "row_nccl", "table", "replica")
+        assert mode in ("row", "row_gather", "row_nccl", "table", "table_nccl", "replica")
         self.mode, self.world, self.rank = mode, world, rank
         self.table_rows = list(table_rows)
         self.T = len(table_rows)
@@ -393,7 +396,17 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 self.exchange_bytes = (world - 1) * (B * T * D * 4 + L * 8 + wsb)
                 self._works = None
                 return
-            # table mode
+            if mode == "table":
+                mine = plan.owned[rank]
+                self.tables = [self._up(emb.tables[t]) for t in mine]
+                self.tbags = TableShardedBags(
+                    world, rank, self.device, plan, self.tables, B, D,
+                    [dict(ids_all=st["ids_all"], segs=st["segs"]) for st in self.sets], combiner=0)
+                self.peer = self.tbags.peer
+                self.embed_launches = self.tbags.launches_per_step + 1
+                self.exchange_bytes = self.tbags.exchange_bytes
+                return
+            # table_nccl mode
             mine = plan.owned[rank]
             self.tables = [self._up(emb.tables[t]) for t in mine]
             sc, rc = plan.send_counts(), plan.recv_counts()
@@ -464,7 +477,11 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 dev.sum_partials(self.recv, world, B * T * D, B, T * D, T * D,
                                  self.z.data_ptr() + D * 4, F * D)
                 return
-            # table mode: ids to the owners, pooled vectors back
+            if mode == "table":
+                pooled = self.tbags.run(self.cur)  # fp32 [B, T, D] written by the owners
+                dev.copy_rows(self.z.data_ptr() + D * 4, F * D, pooled, T * D, T * D, B)
+                return
+            # table_nccl mode: ids to the owners, pooled vectors back
             To = len(plan.owned[rank])
             self.sets[self.cur]["prepass"].run(self.off_ws)
             dist.all_to_all_single(self.ids_r[:sum(self.rc)], self.ids_all, self.rc, self.sc)
@@ -489,6 +506,9 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "row":
                 self.rowbags.prefetch(self.cur)
                 return
+            if mode == "table":
+                self.tbags.prefetch(self.cur)
+                return
             if mode not in ("row_gather", "row_nccl"):
                 return
             n = self.nnz_total
@@ -505,6 +525,8 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 return DlrmPipeline.embed_error_bits(self)
             if mode == "row":
                 return self.rowbags.error_bits()
+            if mode == "table":
+                return self.tbags.error_bits()
             if mode == "row_gather":
                 return self.launches[0].error_bits() | self.launches[1].error_bits()
             return self.launch.error_bits() if self.launch is not None else 0

@@ -57,7 +57,7 @@ def parse_args():
     ap.add_argument("--max-rows", type=float, default=1e7)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_gather", "row_nccl", "table", "replica"],
+    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_gather", "row_nccl", "table", "table_nccl", "replica"],
                     help="table partitioning for --gpus > 1: row = mod row-sharding, lookups split by "
                          "owner at their source, the bag kernel stores partial sums into the owner "
                          "rank's memory; row_gather = the same stores with all-gathered ids; row_nccl = "
