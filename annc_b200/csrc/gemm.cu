@@ -26,18 +26,6 @@ static int validate(const annc_gemm_desc& d) {
   return ANNC_OK;
 }
 
-// ANNC_GEMM_ROUTE=single|pair forces one tensor-core kernel where both fit (for A/B timing).
-static int forced_route() {
-  static const int v = []() {
-    const char* e = getenv("ANNC_GEMM_ROUTE");
-    if (!e) return 0;
-    if (!strcmp(e, "single")) return 1;
-    if (!strcmp(e, "pair")) return 2;
-    return 0;
-  }();
-  return v;
-}
-
 // The CTA-pair kernel works on 256 x 256 tiles with a long main loop per tile: it takes the
 // compute-bound GEMMs.  Skinny layers (small K, output-bound) stay on the single-CTA kernel,
 // whose two resident CTAs per SM and staged, coalesced epilogue stream C faster.
@@ -45,8 +33,6 @@ static bool use_pair(const annc_gemm_desc& d, int math) {
   if (!pair_supported(d, math)) return false;
   if (math == ANNC_MATH_BF16 || (d.io_flags & (ANNC_IO_SOFTMAX | ANNC_IO_PAIR))) return true;
   if (!tc_supported(d, math)) return true;
-  const int f = forced_route();
-  if (f) return f == 2;
   return d.m >= 256 && d.n >= 192 && d.k >= 1024;
 }
 

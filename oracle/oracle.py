@@ -27,13 +27,21 @@ f32p = C.POINTER(C.c_float)
 u8p = C.POINTER(C.c_uint8)
 
 
-def build(reference_root: str | None = "/root/reference") -> None:
-    """Compile the C oracle (and the reference's flag parser where its tree exists)."""
-    targets = ["all"]
-    if reference_root and os.path.isdir(reference_root):
-        targets.append("ref")
-    subprocess.run(["make", "-C", _HERE, f"REFERENCE_ROOT={reference_root}"] + targets,
-                   check=True, stdout=subprocess.DEVNULL)
+def reference_root() -> str | None:
+    """The ANNC checkout named by ANNC_REFERENCE_ROOT, or None when unset / not a directory."""
+    root = os.environ.get("ANNC_REFERENCE_ROOT")
+    return root if root and os.path.isdir(root) else None
+
+
+def build(reference_root_dir: str | None = None) -> None:
+    """Compile the C oracle, and where an ANNC checkout is given (argument, else the
+    ANNC_REFERENCE_ROOT environment variable) the pieces of the reference that compile
+    from their own sources."""
+    root = reference_root_dir or reference_root()
+    cmd = ["make", "-C", _HERE, "all"]
+    if root:
+        cmd += [f"REFERENCE_ROOT={root}", "ref"]
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 _lib = None
@@ -257,20 +265,55 @@ def argmax3d(invals, inidxs, init_value, init_idx):
 
 # ---------------------------------------------------------------- GEMM family
 
+_blas = None
+
+
+def openblas() -> C.CDLL:
+    """scipy's bundled OpenBLAS (LP64 `scipy_cblas_*` names): the library family the reference
+    links (OpenBLAS 0.3.29, third_party/repo.bzl:3-12).  Threads are set to the affinity count."""
+    global _blas
+    if _blas is None:
+        import glob
+        import scipy
+        cand = glob.glob(os.path.join(os.path.dirname(scipy.__file__), os.pardir, "scipy.libs",
+                                      "libscipy_openblas*.so"))
+        if not cand:
+            raise RuntimeError("scipy's bundled OpenBLAS was not found")
+        _blas = C.CDLL(cand[0])
+        _blas.scipy_cblas_sasum.restype = C.c_float
+        _blas.scipy_openblas_set_num_threads(C.c_int(max(1, host_threads())))
+    return _blas
+
+
+def set_blas_threads(n: int) -> None:
+    openblas().scipy_openblas_set_num_threads(C.c_int(max(1, int(n))))
+
+
+_ROW, _NOTR, _TR = 101, 111, 112
+
+
+def cblas_sgemm(trA, trB, M, N, K, alpha, A, lda, B, ldb, beta, Cbuf, ldc) -> None:
+    """cblas_sgemm(CblasRowMajor, ...) on contiguous float32 arrays; Cbuf is updated in place."""
+    openblas().scipy_cblas_sgemm(C.c_int(_ROW), C.c_int(_TR if trA else _NOTR),
+                                 C.c_int(_TR if trB else _NOTR), C.c_int(M), C.c_int(N), C.c_int(K),
+                                 C.c_float(alpha), _p(A, f32p), C.c_int(lda), _p(B, f32p),
+                                 C.c_int(ldb), C.c_float(beta), _p(Cbuf, f32p), C.c_int(ldc))
+
+
 def sgemm(trA, trB, A, B, M, N, K, alpha=1.0, beta=0.0, Cin=None, blas=True) -> np.ndarray:
     """Row-major sgemm with the leading dimensions of
-    annc/service/cpu/xla/kernel_selector.cc:31-43.  ``blas=True`` uses numpy's
-    OpenBLAS sgemm (the library family the reference calls), else the scalar C loop."""
+    annc/service/cpu/xla/kernel_selector.cc:31-43 (lda = trA ? M : K, ldb = trB ? K : N).
+    ``blas=True`` calls OpenBLAS cblas_sgemm like the reference, else the scalar C loop."""
     A = _c(A, np.float32).reshape((M, K) if not trA else (K, M))
     B = _c(B, np.float32).reshape((K, N) if not trB else (N, K))
-    if blas:
-        a = A.T if trA else A
-        b = B.T if trB else B
-        r = np.float32(alpha) * (a @ b)
-        if beta != 0.0:
-            r = r + np.float32(beta) * _c(Cin, np.float32).reshape(M, N)
-        return r.astype(np.float32)
     out = np.zeros((M, N), np.float32) if Cin is None else _c(Cin, np.float32).reshape(M, N).copy()
+    if M * N == 0:
+        return out
+    if blas:
+        if K == 0:
+            return (np.float32(beta) * out).astype(np.float32)
+        cblas_sgemm(trA, trB, M, N, K, alpha, A, M if trA else K, B, K if trB else N, beta, out, N)
+        return out
     lib().oracle_sgemm(C.c_int(int(trA)), C.c_int(int(trB)), C.c_int64(M), C.c_int64(N),
                        C.c_int64(K), C.c_float(alpha), _p(A, f32p), _p(B, f32p),
                        C.c_float(beta), _p(out, f32p))
@@ -278,18 +321,29 @@ def sgemm(trA, trB, A, B, M, N, K, alpha=1.0, beta=0.0, Cin=None, blas=True) -> 
 
 
 def matmul(A, B):
-    """__matmul (annc/service/cpu/gemm_rewriter.cc:161-185)."""
-    return (_c(A, np.float32) @ _c(B, np.float32)).astype(np.float32)
+    """__matmul (annc/service/cpu/gemm_rewriter.cc:161-185): one row-major sgemm, alpha 1 beta 0."""
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    (M, K), N = A.shape, B.shape[1]
+    return sgemm(False, False, A, B, M, N, K)
 
 
 def batch_matmul(A, B):
-    """__batch_matmul (annc/service/cpu/gemm_rewriter.cc:187-216)."""
-    return np.matmul(_c(A, np.float32), _c(B, np.float32)).astype(np.float32)
+    """__batch_matmul (annc/service/cpu/gemm_rewriter.cc:187-216): one sgemm per batch slab."""
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    lead = A.shape[:-2]
+    A3, B3 = A.reshape((-1,) + A.shape[-2:]), B.reshape((-1,) + B.shape[-2:])
+    out = np.empty((A3.shape[0], A3.shape[1], B3.shape[2]), np.float32)
+    for i in range(A3.shape[0]):
+        out[i] = sgemm(False, False, A3[i], B3[i], A3.shape[1], B3.shape[2], A3.shape[2])
+    return out.reshape(lead + out.shape[-2:])
 
 
 def matmul_add(addend, A, B):
-    """__matmul_add (annc/service/cpu/gemm_rewriter.cc:218-247): memcpy + sgemm(beta=1)."""
-    return (_c(addend, np.float32) + _c(A, np.float32) @ _c(B, np.float32)).astype(np.float32)
+    """__matmul_add (annc/service/cpu/gemm_rewriter.cc:218-247): memcpy of the addend into the
+    output, then sgemm with beta = 1."""
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    (M, K), N = A.shape, B.shape[1]
+    return sgemm(False, False, A, B, M, N, K, 1.0, 1.0, np.broadcast_to(_c(addend, np.float32), (M, N)))
 
 
 def matmul_add_relu(addend, A, B):
@@ -405,6 +459,43 @@ def layout_matmul(A, Bpacked):
     K = A.shape[1]
     N = Bpacked.size // K
     return (A @ kn4_unpack(Bpacked, K, N)).astype(np.float32)
+
+
+# ---------------------------------------------------------------- custom-call bodies (real reference)
+
+_XLA_REF_PATH = os.path.join(_HERE, "_ref", "libannc_xla_ref.so")
+_xla_ref = None
+
+
+def xla_ref_available() -> bool:
+    return os.path.exists(_XLA_REF_PATH)
+
+
+def xla_ref() -> C.CDLL:
+    """The reference's own bodies of __matmul, __batch_matmul, __matmul_add, __matmul_add_relu,
+    __pooling and __reduce_mean (oracle/xla_ref_shim.cc, built by `make ref`), with their CBLAS
+    calls pointed at the same OpenBLAS the restatements above call."""
+    global _xla_ref
+    if _xla_ref is None:
+        l = C.CDLL(_XLA_REF_PATH)
+        b = openblas()
+        l.annc_xla_ref_set_blas(C.cast(b.scipy_cblas_sgemm, C.c_void_p), C.cast(b.scipy_cblas_sasum, C.c_void_p))
+        _xla_ref = l
+    return _xla_ref
+
+
+def shape_info(a: np.ndarray) -> np.ndarray:
+    """The s64 operand XLA appends per tensor: [dims..., minor_to_major...]
+    (annc/service/hlo_util.h:14-21); row-major, so minor_to_major = rank-1 .. 0."""
+    return np.array(list(a.shape) + list(range(a.ndim - 1, -1, -1)), np.int64)
+
+
+def xla_ref_call(name: str, out: np.ndarray, operands) -> np.ndarray:
+    """Calls annc_ref_<name>(out, in) with `operands` (contiguous numpy arrays) as in[]."""
+    keep = [np.ascontiguousarray(o) for o in operands]
+    arr = (C.c_void_p * len(keep))(*[C.c_void_p(o.ctypes.data) for o in keep])
+    getattr(xla_ref(), "annc_ref_" + name)(C.c_void_p(out.ctypes.data), arr)
+    return out
 
 
 # ---------------------------------------------------------------- ANNC_FLAGS (real reference)

@@ -1,0 +1,54 @@
+// TEST INFRASTRUCTURE ONLY.  Compiles the reference's own custom-call bodies into
+// oracle/_ref/libannc_xla_ref.so: __matmul, __batch_matmul, __matmul_add, __matmul_add_relu
+// (annc/service/cpu/gemm_rewriter.cc:161-281), __pooling (annc/service/cpu/graph_opt.cc:131-176)
+// and __reduce_mean (annc/service/cpu/reduce_rewriter.cc:31-46).
+//
+// The bodies use nothing of XLA: plain pointers, memcpy, std::max, variable-length arrays and
+// two CBLAS calls.  oracle/Makefile cuts those line ranges out of the reference files where
+// they lie into oracle/_ref/*.inc (never into the repository) and this file supplies what
+// they need around them: the CBLAS names, forwarded to function pointers that the Python side
+// points at an OpenBLAS (cblas_sgemm / cblas_sasum of the library numpy or scipy bundles: the
+// library family the reference links, third_party/repo.bzl:3-12).
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+
+extern "C" {
+typedef enum { CblasRowMajor = 101, CblasColMajor = 102 } CBLAS_LAYOUT;
+typedef enum { CblasNoTrans = 111, CblasTrans = 112, CblasConjTrans = 113 } CBLAS_TRANSPOSE;
+typedef void (*sgemm_fn)(CBLAS_LAYOUT, CBLAS_TRANSPOSE, CBLAS_TRANSPOSE, int, int, int, float,
+                         const float*, int, const float*, int, float, float*, int);
+typedef float (*sasum_fn)(int, const float*, int);
+static sgemm_fn g_sgemm = nullptr;
+static sasum_fn g_sasum = nullptr;
+void annc_xla_ref_set_blas(void* sgemm, void* sasum) {
+  g_sgemm = reinterpret_cast<sgemm_fn>(sgemm);
+  g_sasum = reinterpret_cast<sasum_fn>(sasum);
+}
+}
+
+static inline void cblas_sgemm(CBLAS_LAYOUT l, CBLAS_TRANSPOSE ta, CBLAS_TRANSPOSE tb, int m, int n,
+                               int k, float alpha, const float* a, int lda, const float* b, int ldb,
+                               float beta, float* c, int ldc) {
+  g_sgemm(l, ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+}
+static inline float cblas_sasum(int n, const float* x, int inc) { return g_sasum(n, x, inc); }
+
+#define ANNC_ENABLED_OPENBLAS 1
+
+namespace xla {
+namespace cpu {
+#include "_ref/xla_gemm_bodies.inc"
+#include "_ref/xla_pooling_body.inc"
+#include "_ref/xla_reduce_mean_body.inc"
+}  // namespace cpu
+}  // namespace xla
+
+extern "C" {
+void annc_ref_matmul(void* out, const void** in) { xla::cpu::__matmul(out, in); }
+void annc_ref_batch_matmul(void* out, const void** in) { xla::cpu::__batch_matmul(out, in); }
+void annc_ref_matmul_add(void* out, const void** in) { xla::cpu::__matmul_add(out, in); }
+void annc_ref_matmul_add_relu(void* out, const void** in) { xla::cpu::__matmul_add_relu(out, in); }
+void annc_ref_pooling(void* out, void** in) { xla::cpu::__pooling(out, in); }
+void annc_ref_reduce_mean(void* out, const void** in) { xla::cpu::__reduce_mean(out, in); }
+}

@@ -43,4 +43,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ANNC_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_kn4_golden.py <ANNC checkout>  (or set ANNC_REFERENCE_ROOT)")
+    main(root)
