@@ -82,15 +82,10 @@ def _load() -> C.CDLL:
     lib.annc_sum_partials_masked_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                                  C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
                                                  C.c_int, C.c_void_p]
-    lib.annc_embed_bag_partition_scratch_bytes.restype = C.c_size_t
-    lib.annc_embed_bag_partition_scratch_bytes.argtypes = [C.c_int, C.c_int64, C.c_int]
-    lib.annc_embed_bag_partition_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int,
-                                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                                 C.c_size_t, C.c_void_p]
-    lib.annc_embed_bag_pull_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64,
-                                            C.c_void_p, C.c_void_p, C.c_void_p]
     lib.annc_synth_fill_rows_dev.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_uint64, C.c_int64,
                                              C.c_int64, C.c_int64, C.c_void_p]
+    lib.annc_synth_fill_row_list_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint64,
+                                                 C.c_int64, C.c_void_p]
     lib.annc_register_constant.argtypes = [C.c_void_p, C.c_size_t]
     lib.annc_unregister_constant.argtypes = [C.c_void_p]
     return lib

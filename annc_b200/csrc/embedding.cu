@@ -295,93 +295,6 @@ int annc_embed_bag_owner_mask_dev(const annc_bag_table* tables, int num_tables, 
   return ANNC_OK;
 }
 
-size_t annc_embed_bag_partition_scratch_bytes(int num_tables, int64_t batch, int shard_count) {
-  const long long n = (long long)shard_count * num_tables * batch + 1;
-  return (scan_scratch_ints(n) + 4) * sizeof(int);
-}
-
-int annc_embed_bag_partition_dev(const annc_bag_table* tables, int num_tables, int id_kind,
-                                 int64_t batch, int shard_count, int32_t* positions,
-                                 int32_t* local_rows, uint32_t* owner_mask, void* scratch,
-                                 size_t scratch_bytes, void* stream) {
-  ANNC_REQUIRE(tables && num_tables >= 1 && positions && local_rows && owner_mask && scratch,
-               ANNC_ERR_INVALID_ARGUMENT, "null argument");
-  ANNC_REQUIRE(id_kind >= 0 && id_kind <= 2, ANNC_ERR_INVALID_ARGUMENT, "id_kind must be 0, 1 or 2");
-  ANNC_REQUIRE(shard_count >= 1 && shard_count <= 16, ANNC_ERR_INVALID_ARGUMENT,
-               "partition: shard_count must be 1..16");
-  ANNC_REQUIRE(batch >= 1, ANNC_ERR_INVALID_ARGUMENT, "partition: empty batch");
-  const long long n = (long long)shard_count * num_tables * batch + 1;
-  ANNC_REQUIRE(n < (1LL << 31), ANNC_ERR_UNSUPPORTED, "partition: shards * tables * batch too large");
-  ANNC_REQUIRE(scratch_bytes >= annc_embed_bag_partition_scratch_bytes(num_tables, batch, shard_count),
-               ANNC_ERR_INVALID_ARGUMENT, "partition: scratch too small");
-  long long total_nnz = 0;
-  for (int t = 0; t < num_tables; ++t) {
-    ANNC_REQUIRE(tables[t].offsets && (tables[t].ids || tables[t].nnz == 0), ANNC_ERR_INVALID_ARGUMENT,
-                 "partition needs ids and bag offsets");
-    if (id_kind == 2 && tables[t].num_buckets < 1)
-      return fail(ANNC_ERR_INVALID_ARGUMENT, "num_buckets must be >= 1");
-    total_nnz += tables[t].nnz;
-  }
-  ANNC_REQUIRE(total_nnz < (1LL << 31) - 1, ANNC_ERR_UNSUPPORTED, "partition: more than 2^31-2 lookups");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int* tile_scratch = static_cast<int*>(scratch);
-  int* total_dev = tile_scratch + scan_scratch_ints(n);
-  ANNC_CUDA(cudaMemsetAsync(positions + (n - 1), 0, sizeof(int), s));  // closing entry
-  for (int pass = 0; pass < 2; ++pass) {
-    for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
-      const int nt = std::min(kMaxTables, num_tables - t0);
-      BagParams p;
-      memset(&p, 0, sizeof(p));
-      p.num_tables = nt;
-      p.id_kind = id_kind;
-      p.batch = batch;
-      p.shard_count = shard_count;
-      for (int t = 0; t < nt; ++t) {
-        const annc_bag_table& T = tables[t0 + t];
-        p.t[t].ids = T.ids;
-        p.t[t].num_buckets = (unsigned long long)T.num_buckets;
-        p.t[t].magic = id_kind == 2 ? mod_magic(p.t[t].num_buckets) : 0;
-        p.t[t].nnz = (int)T.nnz;
-        p.t[t].given_off = T.offsets;
-      }
-      const long long groups = (long long)nt * batch;
-      const unsigned blocks = (unsigned)((groups + 15) / 16);
-      if (pass == 0)
-        bag_partition_kernel<false><<<blocks, 256, 0, s>>>(p, num_tables, t0, positions, nullptr, nullptr);
-      else
-        bag_partition_kernel<true><<<blocks, 256, 0, s>>>(p, num_tables, t0, positions, local_rows,
-                                                          owner_mask);
-    }
-    if (pass == 0) exclusive_scan(positions, n, positions, tile_scratch, total_dev, s);
-  }
-  ANNC_CUDA(cudaGetLastError());
-  return ANNC_OK;
-}
-
-int annc_embed_bag_pull_dev(const int32_t* const* peer_positions, const int32_t* const* peer_rows,
-                            int num_sources, int me, int64_t per_rank, int32_t* const* positions_out,
-                            int32_t* const* rows_out, void* stream) {
-  ANNC_REQUIRE(peer_positions && peer_rows && positions_out && rows_out && num_sources >= 1 &&
-                   num_sources <= 32 && me >= 0 && per_rank >= 1,
-               ANNC_ERR_INVALID_ARGUMENT, "pull: bad arguments");
-  PullParams a;
-  memset(&a, 0, sizeof(a));
-  for (int q = 0; q < num_sources; ++q) {
-    ANNC_REQUIRE(peer_positions[q] && peer_rows[q] && positions_out[q] && rows_out[q],
-                 ANNC_ERR_INVALID_ARGUMENT, "pull: null buffer");
-    a.pos[q] = peer_positions[q];
-    a.rows[q] = peer_rows[q];
-    a.pos_out[q] = positions_out[q];
-    a.rows_out[q] = rows_out[q];
-  }
-  a.per_rank = per_rank;
-  a.me = me;
-  dim3 grid(148 * 2, (unsigned)num_sources);
-  bag_pull_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
-  ANNC_CUDA(cudaGetLastError());
-  return ANNC_OK;
-}
-
 int annc_embed_bag_prepass_dev(const annc_bag_table* tables, int num_tables, int64_t ncols,
                                int32_t col, int64_t batch, void* workspace, size_t workspace_bytes,
                                void* stream) {

@@ -9,6 +9,8 @@
 
 #include <cstdint>
 
+#include "emb_device.cuh"
+
 namespace annc {
 namespace emb {
 
@@ -117,29 +119,6 @@ bag_prepass2_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 }
 
-// x % d in uint64 without a division: with magic = floor((2^64 - 1) / d) the estimate
-// q = hi64(x * magic) is floor(x / d) or one less, for every x and every d >= 1, so the
-// remainder needs at most one correction (a second one is kept as a guard).  Bit-exact with
-// the `hash % num_buckets` of fused_embedding_with_hash_bucket.cc:63-64.
-__host__ __device__ __forceinline__ unsigned long long mod_magic(unsigned long long d) {
-  return ~0ull / d;
-}
-__device__ __forceinline__ unsigned long long fast_mod_u64(unsigned long long x, unsigned long long d,
-                                                           unsigned long long magic) {
-  unsigned long long r = x - __umul64hi(x, magic) * d;
-  if (r >= d) r -= d;
-  if (r >= d) r -= d;
-  return r;
-}
-
-__device__ __forceinline__ long long load_row_id(const void* ids, int id_kind, long long i,
-                                                 unsigned long long num_buckets,
-                                                 unsigned long long magic) {
-  if (id_kind == 0) return (long long)((const int*)ids)[i];
-  if (id_kind == 1) return ((const long long*)ids)[i];
-  return (long long)fast_mod_u64(((const unsigned long long*)ids)[i], num_buckets, magic);
-}
-
 // Row sharding.  Returns the local row, or -2 when another rank owns the row.  Rows below
 // 2^32 (every real table) take 32-bit arithmetic.
 constexpr long long kNotMine = -2;
@@ -156,16 +135,6 @@ __device__ __forceinline__ long long shard_row(long long r, int shard_count, int
 __device__ __forceinline__ int shard_owner(long long r, int shard_count) {
   if ((unsigned long long)r <= 0xffffffffull) return (int)((unsigned)r % (unsigned)shard_count);
   return (int)(r % shard_count);
-}
-
-__device__ __forceinline__ float4 ldg4(const float* p) {
-  return __ldg(reinterpret_cast<const float4*>(p));
-}
-__device__ __forceinline__ void add4(float4& a, const float4& b) {
-  a.x = __fadd_rn(a.x, b.x);
-  a.y = __fadd_rn(a.y, b.y);
-  a.z = __fadd_rn(a.z, b.z);
-  a.w = __fadd_rn(a.w, b.w);
 }
 
 // Position of the k-th (0-based) set bit of m; k must be below popc(m).
@@ -313,101 +282,6 @@ bag_owner_mask_kernel(BagParams p, unsigned* mask) {
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) m |= __shfl_xor_sync(gmask, m, o, 16);
   if (lane == 0) mask[group] = m;
-}
-
-// ---- row sharding, ids partitioned at the source -------------------------------------
-// The rank that owns a batch splits every bag's lookups by owner rank (row % shard_count)
-// and resolves them to local rows (row / shard_count): owner g receives, for every bag, only
-// the int32 local rows it has to read, in lookup order.  Two passes of the same walk, half a
-// warp per bag: COUNT writes cnt[(g * tables + t) * batch + s]; after an exclusive scan of
-// that array (positions, with one extra closing entry) SCATTER writes the local rows at
-// pos[(g * tables + t) * batch + s] + (rank of the lookup among the bag's lookups of owner g)
-// and the owner mask of the bag.  Lane g of the group keeps the running count of owner g.
-template <bool SCATTER>
-__global__ void __launch_bounds__(256)
-bag_partition_kernel(BagParams p, int tables_total, int t0, int* __restrict__ cnt_or_pos,
-                     int* __restrict__ rows_out, unsigned* __restrict__ mask) {
-  const int lane = threadIdx.x & 15;
-  const int shift = threadIdx.x & 16;
-  const unsigned gmask = 0xffffu << shift;
-  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
-  const long long total = (long long)p.num_tables * p.batch;
-  if (group >= total) return;
-  const int t = (int)(group / p.batch);
-  const long long s = group - (long long)t * p.batch;
-  const BagTableDev& T = p.t[t];
-  const int G = p.shard_count;
-  const int start = T.given_off[s], end = T.given_off[s + 1];
-  const long long slot = ((long long)lane * tables_total + (t0 + t)) * p.batch + s;  // lane = owner
-  int run = 0;
-  int my_pos = (SCATTER && lane < G) ? cnt_or_pos[slot] : 0;
-  for (int base = start; base < end; base += 16) {
-    const int i = base + lane;
-    int owner = -1, local = -1;
-    if (i < end) {
-      const long long r = load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic);
-      if (r >= 0 && (unsigned long long)r <= 0xffffffffull) {
-        const unsigned b = (unsigned)r, q = b / (unsigned)G;
-        owner = (int)(b - q * (unsigned)G);
-        local = (int)q;
-      } else if (r >= 0) {
-        owner = (int)(r % G);
-        const long long q = r / G;
-        local = q > 0x7fffffffLL ? 0x7fffffff : (int)q;  // past any table: flagged by the owner
-      } else {
-        owner = 0;  // a negative row goes to rank 0 as -1, which flags it
-      }
-    }
-    for (int g = 0; g < G; ++g) {
-      const unsigned m = (__ballot_sync(gmask, owner == g) >> shift) & 0xffffu;
-      if (SCATTER) {
-        const int first = __shfl_sync(gmask, my_pos + run, g, 16);
-        if (owner == g) rows_out[first + __popc(m & ((1u << lane) - 1u))] = local;
-      }
-      if (lane == g) run += __popc(m);
-    }
-  }
-  if (!SCATTER) {
-    if (lane < G) cnt_or_pos[slot] = run;
-  } else {
-    const unsigned m = (__ballot_sync(gmask, lane < G && run > 0) >> shift) & 0xffffu;
-    if (lane == 0) mask[(long long)(t0 + t) * p.batch + s] = m;
-  }
-}
-
-// Pull step of the exchange: copies from every peer the positions and local rows it prepared
-// for this rank.  Source q's arrays are read through peer-mapped pointers with plain loads;
-// rows keep their index, so positions stay valid in the copy.  blockIdx.y = source.
-struct PullParams {
-  const int* pos[32];   // source q: positions, int32[shards * per_rank + 1]
-  const int* rows[32];  // source q: local rows
-  int* pos_out[32];     // int32[per_rank + 1]
-  int* rows_out[32];    // indexed like rows[q]
-  long long per_rank;   // tables * batch
-  int me;
-};
-__global__ void __launch_bounds__(256)
-bag_pull_kernel(PullParams a) {
-  const int q = blockIdx.y;
-  const int* __restrict__ pos = a.pos[q] + (long long)a.me * a.per_rank;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  for (long long i = tid; i <= a.per_rank; i += stride) a.pos_out[q][i] = pos[i];
-  const int lo = pos[0], hi = pos[a.per_rank];
-  const int* __restrict__ src = a.rows[q];
-  int* __restrict__ dst = a.rows_out[q];
-  // 16-byte body between the aligned bounds, scalar head and tail
-  const int lo4 = (lo + 3) & ~3, hi4 = hi & ~3;
-  const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
-  if (!aligned || lo4 >= hi4) {
-    for (long long i = lo + tid; i < hi; i += stride) dst[i] = src[i];
-    return;
-  }
-  for (long long i = lo + tid; i < lo4; i += stride) dst[i] = src[i];
-  for (long long i = hi4 + tid; i < hi; i += stride) dst[i] = src[i];
-  const int4* s4 = reinterpret_cast<const int4*>(src);
-  int4* d4 = reinterpret_cast<int4*>(dst);
-  for (long long i = lo4 / 4 + tid; i < hi4 / 4; i += stride) d4[i] = s4[i];
 }
 
 // Any dim (not a multiple of 4, or unaligned tables): one warp per bag, lanes
@@ -708,88 +582,6 @@ unique_rows_kernel(const float* table, long long rows, long long dim, const long
       continue;
     }
     for (long long c = lane; c < dim; c += 32) out[u * dim + c] = __ldg(table + r * dim + c);
-  }
-}
-
-// ---- exclusive scan of int32 (three passes, 2048 items per block) ---------------
-constexpr int kScanThreads = 512;
-constexpr int kScanItems = 4;
-constexpr int kScanTile = kScanThreads * kScanItems;
-
-__device__ __forceinline__ int block_exclusive_scan(int v, int* total_out) {
-  __shared__ int warp_sums[32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int x = v;
-  for (int o = 1; o < 32; o <<= 1) {
-    int y = __shfl_up_sync(0xffffffffu, x, o);
-    if (lane >= o) x += y;
-  }
-  if (lane == 31) warp_sums[warp] = x;
-  __syncthreads();
-  if (warp == 0) {
-    int w = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0;
-    for (int o = 1; o < 32; o <<= 1) {
-      int y = __shfl_up_sync(0xffffffffu, w, o);
-      if (lane >= o) w += y;
-    }
-    warp_sums[lane] = w;
-  }
-  __syncthreads();
-  const int warp_off = warp == 0 ? 0 : warp_sums[warp - 1];
-  if (total_out) *total_out = warp_sums[(blockDim.x >> 5) - 1];
-  const int r = warp_off + x - v;
-  __syncthreads();
-  return r;
-}
-
-__global__ void __launch_bounds__(kScanThreads)
-scan_tile_sums_kernel(const int* in, long long n, int* tile_sums) {
-  const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * kScanItems;
-  int s = 0;
-#pragma unroll
-  for (int k = 0; k < kScanItems; ++k)
-    if (base + k < n) s += in[base + k];
-  int total;
-  block_exclusive_scan(s, &total);
-  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
-}
-
-// One block walks all tile sums with a running carry; tile_sums becomes exclusive
-// offsets and *grand_total the overall sum.
-__global__ void __launch_bounds__(kScanThreads)
-scan_tile_offsets_kernel(int* tile_sums, long long ntiles, int* grand_total) {
-  __shared__ int carry;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
-  for (long long base = 0; base < ntiles; base += kScanThreads) {
-    const long long i = base + threadIdx.x;
-    const int v = i < ntiles ? tile_sums[i] : 0;
-    int total;
-    const int ex = block_exclusive_scan(v, &total);
-    const int c = carry;
-    if (i < ntiles) tile_sums[i] = c + ex;
-    __syncthreads();
-    if (threadIdx.x == 0) carry = c + total;
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) *grand_total = carry;
-}
-
-__global__ void __launch_bounds__(kScanThreads)
-scan_apply_kernel(const int* in, long long n, const int* tile_offsets, int* out) {
-  const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * kScanItems;
-  int v[kScanItems];
-  int s = 0;
-#pragma unroll
-  for (int k = 0; k < kScanItems; ++k) {
-    v[k] = base + k < n ? in[base + k] : 0;
-    s += v[k];
-  }
-  int ex = block_exclusive_scan(s, nullptr) + tile_offsets[blockIdx.x];
-#pragma unroll
-  for (int k = 0; k < kScanItems; ++k) {
-    if (base + k < n) out[base + k] = ex;
-    ex += v[k];
   }
 }
 

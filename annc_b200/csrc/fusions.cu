@@ -323,7 +323,8 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
 __global__ void __launch_bounds__(256)
 synth_fill_rows_kernel(float* __restrict__ table, long long local_rows, int dim4,
                        unsigned long long seed, unsigned long long table_id,
-                       unsigned long long first_row, unsigned long long row_step) {
+                       unsigned long long first_row, unsigned long long row_step,
+                       const long long* __restrict__ row_list) {
   const long long total = local_rows * dim4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const unsigned long long base = seed ^ (table_id * 0x9E3779B97F4A7C15ull);
@@ -331,7 +332,8 @@ synth_fill_rows_kernel(float* __restrict__ table, long long local_rows, int dim4
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
     const long long i = e / dim4;
     const int c0 = (int)(e - i * dim4) * 4;
-    const unsigned long long row = first_row + (unsigned long long)i * row_step;
+    const unsigned long long row = row_list ? (unsigned long long)row_list[i]
+                                            : first_row + (unsigned long long)i * row_step;
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -466,7 +468,20 @@ int annc_synth_fill_rows_dev(float* table, int64_t local_rows, int64_t dim, uint
   if (local_rows == 0) return ANNC_OK;
   synth_fill_rows_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       table, local_rows, (int)(dim / 4), seed, (unsigned long long)table_id,
-      (unsigned long long)first_row, (unsigned long long)row_step);
+      (unsigned long long)first_row, (unsigned long long)row_step, nullptr);
+  ANNC_CUDA(cudaGetLastError());
+  return ANNC_OK;
+}
+
+int annc_synth_fill_row_list_dev(float* table, const int64_t* rows, int64_t count, int64_t dim,
+                                 uint64_t seed, int64_t table_id, void* stream) {
+  ANNC_REQUIRE(table && rows && count >= 0 && dim >= 4 && (dim & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(table) & 15) == 0,
+               ANNC_ERR_INVALID_ARGUMENT, "synth fill: bad arguments");
+  if (count == 0) return ANNC_OK;
+  synth_fill_rows_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      table, count, (int)(dim / 4), seed, (unsigned long long)table_id, 0ull, 1ull,
+      reinterpret_cast<const long long*>(rows));
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
 }

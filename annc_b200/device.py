@@ -250,45 +250,6 @@ def sum_partials_masked(src_ptr: int, mask: torch.Tensor, parts: int, part_strid
                                            C.c_int64(out_stride), C.c_int(int(out_bf16)), _stream()))
 
 
-class BagPartition:
-    """annc_embed_bag_partition_dev over fixed buffers: splits this rank's lookups by owner.
-    entries: (ids_ptr, nnz, num_buckets, offsets_ptr) per table; positions_ptr / rows_ptr are the
-    (peer-readable) outputs."""
-
-    def __init__(self, entries, batch: int, shard_count: int, positions_ptr: int, rows_ptr: int,
-                 device: torch.device, id_kind: int = 2):
-        self.n, self.batch, self.shard_count, self.id_kind = len(entries), batch, shard_count, id_kind
-        self.desc = (BagTable * self.n)()
-        for i, (ip, nnz, nb, op) in enumerate(entries):
-            d = self.desc[i]
-            d.ids, d.nnz, d.num_buckets, d.offsets = ip, int(nnz), int(nb), op
-        self.positions_ptr, self.rows_ptr = positions_ptr, rows_ptr
-        self.mask = torch.zeros(self.n * batch, dtype=torch.int32, device=device)
-        self.scratch_bytes = int(lib.annc_embed_bag_partition_scratch_bytes(self.n, batch, shard_count))
-        self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=device)
-
-    def run(self) -> None:
-        check(lib.annc_embed_bag_partition_dev(
-            self.desc, C.c_int(self.n), C.c_int(self.id_kind), C.c_int64(self.batch),
-            C.c_int(self.shard_count), C.c_void_p(self.positions_ptr), C.c_void_p(self.rows_ptr),
-            C.c_void_p(self.mask.data_ptr()), C.c_void_p(self.scratch.data_ptr()),
-            C.c_size_t(self.scratch_bytes), _stream()))
-
-
-class BagPull:
-    """annc_embed_bag_pull_dev: this rank's slice of every source's positions and local rows."""
-
-    def __init__(self, peer_pos, peer_rows, me: int, per_rank: int, pos_out, rows_out):
-        n = len(peer_pos)
-        arr = lambda v: (C.c_void_p * n)(*[C.c_void_p(int(x)) for x in v])
-        self.n, self.me, self.per_rank = n, me, per_rank
-        self.a = (arr(peer_pos), arr(peer_rows), arr(pos_out), arr(rows_out))
-
-    def run(self) -> None:
-        check(lib.annc_embed_bag_pull_dev(self.a[0], self.a[1], C.c_int(self.n), C.c_int(self.me),
-                                          C.c_int64(self.per_rank), self.a[2], self.a[3], _stream()))
-
-
 class PeerBuffers:
     """One receive buffer per rank, mapped into every rank (annc_peer_buffer_*).  `local` is
     this rank's buffer, `ptrs[p]` the address under which rank p's buffer is seen here.

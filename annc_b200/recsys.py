@@ -4,9 +4,10 @@ ReLU epilogues and a final sigmoid.  The tables are filled on the device, shard 
 a counter-based hash (annc_synth_fill_rows_dev), so no host copy of the 655 GB exists; the CPU
 oracle regenerates the rows it needs (synth.hashed_table_rows).
 
-Step: prepass + partition of the rank's lookups -> peer pull -> bag kernel storing partial sums
-into the owners' receive buffers -> masked rank-order sum * 1/len, written as bf16 straight into
-the MLP input -> tcgen05 BF16 GEMMs (bf16 activations between layers) -> fp32 last layer.
+Step (row mode): the library's row exchange (lookups split by owner at their source, owners pool
+their lists and store partial sums into the sample owner's memory, masked rank-order sum * 1/len
+written as bf16 straight into the MLP input) -> tcgen05 BF16 GEMMs (bf16 activations between
+layers) -> fp32 last layer.
 """
 from __future__ import annotations
 
@@ -25,9 +26,11 @@ from .synth import RecsysModel
 
 class RecsysPipeline:
     def __init__(self, model: RecsysModel, device: torch.device, keep_host_inputs: bool = False,
-                 shard: str = "row"):
+                 shard: str = "row", hot_rows: int = 0):
         """shard: "row" (mod rule, partial sums stored into the sample owner's memory) or "table"
-        (whole tables per rank, finished pooled vectors stored into the sample owner's memory)."""
+        (whole tables per rank, finished pooled vectors stored into the sample owner's memory).
+        hot_rows > 0 (row mode): the rows of each table's `hot_rows` most popular ids are
+        replicated on every rank (generated from the same hash) and pooled where the sample is."""
         assert shard in ("row", "table")
         world, rank = dist.get_world_size(), dist.get_rank()
         self.world, self.rank, self.device, self.shard = world, rank, device, shard
@@ -76,9 +79,20 @@ class RecsysPipeline:
         nnz_all = [None] * world
         dist.all_gather_object(nnz_all, nnz)
         if shard == "row":
+            hot = None
+            if hot_rows > 0:
+                hot = []
+                for t in range(T):
+                    hr = up(model.bags[t].popular_rows(hot_rows, R))
+                    tab = torch.empty((hr.shape[0], D), dtype=torch.float32, device=device)
+                    check(lib.annc_synth_fill_row_list_dev(C.c_void_p(tab.data_ptr()), C.c_void_p(hr.data_ptr()),
+                                                           C.c_int64(hr.shape[0]), C.c_int64(D),
+                                                           C.c_uint64(model.seed), C.c_int64(t), s))
+                    hot.append((tab, hr if hr.shape[0] < R else None))
             self.bags = RowShardedBags(world, rank, device, [self.table_mem[t] for t in range(T)],
                                        [self.local_rows] * T, [R] * T, B, D, np.array(nnz_all),
-                                       [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=1)
+                                       [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=1,
+                                       hot=hot)
         else:
             plan = ShardPlan("table", world, rank, [R] * T, np.array(nnz_all))
             assert plan.owned[rank] == self.owned

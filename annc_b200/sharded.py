@@ -1,23 +1,20 @@
 """Multi-GPU embedding step of the DLRM-style pipeline: one process per GPU.
 
-Three partitionings of the tables, the MLPs always run on the rank's own batch slice
-(no collective in the MLP):
+Partitionings of the tables; the MLPs always run on the rank's own batch slice (no collective
+in the MLP):
 
   row      every table row-sharded with the reference's mod rule
            (owner = bucket % G, local row = bucket / G,
-           annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71).
-           Each rank splits its own lookups by owner and resolves them to int32 local rows
-           (annc_embed_bag_partition_dev); the owners pull their slices through peer-mapped
-           pointers, pool them, and the bag kernel stores each partial sum straight into the
-           memory of the rank that owns the sample (annc_peer_buffer_*): pooling and
-           exchange are one kernel, and nothing is computed or sent for a (bag, rank) pair
-           without lookups.  One-element all-reduces order the steps; the owner adds the
-           parts in rank order.
-  row_gather  the same fused stores, but raw ids and bag offsets are all-gathered and every
-           rank filters the global batch's ids itself (G times the id work per rank).
-  row_nccl the all-gathered ids with the exchange as a separate step: partial sums are
-           written locally, then go through an NCCL all-to-all (the baseline the fused
-           step is measured against).
+           annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71), optionally
+           with a small replicated set of hot rows per table.  The whole step protocol lives in
+           the library (annc_row_exchange_*, mirrored by annc_b200/row_exchange.py): lookups are
+           split by owner at their source, the owners read their lists through peer-mapped
+           pointers, pool them and store each partial sum straight into the memory of the rank
+           that owns the sample; flags in peer memory order the ranks (no NCCL call on the
+           data path); the owner adds the parts in rank order.
+  row_nccl the baseline the fused step is measured against: raw ids and bag offsets are
+           all-gathered, every rank pools the lookups it owns, and the partial sums go through
+           an NCCL all-to-all.
   table    whole tables per rank (contiguous blocks); the owners fetch the ids and bag offsets
            of their tables through peer-mapped pointers and the bag kernel stores finished
            pooled vectors into the sample owner's memory (TableShardedBags); no add.
@@ -38,7 +35,7 @@ class ShardPlan:
     """Sizes and offsets of the exchange.  nnz[s][t] = lookups of rank s in table t."""
 
     def __init__(self, mode: str, world: int, rank: int, table_rows: List[int], nnz: np.ndarray):
-        assert mode in ("row", "row_gather", "row_nccl", "table", "table_nccl", "replica")
+        assert mode in ("row", "row_nccl", "table", "table_nccl", "replica")
         self.mode, self.world, self.rank = mode, world, rank
         self.table_rows = list(table_rows)
         self.T = len(table_rows)
@@ -84,123 +81,106 @@ class ShardPlan:
         return int(sum(rc[:s]) + self.nnz[s, mine[:j]].sum())
 
 
-def partition_lookups(raw_ids, seg_ids, table_rows: int, batch: int, shards: int):
-    """Host statement of what annc_embed_bag_partition_dev computes for one table (the GPU
-    tests compare the kernel with it; the gloo CPU test runs the exchange protocol on it):
-    bucket = uint64(id) % table_rows, owner = bucket % shards, local row = bucket // shards.
-    Returns counts int64[shards, batch] and, per owner, the int32 local rows in lookup order
-    (segment ids are sorted, so that is bag by bag)."""
+def partition_lookups(raw_ids, seg_ids, table_rows: int, shards: int, source: int = 0, hot_rows=None,
+                      local_rows_of_source: int = 0):
+    """Host statement of the split the row exchange makes for one table of one source rank
+    (the GPU tests compare the library with it; the gloo CPU test runs the protocol on it):
+    bucket = uint64(id) % table_rows; a bucket in `hot_rows` (ascending) stays with the source
+    at local row local_rows_of_source + (index in hot_rows); otherwise owner = bucket % shards
+    and local row = bucket // shards.  Returns per owner the records (local row, segment id)
+    in lookup order."""
     bucket = (np.asarray(raw_ids).view(np.uint64) % np.uint64(table_rows)).astype(np.int64)
     owner, local = bucket % shards, bucket // shards
-    counts = np.zeros((shards, batch), np.int64)
-    rows = []
-    for g in range(shards):
-        sel = owner == g
-        np.add.at(counts[g], np.asarray(seg_ids)[sel], 1)
-        rows.append(local[sel].astype(np.int32))
-    return counts, rows
+    if hot_rows is not None and len(hot_rows):
+        hot_rows = np.asarray(hot_rows, np.int64)
+        idx = np.searchsorted(hot_rows, bucket)
+        idx_c = np.minimum(idx, len(hot_rows) - 1)
+        is_hot = hot_rows[idx_c] == bucket
+        owner = np.where(is_hot, source, owner)
+        local = np.where(is_hot, local_rows_of_source + idx_c, local)
+    seg = np.asarray(seg_ids, np.int64)
+    return [(local[owner == g].astype(np.int32), seg[owner == g]) for g in range(shards)]
 
 
 class RowShardedBags:
-    """Embedding bags over row-sharded tables, one process per GPU of one node, with the
-    lookups split at their source (see the module docstring, mode `row`).
+    """Embedding bags over row-sharded tables, one process per GPU of one node: the torch side
+    of annc_row_exchange_* (peer buffers allocated and exchanged here, every step phase in the
+    library).  prefetch(i) splits input set i by owner and publishes the lists; run(i, out)
+    pools the lists meant for this rank, storing the partial sums into the owners' memory, and
+    adds the parts of this rank's batch into `out` (f32, or bf16 with out_bf16) as
+    [batch, tables, dim] rows of `out_stride` elements.
 
-    Per step: prefetch(i) runs the prepass and the partition of input set i and starts the
-    barrier that tells the peers their slices are ready; run(i, out) pulls this rank's slices,
-    pools them with the bag kernel storing into the owners' receive buffers, waits for every
-    rank's kernel, and adds the parts of this rank's batch in rank order into `out`
-    (f32, or bf16 with out_bf16) as [batch, tables, dim] rows of `out_stride` elements.
-    The receive buffers alternate between steps, so a peer may start storing step i + 1 while
-    this rank still adds step i; positions and local rows are single-buffered because every
-    peer has pulled them before it joins the step's second barrier."""
+    hot: optional per-table (hot_table f32[h, dim] tensor, hot_rows i64[h] tensor or None for
+    "all rows") of replicated rows; None or (None, None) = none."""
 
     def __init__(self, world: int, rank: int, device, local_tables, local_rows, table_rows, batch: int,
-                 dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2):
+                 dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2, hot=None):
         import torch
         import torch.distributed as dist
 
         from . import device as dev
-        self.dist, self.dev, self.torch = dist, dev, torch
-        self.world, self.rank, self.device = world, rank, device
-        T, B, D = len(local_tables), batch, dim
-        self.T, self.B, self.D, self.combiner = T, B, D, combiner
-        TB = T * B
+        from . import row_exchange as rx
+        self.rx, self.dist, self.torch = rx, dist, torch
+        self.world, self.rank = world, rank
+        T = len(local_tables)
+        self.T, self.B, self.D = T, batch, dim
         nnz_all = np.asarray(nnz_all, np.int64).reshape(world, T)
-        L = (max(1, int(nnz_all.sum(axis=1).max())) + 3) // 4 * 4  # rows of rows_in stay 16-byte aligned
-        self.sets = []
-        for st in id_sets:
-            self.sets.append(dict(prepass=dev.BagPrepass(st["segs"], B), ids=st["ids"]))
-        wsb = self.sets[0]["prepass"].ws_bytes
-        self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=device)
-        self.part_bytes = part_bytes = B * T * D * 4
-        up256 = lambda n: (n + 255) // 256 * 256
-        off_pos = 2 * world * part_bytes          # after the two receive buffers [world, B, T, D]
-        off_rows = off_pos + up256((world * TB + 1) * 4)
-        self.peer = dev.PeerBuffers(off_rows + up256(L * 4), world, rank)
-        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
-        pos_of = lambda q: self.peer.ptrs[q] + off_pos
-        rows_of = lambda q: self.peer.ptrs[q] + off_rows
-        off_ptr = lambda t: self.off_ws.data_ptr() + 512 + t * (B + 1) * 4
-        my_nnz = nnz_all[rank]
-        for st in self.sets:
-            st["partition"] = dev.BagPartition(
-                [(st["ids"][t].data_ptr(), int(my_nnz[t]), int(table_rows[t]), off_ptr(t)) for t in range(T)],
-                B, world, pos_of(rank), rows_of(rank), device, id_kind=id_kind)
-        i32 = dict(dtype=torch.int32, device=device)
-        self.pos_in = torch.zeros((world, TB + 1), **i32)
-        self.rows_in = torch.zeros((world, L), **i32)
-        srcs = [q for q in range(world) if q != rank]
-        self.pull = dev.BagPull([pos_of(q) for q in srcs], [rows_of(q) for q in srcs], rank, TB,
-                                [self.pos_in[q].data_ptr() for q in srcs],
-                                [self.rows_in[q].data_ptr() for q in srcs]) if srcs else None
-        self.launches = []
-        for buf in range(2):
-            entries = []
-            for s in range(world):
-                if s == rank:  # own lookups are read in place
-                    ids_ptr, pos_ptr = rows_of(rank), pos_of(rank) + rank * TB * 4
-                else:
-                    ids_ptr, pos_ptr = self.rows_in[s].data_ptr(), self.pos_in[s].data_ptr()
-                for t in range(T):
-                    entries.append((local_tables[t].data_ptr(), int(local_rows[t]), 1, ids_ptr, None, L,
-                                    self.peer.ptrs[s] + (buf * world + rank) * part_bytes + t * D * 4,
-                                    pos_ptr + t * B * 4))
-            self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, device, id_kind=0,
-                                               shard_count=1, shard_rank=0, exchange=True))
-        self.step = 0
-        self.launches_per_step = 2 * ((len(entries) + 119) // 120) + 8
-        self.exchange_bytes = (world - 1) * (part_bytes + TB * 4) + L * 4
-        self._work = None
-        self._partition = None
+        tabs = []
+        self.hot_bytes = 0
+        for t in range(T):
+            h_tab, h_rows = (hot[t] if hot is not None and hot[t] is not None else (None, None))
+            h_count = int(h_tab.shape[0]) if h_tab is not None else 0
+            self.hot_bytes += h_count * dim * 4
+            tabs.append(dict(shard=local_tables[t].data_ptr() if int(local_rows[t]) > 0 else 0,
+                             local_rows=int(local_rows[t]), rows=int(table_rows[t]),
+                             hot=h_tab.data_ptr() if h_count else 0,
+                             hot_rows=h_rows.data_ptr() if (h_count and h_rows is not None) else 0,
+                             hot_count=h_count))
+        self._keep = (list(local_tables), hot)
+        cfg, keep = rx.make_config(world, rank, tabs, dim, batch,
+                                   max(1, int(nnz_all.sum(axis=1).max())), max(1, int(nnz_all.max())),
+                                   combiner=combiner, id_kind=id_kind)
+        self.peer = dev.PeerBuffers(rx.peer_bytes(cfg), world, rank)
+        self.ex = rx.RowExchange(cfg, keep, self.peer.ptrs)
+        if world > 1:
+            dist.barrier()  # every rank's flags are cleared before anybody's first step
+        self.inputs = [rx.StepInputs([x.data_ptr() for x in st["ids"]], [x.data_ptr() for x in st["segs"]],
+                                     [int(x.shape[0]) for x in st["ids"]]) for st in id_sets]
+        self.ncols = int(id_sets[0]["segs"][0].shape[1])
+        self.launches_per_step = 12 + (1 if combiner == 1 else 0)
+        self.exchange_bytes = 0  # measured: see exchange_stats()
+        self._begun = False
 
     def prefetch(self, set_index: int) -> None:
-        st = self.sets[set_index]
-        st["prepass"].run(self.off_ws)
-        self._partition = st["partition"]
-        self._partition.run()
-        self._work = self.dist.all_reduce(self.flag, async_op=True)  # every rank has split its lookups
+        self.ex.begin(self.inputs[set_index], self.ncols, 0)
+        self._begun = True
 
     def run(self, set_index: int, out_ptr: int, out_stride: int, out_bf16: bool = False) -> None:
-        if self._work is None:
+        if not self._begun:
             self.prefetch(set_index)
-        self._work.wait()
-        self._work = None
-        buf = self.step % 2
-        self.step += 1
-        if self.pull is not None:
-            self.pull.run()              # my slices of the peers' positions and local rows
-        self.launches[buf].run()         # partial sums land in their owners' memory
-        self.dist.all_reduce(self.flag)  # every rank's bag kernel has finished
-        self.dev.sum_partials_masked(
-            self.peer.local + buf * self.world * self.part_bytes, self._partition.mask, self.world,
-            self.B * self.T * self.D, self.B, self.T, self.D, out_ptr, out_stride,
-            mean_offsets_ptr=(self.off_ws.data_ptr() + 512) if self.combiner == 1 else None,
-            out_bf16=out_bf16)
+        self._begun = False
+        self.ex.pool()
+        self.ex.finish(out_ptr, out_stride, out_bf16)
+
+    def exchange_stats(self) -> dict:
+        """Last step: records pooled per source, parts received per owner, and the bytes that
+        crossed NVLink into and out of this rank (records read from peers, parts stored)."""
+        recs, parts = self.ex.stats()
+        remote_recs = sum(r for q, r in enumerate(recs) if q != self.rank)
+        remote_parts = sum(p for q, p in enumerate(parts) if q != self.rank)
+        self.exchange_bytes = remote_recs * 8 + remote_parts * self.D * 4
+        return dict(records_per_source=recs, parts_per_owner=parts, remote_records=remote_recs,
+                    remote_parts_received=remote_parts, remote_parts_per_bag=remote_parts / (self.B * self.T),
+                    nvlink_bytes=self.exchange_bytes, hot_bytes=self.hot_bytes)
 
     def error_bits(self) -> int:
-        return self.launches[0].error_bits() | self.launches[1].error_bits()
+        return self.ex.error_bits()
 
     def close(self) -> None:
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()  # nobody still reads or writes a peer's buffer
+        self.ex.destroy()
         self.peer.close()
 
 
@@ -316,7 +296,7 @@ class ShardedDlrmPipeline:
         return _make_pipeline(*args, **kwargs)
 
 
-def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool = False):
+def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool = False, hot_rows: int = 0):
     import torch
     import torch.distributed as dist
 
@@ -343,7 +323,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "row":
                 self._setup_row_partitioned(m, plan)
                 return
-            if mode in ("row_gather", "row_nccl"):
+            if mode == "row_nccl":
                 # Only the raw ids (8 bytes per lookup) and the bag offsets of each rank's
                 # batch travel: every rank runs the prepass on its own index matrices and
                 # the offsets (4 bytes per bag) are gathered with the ids.
@@ -357,41 +337,19 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 self.off_ws = torch.zeros(wsb, dtype=torch.uint8, device=self.device)
                 self.off_g = torch.zeros((world, wsb), dtype=torch.uint8, device=self.device)
                 part_bytes = B * T * D * 4
-                if mode == "row_gather":
-                    # Two receive buffers [world, B, T, D] used on alternate steps: a peer may
-                    # start storing step i+1 while this rank still adds the parts of step i.
-                    self.peer = dev.PeerBuffers(2 * world * part_bytes, world, rank)
-                    self.flag = torch.zeros(1, **f32)
-                    out_of = lambda buf, s: self.peer.ptrs[s] + (buf * world + rank) * part_bytes
-                    nbuf = 2
-                else:
-                    self.partial = torch.empty((world, B, T, D), **f32)
-                    self.recv = torch.empty((world, B, T, D), **f32)
-                    out_of = lambda buf, s: self.partial.data_ptr() + s * part_bytes
-                    nbuf = 1
-                self.launches = []
-                for buf in range(nbuf):
-                    entries = []
-                    for s in range(world):
-                        for t in range(T):
-                            off = plan.gathered_offset(s, t)
-                            entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
-                                            plan.table_rows[t],
-                                            self.ids_g.data_ptr() + (s * L + off) * 8, None,
-                                            int(plan.nnz[s, t]), out_of(buf, s) + t * D * 4,
-                                            self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
-                    self.launches.append(dev.BagLaunch(entries, D, B, 2, T * D, self.device,
-                                                       shard_count=world, shard_rank=rank,
-                                                       exchange=(mode == "row_gather")))
-                if mode == "row_gather":
-                    # which ranks write a part for each bag of this rank's own batch
-                    for st in self.sets:
-                        st["owners"] = dev.OwnerMask(
-                            [(st["ids"][t].data_ptr(), self.nnz[t], plan.table_rows[t],
-                              self.off_ws.data_ptr() + 512 + t * (B + 1) * 4) for t in range(T)],
-                            B, world, self.device)
-                self.launch = self.launches[0]
-                self._row_step = 0
+                self.partial = torch.empty((world, B, T, D), **f32)
+                self.recv = torch.empty((world, B, T, D), **f32)
+                entries = []
+                for s in range(world):
+                    for t in range(T):
+                        off = plan.gathered_offset(s, t)
+                        entries.append((self.tables[t].data_ptr(), plan.local_rows(t),
+                                        plan.table_rows[t],
+                                        self.ids_g.data_ptr() + (s * L + off) * 8, None,
+                                        int(plan.nnz[s, t]), self.partial.data_ptr() + s * part_bytes + t * D * 4,
+                                        self.off_g.data_ptr() + s * wsb + 512 + t * (B + 1) * 4))
+                self.launch = dev.BagLaunch(entries, D, B, 2, T * D, self.device,
+                                            shard_count=world, shard_rank=rank)
                 self.embed_launches = 2 * ((len(entries) + 119) // 120) + 2
                 self.exchange_bytes = (world - 1) * (B * T * D * 4 + L * 8 + wsb)
                 self._works = None
@@ -440,13 +398,27 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
         def _setup_row_partitioned(self, m, plan) -> None:
             emb = m.emb
             self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
+            hot = None
+            if hot_rows > 0:
+                # the replicated hot set: the rows of each table's most popular ids (the
+                # table's own popularity map, identical on every rank)
+                hot = []
+                for t, (tab, bag) in enumerate(zip(emb.tables, emb.bags)):
+                    rows_t = tab.shape[0]
+                    hr = bag.popular_rows(hot_rows, rows_t)
+                    if hr.shape[0] == 0:
+                        hot.append(None)
+                    elif hr.shape[0] == rows_t:
+                        hot.append((self._up(tab), None))
+                    else:
+                        hot.append((self._up(tab[hr]), self._up(hr)))
             self.rowbags = RowShardedBags(
                 world, rank, self.device, self.tables, [plan.local_rows(t) for t in range(self.T)],
                 plan.table_rows, self.batch, self.dim, plan.nnz,
-                [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=0)
+                [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=0, hot=hot)
             self.peer = self.rowbags.peer
             self.embed_launches = self.rowbags.launches_per_step
-            self.exchange_bytes = self.rowbags.exchange_bytes
+            self.exchange_bytes = 0
 
         def embed(self) -> None:
             plan = self.shard
@@ -456,22 +428,12 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "row":
                 self.rowbags.run(self.cur, self.z.data_ptr() + D * 4, F * D)
                 return
-            if mode in ("row_gather", "row_nccl"):
+            if mode == "row_nccl":
                 if self._works is None:
                     self.embed_prefetch()
                 for w in self._works:
                     w.wait()
                 self._works = None
-                if mode == "row_gather":
-                    buf = self._row_step % 2
-                    self._row_step += 1
-                    self.launch = self.launches[buf]
-                    self.launch.run()           # partial sums land in their owners' memory
-                    dist.all_reduce(self.flag)  # every rank's bag kernel has finished
-                    dev.sum_partials_masked(self.peer.local + buf * world * B * T * D * 4,
-                                            self._owners.mask, world, B * T * D, B, T, D,
-                                            self.z.data_ptr() + D * 4, F * D)
-                    return
                 self.launch.run()
                 dist.all_to_all_single(self.recv, self.partial)
                 dev.sum_partials(self.recv, world, B * T * D, B, T * D, T * D,
@@ -501,22 +463,19 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 off += self.back_counts[p]
 
         def embed_prefetch(self) -> None:
-            """Row mode: starts the gathers of ids and bag offsets; the bottom MLP runs
-            while they are in flight."""
+            """Starts the exchange (row: split + publish; table: ids into peer-visible memory;
+            row_nccl: the gathers of ids and bag offsets); the bottom MLP runs beside it."""
             if mode == "row":
                 self.rowbags.prefetch(self.cur)
                 return
             if mode == "table":
                 self.tbags.prefetch(self.cur)
                 return
-            if mode not in ("row_gather", "row_nccl"):
+            if mode != "row_nccl":
                 return
             n = self.nnz_total
             self.ids_pad[:n].copy_(self.ids_all)
             self.sets[self.cur]["prepass"].run(self.off_ws)
-            if mode == "row_gather":
-                self._owners = self.sets[self.cur]["owners"]
-                self._owners.run()
             self._works = [dist.all_gather_into_tensor(self.ids_g, self.ids_pad, async_op=True),
                            dist.all_gather_into_tensor(self.off_g, self.off_ws, async_op=True)]
 
@@ -527,9 +486,15 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                 return self.rowbags.error_bits()
             if mode == "table":
                 return self.tbags.error_bits()
-            if mode == "row_gather":
-                return self.launches[0].error_bits() | self.launches[1].error_bits()
             return self.launch.error_bits() if self.launch is not None else 0
+
+        def close_exchange(self) -> None:
+            """Releases the peer mappings (collective: every rank calls it)."""
+            torch.cuda.synchronize()
+            if mode == "row":
+                self.rowbags.close()
+            elif mode == "table":
+                self.tbags.close()
 
     return _Pipe(model, device, math=MATH_AUTO if math is None else math,
                  keep_host_inputs=keep_host_inputs)

@@ -51,23 +51,47 @@ def batch_matmul_softmax_case(seed: int = 0, b: int = 64, m: int = 256, k: int =
 @dataclass
 class BagInputs:
     """Lookups of one table: raw 64-bit ids and the COO matrix whose column 0 is the
-    sample (segment) id and column 1 the position inside the bag."""
+    sample (segment) id and column 1 the position inside the bag.  `lut` is the table's
+    popularity map: the lookup of Zipf rank r carries the id lut[r mod 2^22]."""
     raw_ids: np.ndarray      # int64[nnz], values in [0, 2^62)
     slice_input: np.ndarray  # int64[nnz, 2]
+    lut: np.ndarray | None = None
+
+    def popular_rows(self, k: int, rows: int) -> np.ndarray:
+        """Rows (hash buckets) of the k most popular ids of this table, ascending and unique:
+        the replicated hot set of a row-sharded run is chosen from them."""
+        if k <= 0:
+            return np.zeros(0, np.int64)
+        if k >= rows:
+            return np.arange(rows, dtype=np.int64)
+        ids = self.lut[1:min(k, self.lut.shape[0] - 1) + 1]
+        return np.unique((ids.view(np.uint64) % np.uint64(rows)).astype(np.int64))
 
 
-def _bag_inputs(rng: np.random.Generator, batch: int, max_bag: int, zipf_a: float) -> BagInputs:
+_LUT_BITS = 22
+
+
+def _bag_inputs(rng: np.random.Generator, batch: int, max_bag: int, zipf_a: float,
+                table_rng: np.random.Generator | None = None) -> BagInputs:
+    """`rng` draws the bag lengths and the Zipf ranks.  The rank -> id map belongs to the
+    table, not to the batch: with `table_rng` (ranks of a multi-GPU run, which draw their own
+    batches from their own `rng`) it is taken from that stream at the position the
+    single-stream form draws it, so every rank sees the same popular ids for a table."""
     lens = rng.integers(1, max_bag + 1, batch)
     nnz = int(lens.sum())
     seg = np.repeat(np.arange(batch, dtype=np.int64), lens)
     starts = np.cumsum(lens) - lens
     pos = np.arange(nnz, dtype=np.int64) - np.repeat(starts, lens)
     # uniform 62-bit values with Zipf frequencies: rank r -> a fixed random 62-bit id
-    lut = rng.integers(0, 1 << 62, 1 << 22, dtype=np.int64)
+    if table_rng is None:
+        lut = rng.integers(0, 1 << 62, 1 << _LUT_BITS, dtype=np.int64)
+    else:
+        table_rng.integers(1, max_bag + 1, batch)  # the draw that precedes the map in that stream
+        lut = table_rng.integers(0, 1 << 62, 1 << _LUT_BITS, dtype=np.int64)
     ranks = rng.zipf(zipf_a, nnz)
-    raw = lut[(ranks.astype(np.uint64) & np.uint64((1 << 22) - 1)).astype(np.int64)]
+    raw = lut[(ranks.astype(np.uint64) & np.uint64((1 << _LUT_BITS) - 1)).astype(np.int64)]
     return BagInputs(raw_ids=np.ascontiguousarray(raw),
-                     slice_input=np.ascontiguousarray(np.stack([seg, pos], axis=1)))
+                     slice_input=np.ascontiguousarray(np.stack([seg, pos], axis=1)), lut=lut)
 
 
 def _table(rng: np.random.Generator, rows: int, dim: int) -> np.ndarray:
@@ -100,10 +124,13 @@ def embedding_workload(seed: int, rows: List[int], dim: int, batch: int, max_bag
     multi-GPU run share the tables and draw their own batches)."""
     n = len(rows)
     ch = _children(seed, 2 * n)
-    bag_rngs = [ch[2 * t + 1] for t in range(n)] if input_seed is None else _children(input_seed, n)
+    own = _children(input_seed, n) if input_seed is not None else None
 
     def make(t):
-        return _table(ch[2 * t], rows[t], dim), _bag_inputs(bag_rngs[t], batch, max_bag, zipf_a)
+        if own is None:
+            return _table(ch[2 * t], rows[t], dim), _bag_inputs(ch[2 * t + 1], batch, max_bag, zipf_a)
+        return _table(ch[2 * t], rows[t], dim), _bag_inputs(own[t], batch, max_bag, zipf_a,
+                                                            table_rng=ch[2 * t + 1])
 
     with cf.ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
         res = list(ex.map(make, range(n)))
@@ -224,7 +251,14 @@ def recsys_model(seed: int = 0, tables: int = 64, rows: int = 20_000_000, dim: i
     r_mlp, r_in = root.spawn(2)
     sizes = (tables * dim,) + tuple(hidden)
     mlp = _mlp(r_mlp.spawn(2 * len(hidden)), sizes)
-    bag_rngs = (r_in if input_seed is None else np.random.default_rng(input_seed)).spawn(tables)
+    table_rngs = r_in.spawn(tables)
+    own = np.random.default_rng(input_seed).spawn(tables) if input_seed is not None else None
+
+    def make(t):
+        if own is None:
+            return _bag_inputs(table_rngs[t], batch, max_bag, zipf_a)
+        return _bag_inputs(own[t], batch, max_bag, zipf_a, table_rng=table_rngs[t])
+
     with cf.ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
-        bags = list(ex.map(lambda g: _bag_inputs(g, batch, max_bag, zipf_a), bag_rngs))
+        bags = list(ex.map(make, range(tables)))
     return RecsysModel(seed, tables, rows, dim, batch, bags, mlp)

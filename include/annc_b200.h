@@ -273,9 +273,9 @@ int annc_embed_bags_sharded_dev(const annc_bag_table* tables /* host array */, i
  * so the partial sums cross NVLink as the kernel's own stores and nothing is sent for bags
  * this rank does not contribute to.  The owner learns which parts exist from its own ids
  * (annc_embed_bag_owner_mask_dev) and adds them with annc_sum_partials_masked_dev.
- * With shard_count 1 the ids are already this rank's local rows (annc_embed_bag_partition_dev
- * ran at the source): every lookup is read and bags with offsets[s] == offsets[s + 1] are the
- * ones left unwritten. */
+ * With shard_count 1 the ids are taken as this rank's local rows: every lookup is read and
+ * bags with offsets[s] == offsets[s + 1] are the ones left unwritten.  The multi-GPU step
+ * itself is annc_row_exchange_* below, which splits the lookups at their source. */
 int annc_embed_bags_exchange_dev(const annc_bag_table* tables /* host array */, int num_tables,
                                  int64_t dim, int id_kind, int combiner, int64_t batch,
                                  int64_t out_stride, int shard_count, int shard_rank,
@@ -298,32 +298,6 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
                                  const int32_t* mean_offsets, void* out, int64_t out_stride,
                                  int out_bf16, void* stream);
 
-/* Row sharding with the ids partitioned at their source (the exchange the multi-GPU pipeline
- * uses).  The rank that owns a batch splits the lookups of every bag by owner rank
- * (row % shard_count, the mod partition of embedding_fused_sparse_dynamic_stitch.cc:70-71) and
- * resolves them to local rows (row / shard_count), keeping lookup order:
- *   positions  i32[shard_count * num_tables * batch + 1]: exclusive prefix of the per-(owner g,
- *              table t, bag s) counts in (g, t, s) order; the lookups owner g needs of bag s of
- *              table t are local_rows[positions[i] .. positions[i + 1]), i = (g * T + t) * batch + s
- *   local_rows i32[sum of nnz]
- *   owner_mask u32[num_tables * batch]: bit g set when owner g has a lookup of the bag
- * tables[t] supplies ids, nnz, num_buckets and offsets (bag offsets of the prepass).  Owner g
- * then copies its slice of both arrays from every source (annc_embed_bag_pull_dev, plain loads
- * through peer-mapped pointers), pools it with annc_embed_bags_exchange_dev (shard_count 1,
- * id_kind 0, offsets = the copied positions) straight into the sources' receive buffers, and each
- * source adds the parts named by owner_mask.  shard_count <= 16. */
-size_t annc_embed_bag_partition_scratch_bytes(int num_tables, int64_t batch, int shard_count);
-int annc_embed_bag_partition_dev(const annc_bag_table* tables /* host array */, int num_tables,
-                                 int id_kind, int64_t batch, int shard_count, int32_t* positions,
-                                 int32_t* local_rows, uint32_t* owner_mask, void* scratch,
-                                 size_t scratch_bytes, void* stream);
-/* For each source q < num_sources: positions_out[q][0 .. per_rank] = peer_positions[q][me *
- * per_rank .. (me + 1) * per_rank] and rows_out[q][i] = peer_rows[q][i] for i between the
- * first and the last of those positions (indices are kept, so the positions address the copy).
- * All four arguments are host arrays of device pointers; per_rank = num_tables * batch. */
-int annc_embed_bag_pull_dev(const int32_t* const* peer_positions, const int32_t* const* peer_rows,
-                            int num_sources, int me, int64_t per_rank, int32_t* const* positions_out,
-                            int32_t* const* rows_out, void* stream);
 /* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
  * reduce step after the all-to-all of partial sums).  src part p starts at
  * src + p * part_stride floats, rows are src_stride / out_stride floats apart. */
@@ -354,6 +328,86 @@ int annc_peer_buffer_open(const void* handle64, void** dev_ptr);
 int annc_peer_copy_dev(void* dst, const void* src, size_t bytes, void* stream);
 int annc_peer_buffer_close(void* dev_ptr);
 int annc_peer_buffer_destroy(void* dev_ptr);
+
+/* ---- Row-sharded embedding step for several GPUs of one node (one process per GPU) ----
+ * The partitioning is the reference's mod rule (owner = row % world, local row = row / world,
+ * annc/tensorflow/kernels/embedding_fused_sparse_dynamic_stitch.cc:70-71), applied to the rows
+ * of every table after the hash-bucket modulo.  The reference has no multi-device code: this
+ * object has no counterpart there beyond that rule.  Per step each rank
+ *   begin   splits the lookups of its own batch by owner rank into one record list per owner
+ *           (record = local row + bag), in lookup order, and publishes the lists;
+ *   pool    reads the lists meant for it from every rank through peer-mapped pointers, pools
+ *           them lookup by lookup and stores every finished partial sum straight into the
+ *           receive slab of the rank that owns the sample (pooling and exchange in one kernel,
+ *           ordinary 16-byte stores over NVLink, no multicast, no NCCL call);
+ *   finish  adds the parts of its own batch in rank order (deterministic; within 1e-5 relative
+ *           of the unsharded sum) and applies 1/len for the mean combiner.
+ * Ranks are ordered by flags in peer memory; every wait is bounded (2 s by default, then the
+ * error bit ANNC_ROWX_ERR_TIMEOUT is set, the kernel returns and the rank's step completes
+ * with whatever arrived).  A step allocates nothing and does not synchronise the host.
+ *
+ * Hot rows: a table may come with a replicated set of rows (every rank holds a copy).  A lookup
+ * of such a row is pooled by the rank that owns the sample and sends nothing; with skewed ids
+ * this removes most (bag, owner) pairs from the exchange.  hot_count == rows with hot_rows NULL
+ * replicates the whole table (`hot` is then the whole table).
+ *
+ * Set-up: every rank allocates annc_row_exchange_peer_bytes() with annc_peer_buffer_create,
+ * exchanges the handles over any host channel, maps the peers' buffers (annc_peer_buffer_open)
+ * and calls annc_row_exchange_create; a host-side barrier must separate the creates from the
+ * first step.  begin / pool / finish may be called one after the other (annc_row_exchange_step)
+ * or with other work of the same stream between them.  Sorted segment ids are required
+ * (ANNC_ROWX_ERR_UNSORTED otherwise). */
+typedef struct annc_row_shard_table {
+  const float* shard;       /* f32[local_rows, D]: rows r with r % world == rank, at r / world */
+  int64_t local_rows;
+  int64_t rows;             /* rows of the whole table (the modulus for id_kind 2)            */
+  const float* hot;         /* f32[hot_count, D] replicated rows in ascending row order, or NULL */
+  const int64_t* hot_rows;  /* device i64[hot_count], strictly ascending rows of the table      */
+  int64_t hot_count;
+} annc_row_shard_table;
+
+typedef struct annc_row_exchange_config {
+  int32_t world, rank, num_tables, id_kind, combiner, reserved;
+  int64_t dim, batch;                /* batch = samples of ONE rank per step                  */
+  int64_t max_lookups;               /* capacity: lookups of one rank per step, all tables    */
+  int64_t max_lookups_per_table;
+  const annc_row_shard_table* tables; /* host array [num_tables]                              */
+} annc_row_exchange_config;
+
+typedef struct annc_row_exchange annc_row_exchange;
+
+enum {
+  ANNC_ROWX_ERR_ROW = 1, ANNC_ROWX_ERR_SEGMENT = 2, ANNC_ROWX_ERR_UNSORTED = 4,
+  ANNC_ROWX_ERR_TIMEOUT = 8, ANNC_ROWX_ERR_BOUNDS = 16
+};
+
+size_t annc_row_exchange_peer_bytes(const annc_row_exchange_config* config);
+int annc_row_exchange_create(const annc_row_exchange_config* config,
+                             void* const* peer_buffers /* [world], [rank] = own */,
+                             annc_row_exchange** out);
+int annc_row_exchange_destroy(annc_row_exchange* ex);
+/* inputs: host array [num_tables]; ids, slice_input and nnz of annc_bag_table are read. */
+int annc_row_exchange_begin(annc_row_exchange* ex, const annc_bag_table* inputs, int64_t ncols,
+                            int32_t col, void* stream);
+int annc_row_exchange_pool(annc_row_exchange* ex, void* stream);
+/* out: f32 (or bf16 with out_bf16) [batch, num_tables, dim] rows of out_stride elements. */
+int annc_row_exchange_finish(annc_row_exchange* ex, void* out, int64_t out_stride, int out_bf16,
+                             void* stream);
+int annc_row_exchange_step(annc_row_exchange* ex, const annc_bag_table* inputs, int64_t ncols,
+                           int32_t col, void* out, int64_t out_stride, int out_bf16, void* stream);
+/* Synchronises `stream` and returns the ANNC_ROWX_ERR_* bits seen since the last clear;
+ * ANNC_ERR_TIMEOUT when a wait ran out. */
+int annc_row_exchange_check(annc_row_exchange* ex, void* stream, int* error_bits);
+int annc_row_exchange_clear_errors(annc_row_exchange* ex, void* stream);
+int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms);
+/* With profiling on, every step records CUDA events between its phases; phase_ms returns the
+ * last step's {split, first barrier, pool + exchange, second barrier, sum} in milliseconds. */
+int annc_row_exchange_set_profiling(annc_row_exchange* ex, int on);
+int annc_row_exchange_phase_ms(annc_row_exchange* ex, float* ms5);
+/* Last step: records this rank pooled per source rank, and the bags of its own batch each
+ * owner rank sent a part for (synchronises `stream`; a reporting aid, not for the hot loop). */
+int annc_row_exchange_stats(annc_row_exchange* ex, void* stream, int64_t* records_per_source,
+                            int64_t* parts_per_owner);
 
 /* Same operation as annc_embed_bags_dev for callers that must not allocate device
  * memory and have none to lend: code running inside a framework callback where
@@ -454,6 +508,10 @@ int annc_bf16_weight_dev(const float* b_kn, int64_t ldb, void* b_nk_bf16, int64_
  * CPU oracle regenerates any row with the same integer steps (annc_b200/synth.py). */
 int annc_synth_fill_rows_dev(float* table, int64_t local_rows, int64_t dim, uint64_t seed,
                              int64_t table_id, int64_t first_row, int64_t row_step, void* stream);
+/* The same values for an explicit list of rows (device i64[count]): table[i, :] = row rows[i].
+ * Fills the replicated hot rows of a hashed table. */
+int annc_synth_fill_row_list_dev(float* table, const int64_t* rows, int64_t count, int64_t dim,
+                                 uint64_t seed, int64_t table_id, void* stream);
 
 /* kn4 <-> [K,N] conversion on the device (layout of python/annc/optimize/data_pack.py,
  * vector 12, tiles 352 x 128, python/annc/optimize/constant_folding.py:77-88). */

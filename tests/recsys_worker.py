@@ -27,7 +27,10 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     model = synth.recsys_model(seed=3, tables=5, rows=50_001, dim=128, batch=512, max_bag=50,
                                zipf_a=1.2, hidden=(256, 128, 1), input_seed=200 + rank, threads=2)
-    pipe = RecsysPipeline(model, dev, shard=shard)
+    hot = 0
+    if shard == "row_hot":  # row sharding with the rows of each table's 100 most popular ids replicated
+        shard, hot = "row", 100
+    pipe = RecsysPipeline(model, dev, shard=shard, hot_rows=hot)
     got = pipe.forward().cpu().numpy()
     assert pipe.embed_error_bits() == 0
     again = pipe.forward().cpu().numpy()  # second receive buffer

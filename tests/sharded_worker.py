@@ -23,14 +23,20 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     model = synth.dlrm_model(seed=5, batch=2048, tables=7, max_rows=2e5, input_seed=100 + rank)
-    pipe = ShardedDlrmPipeline(model, dev, mode)
+    # "row_hot": row sharding with the rows of each table's 300 most popular ids replicated
+    hot = 300 if mode == "row_hot" else 0
+    pipe = ShardedDlrmPipeline(model, dev, "row" if mode == "row_hot" else mode, hot_rows=hot)
     got = pipe.forward().cpu().numpy()
     assert pipe.embed_error_bits() == 0
-    if mode in ("row", "row_gather", "table"):
-        # the receive buffers alternate between steps: a second and third step must agree
+    if mode in ("row", "row_hot", "table"):
+        # lists, masks and receive slabs are reused: a second and third step must agree
         for _ in range(2):
             again = pipe.forward().cpu().numpy()
-            assert np.array_equal(again, got), "row-sharded steps differ between receive buffers"
+            assert np.array_equal(again, got), "row-sharded steps differ from one step to the next"
+    if mode in ("row", "row_hot"):
+        st = pipe.rowbags.exchange_stats()
+        print(f"rank {rank} {mode}: remote parts per bag {st['remote_parts_per_bag']:.2f}, "
+              f"NVLink bytes {st['nvlink_bytes']}, hot bytes {st['hot_bytes']}")
     want = oracle.dlrm_forward(model, threads=4)
     z = pipe.z.cpu().numpy()
     emb = model.emb
@@ -44,9 +50,7 @@ def main():
     assert perr <= 1e-5, perr          # fp32 pooling tolerance under row sharding
     assert np.abs(got - want).max() <= 2e-3  # TF32 MLP
     dist.barrier()
-    if hasattr(pipe, "peer"):
-        torch.cuda.synchronize()
-        pipe.peer.close()
+    pipe.close_exchange()
     dist.destroy_process_group()
     print(f"rank {rank} mode {mode} ok pooled_err {perr:.2e}")
 

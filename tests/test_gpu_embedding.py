@@ -356,79 +356,3 @@ def test_division_free_modulo_is_exact(num_buckets):
         got = m.mask.cpu().numpy().view(np.uint32)
         want = np.array([1 << (int(b) % g) for b in want_bucket], dtype=np.uint32)
         np.testing.assert_array_equal(got, want)
-
-
-@pytest.mark.parametrize("shards,combiner", [(2, 0), (3, 1), (8, 0), (8, 1)])
-def test_partitioned_row_exchange_on_one_gpu(shards, combiner):
-    """Row sharding with the lookups split at their source, ranks emulated one after the other
-    on one GPU: the partition (positions, int32 local rows, owner mask) is bit-exact against
-    numpy; each owner then pulls its slice, pools it into its part of a NaN-poisoned receive
-    buffer (empty parts stay unwritten), and the masked rank-order sum (times 1/len for mean)
-    matches the unsharded oracle within the fp32 pooling tolerance."""
-    from annc_b200.device import BagLaunch, BagPartition, BagPrepass, BagPull, sum_partials_masked
-    rows = [1000, 37, 50_000, 5, 3]
-    B, D = 1024, 64
-    T = len(rows)
-    TB = T * B
-    w = synth.embedding_workload(12, rows, D, B, 40, 1.05)  # bags up to 40: longer than a group
-    dev = torch.device("cuda")
-    ids = [_dev(b.raw_ids) for b in w.bags]
-    segs = [_dev(b.slice_input) for b in w.bags]
-    nnz = [int(x.shape[0]) for x in ids]
-    pre = BagPrepass(segs, B)
-    ws = torch.zeros(pre.ws_bytes, dtype=torch.uint8, device=dev)
-    pre.run(ws)
-    off_ptr = lambda t: ws.data_ptr() + 512 + t * (B + 1) * 4
-    pos = torch.full((shards * TB + 1,), -1, dtype=torch.int32, device=dev)
-    lrows = torch.full((sum(nnz),), -7, dtype=torch.int32, device=dev)
-    part = BagPartition([(ids[t].data_ptr(), nnz[t], rows[t], off_ptr(t)) for t in range(T)], B, shards,
-                        pos.data_ptr(), lrows.data_ptr(), dev)
-    part.run()
-    # numpy restatement
-    counts = np.zeros((shards, T, B), np.int64)
-    per = {}
-    for t, bag in enumerate(w.bags):
-        bucket = (bag.raw_ids.view(np.uint64) % np.uint64(rows[t])).astype(np.int64)
-        owner, local, seg = bucket % shards, bucket // shards, bag.slice_input[:, 0]
-        for g in range(shards):
-            sel = owner == g
-            np.add.at(counts[g, t], seg[sel], 1)
-            per[(g, t)] = local[sel]  # segment ids are sorted, so this is (bag, lookup) order
-    want_pos = np.concatenate([[0], np.cumsum(counts.reshape(-1))])
-    np.testing.assert_array_equal(pos.cpu().numpy(), want_pos)
-    want_rows = np.concatenate([per[(g, t)] for g in range(shards) for t in range(T)])
-    np.testing.assert_array_equal(lrows.cpu().numpy(), want_rows)
-    want_mask = np.zeros((T, B), np.int64)
-    for g in range(shards):
-        want_mask |= (counts[g] > 0).astype(np.int64) << g
-    np.testing.assert_array_equal(part.mask.cpu().numpy().reshape(T, B), want_mask)
-
-    recv = torch.full((shards, B, T, D), float("nan"), device=dev)
-    keep = []
-    for g in range(shards):
-        pos_in = torch.zeros(TB + 1, dtype=torch.int32, device=dev)
-        rows_in = torch.full((sum(nnz),), -9, dtype=torch.int32, device=dev)
-        BagPull([pos.data_ptr()], [lrows.data_ptr()], g, TB, [pos_in.data_ptr()], [rows_in.data_ptr()]).run()
-        shard_tabs = [_dev(np.ascontiguousarray(t[g::shards]) if t[g::shards].shape[0] else
-                           np.zeros((1, D), np.float32)) for t in w.tables]
-        keep.append((pos_in, rows_in, shard_tabs))
-        entries = [(shard_tabs[t].data_ptr(), len(range(g, rows[t], shards)), 1, rows_in.data_ptr(), None,
-                    sum(nnz), recv.data_ptr() + ((g * B) * T + t) * D * 4, pos_in.data_ptr() + t * B * 4)
-                   for t in range(T)]
-        launch = BagLaunch(entries, D, B, 2, T * D, dev, id_kind=0, combiner=0, shard_count=1,
-                           shard_rank=0, exchange=True)
-        launch.run()
-        assert launch.error_bits() == 0
-    written = ~torch.isnan(recv[:, :, :, 0]).cpu().numpy()  # [shards, B, T]
-    for g in range(shards):
-        np.testing.assert_array_equal(written[g].T, counts[g] > 0)
-    out = torch.full((B, T, D), 3.0, device=dev)
-    sum_partials_masked(recv.data_ptr(), part.mask, shards, B * T * D, B, T, D, out.data_ptr(), T * D,
-                        mean_offsets_ptr=(ws.data_ptr() + 512) if combiner == 1 else None)
-    got = out.cpu().numpy()
-    for t, (tab, bag) in enumerate(zip(w.tables, w.bags)):
-        idx = oracle.hash_bucket(bag.raw_ids.view(np.uint64), rows[t])
-        want, _ = oracle.sparse_segment_reduce(tab, idx, bag.slice_input, np.array([0, 0], np.int32),
-                                               np.array([0], np.int32), combiner)
-        scale = max(float(np.abs(want).max()), 1e-30)
-        assert float(np.abs(got[:, t, :] - want).max()) / scale <= 1e-5

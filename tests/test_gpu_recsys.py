@@ -12,7 +12,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("shard", ["row", "table"])
+@pytest.mark.parametrize("shard", ["row", "row_hot", "table"])
 @pytest.mark.parametrize("ranks", [1, 2])
 def test_recsys_pipeline_matches_oracle(ranks, shard):
     if torch.cuda.device_count() < ranks:

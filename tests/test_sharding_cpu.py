@@ -132,11 +132,12 @@ def test_local_rows_rule():
 # ---------------------------------------------------------------- partition-at-source protocol
 
 def _worker_partitioned(rank, world, port, q):
-    """The `row` mode's protocol on CPU ranks, numpy and the CPU oracle standing in for the
-    kernels, gloo collectives for the peer loads and stores: split own lookups by owner ->
-    owners receive positions + local rows -> owners pool their slices (empty parts are not
-    produced) -> parts go back to the sample owner -> masked sum in rank order (x 1/len for
-    mean).  Must match the unsharded oracle within the fp32 pooling tolerance."""
+    """The row exchange's protocol on CPU ranks, numpy and the CPU oracle standing in for the
+    kernels, gloo collectives for the peer loads and stores: split own lookups by owner into
+    record lists (local row, bag), hot rows staying with the source -> every owner reads the
+    lists meant for it -> pools them record by record, one part per (source, bag) that has
+    records -> parts go to the sample owner -> masked sum in rank order (x 1/len for mean).
+    Must match the unsharded oracle within the fp32 pooling tolerance."""
     import torch
     from annc_b200 import synth
     from annc_b200.sharded import ShardPlan, partition_lookups
@@ -147,6 +148,11 @@ def _worker_partitioned(rank, world, port, q):
         B, D, rows = 48, 8, [1000, 37, 5000, 3]
         T = len(rows)
         w = synth.embedding_workload(21, rows, D, B, 30, 1.2, threads=1, input_seed=70 + rank)
+        plan = ShardPlan("row", world, rank, rows, np.zeros((world, T)))
+        hot_k = [40, 0, 200, 3]  # table 3 is replicated whole, table 1 has no hot rows
+        hot_rows = [w.bags[t].popular_rows(hot_k[t], rows[t]) for t in range(T)]
+        # what this rank holds of table t: its shard, then the replicated hot rows
+        held = [np.concatenate([plan.local_shard(w.tables[t]), w.tables[t][hot_rows[t]]]) for t in range(T)]
         errs = []
         for combiner in (0, 1):
             want = np.zeros((B, T, D), np.float32)
@@ -155,45 +161,44 @@ def _worker_partitioned(rank, world, port, q):
                 o, _ = oracle.sparse_segment_reduce(w.tables[t], idx, bag.slice_input, np.array([0, 0], np.int32),
                                                     np.array([0], np.int32), combiner)
                 want[:o.shape[0], t] = o
-            # 1. split at the source
-            mine = [partition_lookups(b.raw_ids, b.slice_input[:, 0], rows[t], B, world) for t, b in enumerate(w.bags)]
+            # 1. split at the source: mine[t][g] = (local rows, bags) for owner g
+            mine = [partition_lookups(b.raw_ids, b.slice_input[:, 0], rows[t], world, source=rank,
+                                      hot_rows=hot_rows[t], local_rows_of_source=plan.local_rows(t))
+                    for t, b in enumerate(w.bags)]
             lens = np.stack([np.bincount(b.slice_input[:, 0], minlength=B) for b in w.bags])  # [T, B]
-            # 2. owners receive their slices (all_gather_object stands in for the peer pull)
+            # 2. owners read the lists meant for them (all_gather_object stands in for the peer loads)
             everyone = [None] * world
-            dist.all_gather_object(everyone, [[(mine[t][0][g], mine[t][1][g]) for t in range(T)]
-                                              for g in range(world)])  # everyone[s][g][t]
-            plan = ShardPlan("row", world, rank, rows, np.zeros((world, T)))
-            # 3. this owner pools, for every source s, the lookups it owns
+            dist.all_gather_object(everyone, [[mine[t][g] for t in range(T)] for g in range(world)])
+            # 3. this owner pools, for every source s, the records of its list
             parts_out = np.zeros((world, B, T, D), np.float32)   # [source, ...]: goes back to s
-            present_out = np.zeros((world, T, B), bool)
             for s in range(world):
                 for t in range(T):
-                    counts, local = everyone[s][rank][t]
-                    shard = plan.local_shard(w.tables[t])
-                    assert local.size == 0 or int(local.max()) < shard.shape[0]
+                    local, seg = everyone[s][rank][t]
                     if local.size == 0:
                         continue
-                    seg = np.repeat(np.arange(B, dtype=np.int64), counts)
+                    assert int(local.max()) < held[t].shape[0]
                     sl = np.stack([seg, np.zeros_like(seg)], axis=1)
-                    o, _ = oracle.sparse_segment_reduce(shard, local.astype(np.int64), sl, np.array([0, 0], np.int32),
+                    o, _ = oracle.sparse_segment_reduce(held[t], local.astype(np.int64), sl, np.array([0, 0], np.int32),
                                                         np.array([0], np.int32), 0)
                     parts_out[s, :o.shape[0], t] = o
-                    present_out[s, t] = counts > 0
             # 4. parts travel to the sample owner (an all_gather stands in for the peer stores:
             #    rank g's part for source s is gathered[g][s])
             gathered = [torch.zeros((world, B, T, D)) for _ in range(world)]
             dist.all_gather(gathered, torch.from_numpy(parts_out))
             recv = [gathered[g][rank] for g in range(world)]
-            # 5. masked sum in rank order; the mask comes from this rank's own counts
+            # 5. masked sum in rank order; the mask comes from this rank's own split
             got = np.zeros((B, T, D), np.float32)
             for g in range(world):
                 for t in range(T):
-                    have = mine[t][0][g] > 0
+                    have = np.zeros(B, bool)
+                    have[mine[t][g][1]] = True
                     got[have, t] = got[have, t] + recv[g].numpy()[have, t]
             if combiner == 1:
                 inv = np.where(lens > 0, np.float32(1.0) / np.maximum(lens, 1).astype(np.float32), np.float32(1.0))
                 got = got * inv.T[:, :, None].astype(np.float32)
             errs.append(float(np.abs(got - want).max() / np.abs(want).max()))
+            # nothing of a whole-replicated table crosses ranks
+            assert all(mine[3][g][0].size == 0 for g in range(world) if g != rank)
         q.put((rank, errs))
     finally:
         dist.destroy_process_group()
