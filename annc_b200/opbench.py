@@ -1,13 +1,11 @@
-"""Per-operator timing on one GPU: GEMM TFLOP/s against the tensor peak and bandwidth
-kernels against the HBM peak, for the benchmark configurations and the DLRM layers.
+"""Per-operator timings on one GPU for the benchmark configurations: GEMM TFLOP/s against the
+tensor peak and bandwidth kernels against the HBM peak.  `ops_record()` is what `bench.py` puts
+into its JSON line; `python -m annc_b200.opbench` prints the same record, one case per line.
 
-    python -m annc_b200.opbench [--only gemm|embed|misc] [--reps 20]
-
-CUDA events on the launching stream, 3 warm-ups, a 256 MB L2 flush between repetitions
-for working sets smaller than L2.  Prints one JSON line per case."""
+CUDA events on the launching stream, 3 warm-ups, median of `reps`; a 256 MB buffer is written
+between repetitions when the working set is smaller than L2."""
 from __future__ import annotations
 
-import argparse
 import json
 import os
 
@@ -16,36 +14,19 @@ import torch
 
 from . import device as dev
 from . import synth
-from ._lib import (ACT_NONE, ACT_RELU, B_KN4, B_PLAIN, IO_A_BF16, IO_B_BF16, IO_C_BF16, IO_SOFTMAX,
-                   MATH_AUTO, MATH_BF16)
+from ._lib import ACT_NONE, ACT_RELU, B_KN4, IO_SOFTMAX, MATH_AUTO
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_flush = None
 
 
 def peaks():
+    """(HBM GB/s, TF32 TFLOP/s, source).  TF32 dense peak = half the measured BF16 figure."""
     try:
         p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         return float(p["hbm_gbs"]), float(p["bf16_tflops"]) / 2, "measured"
     except Exception:
         return 6650.0, 1590.0 / 2, "fallback"
-
-
-_flush = None
-_nvml = None
-
-
-def sm_clock_mhz():
-    """Current SM clock (read only), reported beside each timing: the tensor-core cases move
-    with the clock the power cap allows."""
-    global _nvml
-    try:
-        if _nvml is None:
-            import pynvml
-            pynvml.nvmlInit()
-            _nvml = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device()))
-        return int(_nvml[0].nvmlDeviceGetClockInfo(_nvml[1], _nvml[0].NVML_CLOCK_SM))
-    except Exception:
-        return None
 
 
 def time_ms(fn, reps, flush):
@@ -65,175 +46,117 @@ def time_ms(fn, reps, flush):
         e1.record()
         e1.synchronize()
         ts.append(e0.elapsed_time(e1))
-    global LAST_CLOCK
-    LAST_CLOCK = sm_clock_mhz()
     return float(np.median(ts))
 
 
-LAST_CLOCK = None
-
-
-def bmm_case(name, b, m, n, k, reps):
-    if MATCH and MATCH not in f"{name}/kn":
-        return
+def _gemm_fields(ms, m, n, k, byt, batch=1):
     hbm, tf32, src = peaks()
-    g = torch.Generator(device="cuda").manual_seed(0)
-    a = torch.randn((b, m, k), device="cuda", generator=g)
-    w = torch.randn((b, k, n), device="cuda", generator=g)
-    c = torch.empty((b, m, n), device="cuda")
-    names = []
-    fn = lambda: names.append(dev.gemm(a, w, c, m=m, n=n, k=k, batch=b, stride_a=m * k,
-                                       stride_b=k * n, stride_c=m * n))
-    byt = 4 * b * (m * k + k * n + m * n)
-    ms = time_ms(fn, reps, flush=True)
-    fl = 2.0 * b * m * n * k
-    print(json.dumps({"op": name, "kernel": names[-1], "b": "kn", "m": m, "n": n, "k": k, "batch": b,
-                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
-                      "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
-                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
+    fl = 2.0 * batch * m * n * k
+    return {"m": m, "n": n, "k": k, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+            "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3), "gbs": round(byt / ms / 1e6, 1),
+            "frac_hbm": round(byt / ms / 1e6 / hbm, 3), "peak": src}
 
 
-MATCH = ""
-
-
-def bf16_case(name, m, n, k, reps):
-    """bf16 A [M,K] x bf16 B [N,K] -> bf16 C with bias + ReLU (the large recsys MLP layers)."""
-    if MATCH and MATCH not in f"{name}/bf16":
-        return
-    hbm, tf32, src = peaks()
-    g = torch.Generator(device="cuda").manual_seed(0)
-    a = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
-    b = (torch.randn((n, k), device="cuda", generator=g) / k ** 0.5).to(torch.bfloat16)
-    bv = torch.randn(n, device="cuda", generator=g)
-    c = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
-    names = []
-    fn = lambda: names.append(dev.gemm(a, b, c, m=m, n=n, k=k, trans_b=True, bias=bv, activation=ACT_RELU,
-                                       math=MATH_BF16, io_flags=IO_A_BF16 | IO_B_BF16 | IO_C_BF16))
-    byt = 2 * (m * k + k * n + m * n)
-    ms = time_ms(fn, reps, flush=byt < (200 << 20))
-    fl = 2.0 * m * n * k
-    print(json.dumps({"op": name, "kernel": names[-1], "b": "nk bf16", "m": m, "n": n, "k": k,
-                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
-                      "frac_bf16_peak": round(fl / ms / 1e9 / (2 * tf32), 3),
-                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
-
-
-def bmm_softmax_case(name, b, m, n, k, reps):
-    """batch_matmul + row softmax: two kernels (matmul, then softmax) against the fused epilogue."""
-    if MATCH and MATCH not in f"{name}/kn":
-        return
-    hbm, _, src = peaks()
-    g = torch.Generator(device="cuda").manual_seed(0)
-    a = torch.randn((b, m, k), device="cuda", generator=g) / 8
-    w = torch.randn((b, k, n), device="cuda", generator=g)
-    c = torch.empty((b, m, n), device="cuda")
-    y = torch.empty((b, m, n), device="cuda")
-    kw = dict(m=m, n=n, k=k, batch=b, stride_a=m * k, stride_b=k * n, stride_c=m * n)
-
-    def two():
-        dev.gemm(a, w, c, **kw)
-        dev.softmax(c.view(-1, n), y.view(-1, n))
-    ms2 = time_ms(two, reps, flush=True)
-    ms1 = time_ms(lambda: dev.gemm(a, w, y, io_flags=IO_SOFTMAX, **kw), reps, flush=True)
-    byt = 4 * b * (m * k + k * n + m * n)
-    print(json.dumps({"op": name, "two_kernels_ms": round(ms2, 4), "fused_ms": round(ms1, 4),
-                      "fused_gbs": round(byt / ms1 / 1e6, 1), "fused_frac_hbm": round(byt / ms1 / 1e6 / hbm, 3),
-                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
-
-
-def gemm_case(name, m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False):
-    if MATCH and MATCH not in f"{name}/{bsrc}":
-        return
-    hbm, tf32, src = peaks()
+def gemm_case(m, n, k, reps, bsrc="kn", bias=False, act=ACT_NONE, addend=False, b_cached=None):
+    """bsrc: "kn" (B as [K,N]), "nk" (B as [N,K]), "kn4" (the prepacked layout, consumed
+    directly), "kn4+ws" (prepacked, re-laid into a caller workspace on every call)."""
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randn((m, k), device="cuda", generator=g)
-    w = torch.randn((k, n), device="cuda", generator=g)
+    w = torch.randn((k, n), device="cuda", generator=g) if b_cached is None else None
     c = torch.empty((m, n), device="cuda")
     bv = torch.randn(n, device="cuda", generator=g) if bias else None
     ad = torch.randn((m, n), device="cuda", generator=g) if addend else None
     kw = dict(m=m, n=n, k=k, bias=bv, addend=ad, activation=act, math=MATH_AUTO)
-    if bsrc == "nk":
+    if b_cached is not None:
+        b = b_cached
+        kw["b_format"] = B_KN4
+    elif bsrc == "nk":
         b = w.t().contiguous()
         kw["trans_b"] = True
     elif bsrc in ("kn4", "kn4+ws"):
         b = dev.kn4_pack(w)
         kw["b_format"] = B_KN4
-        if bsrc == "kn4+ws":
-            kw["workspace"] = torch.empty((k, n), device="cuda")
     else:
         b = w
+    if bsrc == "kn4+ws":
+        kw["workspace"] = torch.empty((k, n), device="cuda")
     names = []
     fn = lambda: names.append(dev.gemm(a, b, c, **kw))
     byt = 4 * (m * k + k * n + m * n * (2 if addend else 1))
     ms = time_ms(fn, reps, flush=byt < (200 << 20))
-    fl = 2.0 * m * n * k
-    print(json.dumps({"op": name, "kernel": names[-1], "b": bsrc, "m": m, "n": n, "k": k,
-                      "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
-                      "frac_tf32_peak": round(fl / ms / 1e9 / tf32, 3),
-                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
+    r = _gemm_fields(ms, m, n, k, byt)
+    r.update(kernel=names[-1], b=bsrc)
+    return r
 
 
-def run_gemm(reps):
-    gemm_case("matmul_add_relu C1", 512, 1024, 1024, reps, addend=True, act=ACT_RELU)
-    for bsrc in ("kn4", "kn4+ws", "kn", "nk"):
-        gemm_case("layout_matmul C2", 8192, 4096, 2048, reps, bsrc=bsrc)
-    bmm_case("batch_matmul C2", 64, 256, 256, 64, reps)
-    bmm_softmax_case("batch_matmul + softmax C2", 64, 256, 256, 64, reps)
-    for (m, n, k) in ((16384, 1024, 8192), (131072, 1024, 8192), (131072, 512, 1024), (8192, 8192, 8192)):
-        bf16_case("recsys MLP bf16", m, n, k, reps)
-    gemm_case("square tf32", 8192, 8192, 8192, reps, bsrc="nk")
-    for m in (128, 256, 512):
-        gemm_case("small-M sweep", m, 1024, 1024, reps)
-    for (k, n) in ((512, 256), (256, 64), (416, 512), (512, 256)):
-        for bsrc in ("kn", "nk"):
-            gemm_case("dlrm layer", 65536, n, k, reps, bsrc=bsrc, bias=True, act=ACT_RELU)
-    gemm_case("dlrm layer0 (K=13)", 65536, 512, 13, reps, bias=True, act=ACT_RELU)
-
-
-def run_embed(reps):
+def bmm_softmax_case(b, m, n, k, reps):
+    """batch_matmul + row softmax: two kernels (matmul, then softmax) and the fused epilogue."""
     hbm, _, src = peaks()
-    w = synth.hash_bucket_bag_case(0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((b, m, k), device="cuda", generator=g) / 8
+    w = torch.randn((b, k, n), device="cuda", generator=g) / 8
+    c = torch.empty((b, m, n), device="cuda")
+    y = torch.empty((b, m, n), device="cuda")
+    kw = dict(m=m, n=n, k=k, batch=b, stride_a=m * k, stride_b=k * n, stride_c=m * n)
+    names = []
+    ms_mm = time_ms(lambda: names.append(dev.gemm(a, w, c, **kw)), reps, flush=True)
+    ms_sm = time_ms(lambda: dev.softmax(c.view(-1, n), y.view(-1, n)), reps, flush=True)
+    ms_f = time_ms(lambda: dev.gemm(a, w, y, io_flags=IO_SOFTMAX, **kw), reps, flush=True)
+    byt_mm = 4 * b * (m * k + k * n + m * n)
+    byt_sm = 2 * 4 * b * m * n
+    return {"batch_matmul": dict(_gemm_fields(ms_mm, m, n, k, byt_mm, batch=b), kernel=names[-1], batch=b),
+            "softmax": {"rows": b * m, "channels": n, "ms": round(ms_sm, 4),
+                        "gbs": round(byt_sm / ms_sm / 1e6, 1), "frac_hbm": round(byt_sm / ms_sm / 1e6 / hbm, 3)},
+            "fused_bmm_softmax": {"ms": round(ms_f, 4), "gbs": round(byt_mm / ms_f / 1e6, 1),
+                                  "frac_hbm": round(byt_mm / ms_f / 1e6 / hbm, 3),
+                                  "note": "one kernel; not routed to by default while two kernels are faster"},
+            "peak": src}
+
+
+def embed_case(reps, tables=26, rows=1_000_000, dim=64, batch=16384):
+    """26 tables x 1 M rows x dim 64, batch 16384, bags U{1..20}, Zipf 1.05 ids, sum pooling:
+    prepass + grouped bag kernel.  Tables are drawn on the device (U(-0.05, 0.05)); the ids come
+    from the host generator."""
+    hbm, _, src = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    tabs = [torch.rand((rows, dim), device="cuda", generator=g) * 0.1 - 0.05 for _ in range(tables)]
+    rngs = np.random.default_rng(0).spawn(tables)
+    bags = [synth._bag_inputs(r, batch, 20, 1.05) for r in rngs]
     up = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    out = torch.empty((w.batch, len(w.tables), w.dim), device="cuda")
-    plan = dev.BagPlan([up(t) for t in w.tables], [up(b.raw_ids) for b in w.bags],
-                       [up(b.slice_input) for b in w.bags], out, 0, w.batch)
+    out = torch.empty((batch, tables, dim), device="cuda")
+    plan = dev.BagPlan(tabs, [up(b.raw_ids) for b in bags], [up(b.slice_input) for b in bags], out, 0, batch)
     ms = time_ms(plan.run, reps, flush=False)
-    byt = w.algorithmic_bytes()
-    print(json.dumps({"op": "embed_hash_bucket + segment sum C3 (prepass + bags)", "ms": round(ms, 4),
-                      "lookups": w.nnz, "gbs": round(byt / ms / 1e6, 1),
-                      "frac_hbm": round(byt / ms / 1e6 / hbm, 3),
-                      "samples_per_s": round(w.batch / ms * 1e3), "peak": src, "sm_mhz": LAST_CLOCK}), flush=True)
+    assert plan.error_bits() == 0
+    nnz = int(sum(b.raw_ids.shape[0] for b in bags))
+    byt = nnz * (4 * dim + 16) + tables * batch * 4 * dim
+    return {"tables": tables, "rows": rows, "dim": dim, "batch": batch, "lookups": nnz, "ms": round(ms, 4),
+            "algorithmic_gbs": round(byt / ms / 1e6, 1), "frac_hbm_algorithmic": round(byt / ms / 1e6 / hbm, 3),
+            "label": "algorithmic GB/s of prepass + bag kernel (L2-assisted: Zipf-hot rows are served by "
+                     "L2, DRAM traffic is lower)", "samples_per_s": round(batch / ms * 1e3), "peak": src,
+            "l2": "6.6 GB of tables, larger than L2; no flush"}
 
 
-def run_misc(reps):
-    hbm, _, src = peaks()
-    x = torch.randn((16384, 256), device="cuda")
-    y = torch.empty_like(x)
-    ms = time_ms(lambda: dev.softmax(x, y), reps, flush=True)
-    print(json.dumps({"op": "softmax 16384x256", "ms": round(ms, 4),
-                      "gbs": round(2 * x.numel() * 4 / ms / 1e6, 1)}), flush=True)
-    z = torch.randn((65536, 27, 64), device="cuda")
-    o = torch.empty((65536, 416), device="cuda")
-    ms = time_ms(lambda: dev.dot_interaction(z, o), reps, flush=False)
-    byt = (z.numel() + o.numel()) * 4
-    print(json.dumps({"op": "dot interaction 65536x27x64", "ms": round(ms, 4),
-                      "gbs": round(byt / ms / 1e6, 1), "frac_hbm": round(byt / ms / 1e6 / hbm, 3)}),
-          flush=True)
+def ops_record(reps: int = 10) -> dict:
+    """The operator figures of the benchmark configurations (one GPU, device-resident operands)."""
+    rec = {"method": "CUDA events, median of %d, 3 warm-ups; L2 flushed between repetitions when the "
+                     "working set is below 200 MB" % reps}
+    rec["c1_matmul_add_relu_512x1024x1024"] = gemm_case(512, 1024, 1024, reps, addend=True, act=ACT_RELU)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    w = torch.randn((2048, 4096), device="cuda", generator=g) / 64
+    packed = dev.kn4_pack(w)
+    del w
+    rec["c2_layout_matmul_8192x4096x2048_from_kn4_direct"] = gemm_case(8192, 4096, 2048, reps, bsrc="kn4", b_cached=packed)
+    rec["c2_layout_matmul_8192x4096x2048_from_kn4_relaid_each_call"] = gemm_case(8192, 4096, 2048, reps, bsrc="kn4+ws", b_cached=packed)
+    rec["c2_layout_matmul_8192x4096x2048_b_as_nk"] = gemm_case(8192, 4096, 2048, reps, bsrc="nk")
+    rec["small_m_sweep_layout_matmul_kn4_n4096_k2048"] = {
+        "M=%d" % m: gemm_case(m, 4096, 2048, reps, bsrc="kn4", b_cached=packed) for m in (128, 256, 512)}
+    rec["c2_batch_matmul_softmax_64x256x64x256"] = bmm_softmax_case(64, 256, 256, 64, reps)
+    torch.cuda.empty_cache()
+    rec["c3_embed_hash_bucket_segment_sum"] = embed_case(reps)
+    torch.cuda.empty_cache()
+    return rec
 
 
 if __name__ == "__main__":
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all")
-    ap.add_argument("--reps", type=int, default=20)
-    ap.add_argument("--match", default="", help="run only GEMM cases whose 'name/b-source' contains this")
-    a = ap.parse_args()
-    MATCH = a.match
-    if a.only in ("all", "gemm"):
-        run_gemm(a.reps)
-    if a.only in ("all", "embed"):
-        run_embed(a.reps)
-    if a.only in ("all", "misc"):
-        run_misc(a.reps)
+    for name, val in ops_record().items():
+        print(json.dumps({name: val}), flush=True)

@@ -36,8 +36,8 @@ if ROOT not in sys.path:
 METRIC = "dlrm_inference_samples_per_s"
 UNIT = "samples/s"
 
-# DRAM bytes (read + write) of one bag-kernel launch, from a single-pass ncu capture of this
-# command's default workload (profiles/bag_reduce_kernel_dlrm_batch65536_traffic_and_launch_list.md).
+# DRAM bytes (read + write) of one bag-kernel launch: a constant from an earlier single-pass
+# profiler capture of this command's default workload, not measured by this run.
 # Keyed by (batch, max_rows, seed); any other workload reports null.
 NCU_BAG_TRAFFIC_BYTES = {(65536, 1e7, 0): 1.573e9}
 
@@ -57,18 +57,41 @@ def parse_args():
     ap.add_argument("--max-rows", type=float, default=1e7)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard", default="auto", choices=["auto", "row", "row_gather", "row_nccl", "table", "table_nccl", "replica"],
-                    help="table partitioning for --gpus > 1: row = mod row-sharding, lookups split by "
-                         "owner at their source, the bag kernel stores partial sums into the owner "
-                         "rank's memory; row_gather = the same stores with all-gathered ids; row_nccl = "
-                         "all-gathered ids and a separate NCCL all-to-all; table = whole tables per rank; replica = no exchange; auto = "
-                         "row when the tables exceed --hbm-budget-gb per GPU, else replica")
-    ap.add_argument("--hbm-budget-gb", type=float, default=100.0,
-                    help="per-GPU memory the tables may take before auto switches to row sharding")
+    ap.add_argument("--shard", default="row", choices=["row", "row_nccl", "table", "table_nccl", "replica"],
+                    help="table partitioning timed as the line's `value` for --gpus > 1: row = mod "
+                         "row-sharding (the library's row exchange: lookups split by owner at their "
+                         "source, partial sums stored into the sample owner's memory, optional "
+                         "replicated hot rows); row_nccl = all-gathered ids and an NCCL all-to-all; "
+                         "table = whole tables per rank; replica = no exchange")
+    ap.add_argument("--hot-rows", type=int, default=65536,
+                    help="row sharding: rows of each table's this many most popular ids are replicated "
+                         "on every rank and pooled where the sample is (0 = pure row sharding)")
+    ap.add_argument("--extras", default="row_k0,table,replica",
+                    help="--gpus > 1: other partitionings timed after the headline and reported as "
+                         "labelled sub-records (comma list of row_k0, row_nccl, table, table_nccl, replica; "
+                         "empty = none)")
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-operator record at N=1")
     args = ap.parse_args()
     if args.batch is None:
         args.batch = 65536 if args.workload == "dlrm" else 16384
     return args
+
+
+def parallelism_label(args, world, mode=None):
+    mode = mode or args.shard
+    if world == 1 and args.workload == "dlrm":
+        return "single"
+    hot = (" + rows of each table's %d most popular ids replicated" % args.hot_rows) if args.hot_rows > 0 else ""
+    return {
+        "row": "dp%d MLP + row-sharded tables (owner = row %% %d)%s; lookups split by owner at their source, "
+               "partial sums stored into the sample owner's memory by the pooling kernel, flag barriers"
+               % (world, world, hot),
+        "row_k0": "dp%d MLP + row-sharded tables (owner = row %% %d), no replicated rows" % (world, world),
+        "row_nccl": "dp%d MLP + row-sharded tables, all-gathered ids + NCCL all-to-all of partial sums" % world,
+        "table": "dp%d MLP + whole tables per rank, pooled vectors stored into the sample owner's memory" % world,
+        "table_nccl": "dp%d MLP + whole tables per rank, NCCL all-to-all of ids and pooled vectors" % world,
+        "replica": "dp%d MLP + every table on every rank (no exchange)" % world,
+    }[mode]
 
 
 def workload_config(args, world):
@@ -79,15 +102,12 @@ def workload_config(args, world):
                 "global_batch": args.batch * world, "per_gpu_batch": args.batch, "tables": args.tables,
                 "dim": 128, "rows": rows, "bag": "U{1..50}, Zipf 1.2, mean",
                 "table_bytes_total": args.tables * rows * 512,
-                "parallelism": ("table-wise sharded tables over %d GPU(s), pooled vectors stored into the "
-                                "sample owner's memory; dp MLP" % world) if args.shard == "table" else
-                               ("row-sharded tables (mod rule) over %d GPU(s), lookups split at their "
-                                "source, partial sums stored into the owner's memory; dp MLP" % world),
+                "parallelism": parallelism_label(args, world),
                 "l2": "inputs larger than L2 (table shard %.1f GB per GPU)" % (args.tables * int(args.rows_per_gpu) * 512 / 1e9)}
     return {"workload": "dlrm_style_fp32w_tf32math_batch%d_26tables_dim64_zipf1.05" % args.batch,
             "global_batch": args.batch * world, "per_gpu_batch": args.batch,
             "tables": 26, "dim": 64, "rows": "log-uniform 1e3..%g" % args.max_rows,
-            "parallelism": ("dp%d MLP + %s-sharded tables" % (world, args.shard)) if world > 1 else "single",
+            "parallelism": parallelism_label(args, world),
             "l2": "inputs larger than L2 (tables 6.6 GB, ids 0.43 GB per step)"}
 
 
@@ -239,9 +259,46 @@ def run_reference(args):
 
 # ---------------------------------------------------------------- GPU arm
 
+def cpu_baselines(args, model, pipe_out):
+    """CPU legs at N=1 (DLRM): the C port of the reference kernels + OpenBLAS on all host cores
+    over full batches, the same on one thread (the reference's deployment setting,
+    OMP_NUM_THREADS=1) over a bounded sample, and the parity of the GPU predictions of the very
+    batch that was timed against the all-core leg's output."""
+    import numpy as np
+    from oracle import oracle
+    threads = oracle.host_threads()
+    oracle.set_blas_threads(threads)
+    oracle.dlrm_forward(model, sample=min(2048, model.emb.batch), threads=threads)  # page-in
+    t, ref = [], None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        ref = oracle.dlrm_forward(model, threads=threads)
+        t.append(time.perf_counter() - t0)
+    cpu_ms = 1e3 * sum(t) / len(t)
+    base = {"value": args.batch / (cpu_ms / 1e3), "unit": UNIT, "cores": threads, "kind": "port",
+            "ms_per_step": cpu_ms,
+            "sample": "3 full batches of %d samples (C restatement of the reference kernels, one table "
+                      "per thread, + OpenBLAS sgemm)" % args.batch}
+    parity = float(np.abs(pipe_out - ref).max())
+    n1 = min(8192, model.emb.batch)
+    oracle.set_blas_threads(1)
+    t1 = []
+    for _ in range(2):
+        t0 = time.perf_counter()
+        oracle.dlrm_forward(model, sample=n1, threads=1)
+        t1.append(time.perf_counter() - t0)
+    oracle.set_blas_threads(threads)
+    ms1 = 1e3 * sum(t1) / len(t1)
+    one = {"value": n1 / (ms1 / 1e3), "unit": UNIT, "cores": 1, "kind": "port", "ms_per_sample_batch": ms1,
+           "sample": "2 passes over the first %d samples of the batch, one thread (OMP_NUM_THREADS=1 is the "
+                     "reference's deployment setting)" % n1}
+    return base, one, parity
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
+    import numpy as np
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -257,38 +314,6 @@ def run_gpu(args):
     from annc_b200._lib import lib
     from annc_b200.dlrm import DlrmPipeline
     import ctypes as C
-
-    if args.workload == "recsys":
-        from annc_b200.recsys import RecsysPipeline
-        if world == 1:  # the row-sharded step uses torch.distributed for its barriers at every N
-            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29000 + os.getpid() % 2000),
-                                    rank=0, world_size=1, device_id=devi)
-        args.shard = "table" if args.shard == "table" else "row"
-        model = synth.recsys_model(seed=args.seed, tables=args.tables, rows=int(args.rows_per_gpu) * world,
-                                   batch=args.batch, input_seed=1000 + rank)
-        pipe = RecsysPipeline(model, devi, keep_host_inputs=True, shard=args.shard)
-        nnz = model.nnz
-        # the bag kernel of the partitioned step reads an int32 local row per lookup and two
-        # int32 positions per bag, and writes one fp32 part per bag
-        emb_bytes = nnz * (4 * 128 + 4) + args.tables * args.batch * (4 * 128 + 8)
-        bag_kernel = "bag_reduce_kernel<32,1> (gather + segment sum of the partitioned step, %d tables)" % args.tables
-        if args.shard == "table":  # whole bags: raw 8-byte ids hashed in the kernel, mean applied there
-            emb_bytes = nnz * (4 * 128 + 8) + args.tables * args.batch * (4 * 128 + 8)
-            bag_kernel = "bag_reduce_kernel<32,1> (hash-bucket + gather + segment mean, %d tables)" % args.tables
-    else:
-        model = synth.dlrm_model(seed=args.seed, batch=args.batch, max_rows=args.max_rows,
-                                 input_seed=(1000 + rank) if world > 1 else None)
-        if world > 1:
-            from annc_b200.sharded import ShardedDlrmPipeline
-            if args.shard == "auto":
-                table_gb = sum(t.nbytes for t in model.emb.tables) / 1e9
-                args.shard = "row" if table_gb > args.hbm_budget_gb else "replica"
-            pipe = ShardedDlrmPipeline(model, devi, args.shard, keep_host_inputs=True)
-        else:
-            pipe = DlrmPipeline(model, devi, keep_host_inputs=True)
-        emb_bytes = model.emb.algorithmic_bytes()
-        nnz = model.emb.nnz
-        bag_kernel = "bag_reduce_kernel<16,1> (hash-bucket + gather + segment sum, 26 tables in one launch)"
 
     def barrier():
         if world > 1:
@@ -310,12 +335,54 @@ def run_gpu(args):
             ms = float(t.item())
         return ms
 
+    def close(pipe):
+        torch.cuda.synchronize()
+        if args.workload == "recsys":
+            pipe.close()
+        elif hasattr(pipe, "close_exchange"):
+            pipe.close_exchange()
+
+    recsys = args.workload == "recsys"
+    if recsys:
+        from annc_b200.recsys import RecsysPipeline
+        if world == 1:  # the peer buffers are exchanged over torch.distributed at every N
+            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29000 + os.getpid() % 2000),
+                                    rank=0, world_size=1, device_id=devi)
+        args.shard = "table" if args.shard == "table" else "row"
+        model = synth.recsys_model(seed=args.seed, tables=args.tables, rows=int(args.rows_per_gpu) * world,
+                                   batch=args.batch, input_seed=1000 + rank)
+        nnz = model.nnz
+        emb_bytes = nnz * (4 * 128 + 8 + 8) + args.tables * args.batch * 4 * 128
+        bag_kernel = "pool_kernel<32,1> (row exchange: gather + segment mean + peer stores, %d tables)" % args.tables
+        if args.shard == "table":
+            bag_kernel = "bag_reduce_kernel<32,1> (hash-bucket + gather + segment mean, %d tables)" % args.tables
+
+        def build(mode):
+            return RecsysPipeline(model, devi, keep_host_inputs=True, shard="table" if mode == "table" else "row",
+                                  hot_rows=args.hot_rows if mode == "row" else 0)
+    else:
+        model = synth.dlrm_model(seed=args.seed, batch=args.batch, max_rows=args.max_rows,
+                                 input_seed=(1000 + rank) if world > 1 else None)
+        emb_bytes = model.emb.algorithmic_bytes()
+        nnz = model.emb.nnz
+        bag_kernel = "bag_reduce_kernel<16,1> (hash-bucket + gather + segment sum, 26 tables in one launch)"
+
+        def build(mode):
+            if world == 1:
+                return DlrmPipeline(model, devi, keep_host_inputs=True)
+            from annc_b200.sharded import ShardedDlrmPipeline
+            if mode == "row_k0":
+                return ShardedDlrmPipeline(model, devi, "row", keep_host_inputs=True, hot_rows=0)
+            return ShardedDlrmPipeline(model, devi, mode, keep_host_inputs=True,
+                                       hot_rows=args.hot_rows if mode == "row" else 0)
+
+    pipe = build(args.shard)
     for _ in range(max(3, args.warmup)):
         pipe.forward()
     torch.cuda.synchronize()
     assert pipe.embed_error_bits() == 0, "embedding kernels flagged an index error"
 
-    # device-resident pass: the whole step, and the bag kernel alone through event hooks
+    # device-resident pass: the whole step, and (N=1) the bag kernel alone through event hooks
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     pairs = [(C.c_void_p(lib.annc_timer_create()), C.c_void_p(lib.annc_timer_create()))
@@ -327,16 +394,19 @@ def run_gpu(args):
         lib.annc_embed_bag_set_timing_events(a, b)
         pipe.forward()
 
-    ms_total = timed(step_with_hooks, args.steps)
+    hooks = world == 1 and not recsys
+    ms_total = timed(step_with_hooks if hooks else pipe.forward, args.steps)
     lib.annc_embed_bag_set_timing_events(None, None)
     bag_ms = []
     for a, b in pairs:
-        v = C.c_float(0)
-        lib.annc_timer_elapsed_ms(a, b, C.byref(v))
-        bag_ms.append(v.value)
+        if hooks:
+            v = C.c_float(0)
+            lib.annc_timer_elapsed_ms(a, b, C.byref(v))
+            bag_ms.append(v.value)
         lib.annc_timer_destroy(a)
         lib.annc_timer_destroy(b)
     ms_step = ms_total / args.steps
+    assert pipe.embed_error_bits() == 0, "embedding kernels flagged an error in the timed steps"
 
     # end-to-end pass: host buffers in, host result out
     for _ in range(2):
@@ -354,28 +424,84 @@ def run_gpu(args):
     except Exception:
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-    bag_avg_ms = sum(bag_ms) / len(bag_ms)
-    achieved = emb_bytes / (bag_avg_ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": bag_kernel,
-                "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
-                "algorithmic_bytes_per_launch": emb_bytes, "lookups_per_launch": nnz,
-                "kernel_ms": bag_avg_ms,
-                "traffic": NCU_BAG_TRAFFIC_BYTES.get((args.batch, float(args.max_rows), args.seed))
-                if args.workload == "dlrm" else None,
-                "traffic_note": "dram read+write bytes per launch from ncu; below the algorithmic "
-                                "bytes because Zipf-hot rows are served by L2"}
+    peak_source = "measured" if "hbm_gbs" in peaks else "fallback"
 
-    if world > 1:
-        roofline = {"bound": "hbm", "kernel": roofline["kernel"], "achieved": None, "peak": hbm_peak,
-                    "unit": "GB/s", "frac": None, "traffic": None,
-                    "note": "the bag kernel is timed alone at N=1; a sharded step launches it in "
-                            "several groups and its bytes per launch depend on the partitioning"}
+    # row exchange: per-rank phase times (CUDA events inside the library, profiled steps after
+    # the timed region) and what crossed NVLink
+    exchange = None
+    rowbags = getattr(pipe, "rowbags", None) or (getattr(pipe, "bags", None) if recsys and args.shard == "row" else None)
+    if rowbags is not None and hasattr(rowbags, "ex"):
+        rowbags.ex.set_profiling(True)
+        ph = []
+        for _ in range(5):
+            barrier()
+            pipe.forward()
+            torch.cuda.synchronize()
+            ph.append(rowbags.ex.phase_ms())
+        rowbags.ex.set_profiling(False)
+        med = [float(np.median([p[i] for p in ph])) for i in range(5)]
+        st = rowbags.exchange_stats()
+        mine = torch.tensor(med + [float(st["nvlink_bytes"]), float(st["remote_parts_received"]),
+                                   float(st["remote_records"])], device=devi, dtype=torch.float64)
+        if world > 1:
+            allr = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+        else:
+            allr = [mine]
+        allr = [x.cpu().tolist() for x in allr]
+        from annc_b200.row_exchange import PHASES
+        pool_ms = max(x[2] for x in allr)
+        nv_bytes = max(x[5] for x in allr)
+        exchange = {
+            "phases": list(PHASES),
+            "phase_ms_per_rank": [[round(v, 4) for v in x[:5]] for x in allr],
+            "phase_ms_max_over_ranks": [round(max(x[i] for x in allr), 4) for i in range(5)],
+            "hot_rows_per_table": args.hot_rows, "hot_bytes_per_gpu": st["hot_bytes"],
+            "remote_parts_per_bag": st["remote_parts_per_bag"],
+            "nvlink_bytes_per_gpu_per_step": nv_bytes,
+            "nvlink_gbs_in_pool_kernel": nv_bytes / (pool_ms / 1e3) / 1e9 if pool_ms > 0 else None,
+            "nvlink_peak_gbs": 900.0, "nvlink_measured_peer_copy_gbs": 770.0,
+            "limiting_kernel": "pool_kernel (pooling + peer stores)" if pool_ms >= max(x[0] for x in allr)
+                               else "classify + scan + scatter",
+        }
+
+    roofline = None
+    if hooks:
+        bag_avg_ms = sum(bag_ms) / len(bag_ms)
+        achieved = emb_bytes / (bag_avg_ms / 1e3) / 1e9
+        traffic = NCU_BAG_TRAFFIC_BYTES.get((args.batch, float(args.max_rows), args.seed))
+        roofline = {"bound": "hbm", "kernel": bag_kernel,
+                    "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                    "peak_source": peak_source,
+                    "label": "algorithmic GB/s (L2-assisted): algorithmic bytes per launch / kernel time; "
+                             "Zipf-hot rows are served by L2, so DRAM moves less (dram_frac)",
+                    "limited_by": "L2 / row-gather latency, not DRAM bandwidth",
+                    "algorithmic_bytes_per_launch": emb_bytes, "lookups_per_launch": nnz,
+                    "kernel_ms": bag_avg_ms, "traffic": traffic,
+                    "traffic_source": "constant from an offline single-pass ncu capture of this workload "
+                                      "(dram__bytes_read.sum + dram__bytes_write.sum), not measured by this run"
+                                      if traffic else None,
+                    "dram_gbs": traffic / (bag_avg_ms / 1e3) / 1e9 if traffic else None,
+                    "dram_frac": traffic / (bag_avg_ms / 1e3) / 1e9 / hbm_peak if traffic else None}
+    else:
+        roofline = {"bound": "hbm", "kernel": bag_kernel, "achieved": None, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": None, "traffic": None, "peak_source": peak_source,
+                    "note": "the bag kernel is timed alone at N=1; the sharded step's pooling kernel also "
+                            "stores over NVLink: its time and bytes are in `exchange`"}
+        if exchange is not None:
+            pool_ms = exchange["phase_ms_max_over_ranks"][2]
+            roofline.update(kernel_ms=pool_ms, achieved=emb_bytes / (pool_ms / 1e3) / 1e9 if pool_ms else None,
+                            frac=emb_bytes / (pool_ms / 1e3) / 1e9 / hbm_peak if pool_ms else None,
+                            algorithmic_bytes_per_launch=emb_bytes,
+                            label="algorithmic GB/s (L2-assisted) of the pooling + exchange kernel: one rank's "
+                                  "lookups x (row + raw id + segment id) + one output row per bag")
+
+    line = None
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None,
-                "dtype": "tf32" if args.workload == "dlrm" else "bf16", "data": "synthetic",
+                "dtype": "tf32" if not recsys else "bf16", "data": "synthetic",
                 "impl": "annc_b200", "config": workload_config(args, world),
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
@@ -385,7 +511,42 @@ def run_gpu(args):
                 "gpu_launches": pipe.launches_per_step * args.steps,
                 "gemm_kernels": sorted(set(pipe.kernel_names)),
                 "roofline": roofline, "clocks": sampler.summary()}
-        if world == 1 and not args.no_cpu_baseline and args.workload == "recsys":
+        if exchange is not None:
+            line["exchange"] = exchange
+
+    pipe_out = pipe.out.float().cpu().numpy() if (world == 1 and not recsys) else None
+    close(pipe)
+    del pipe
+    torch.cuda.empty_cache()
+
+    # other partitionings, as labelled sub-records of the same line
+    if world > 1 and not recsys and args.extras:
+        extras = {}
+        for mode in [m for m in args.extras.split(",") if m and m != args.shard]:
+            if mode == "row_k0" and args.hot_rows == 0:
+                continue
+            p2 = build(mode)
+            for _ in range(3):
+                p2.forward()
+            torch.cuda.synchronize()
+            assert p2.embed_error_bits() == 0
+            ms2 = timed(p2.forward, args.steps) / args.steps
+            rec = {"value": args.batch * world / (ms2 / 1e3), "unit": UNIT, "ms_per_step": ms2,
+                   "parallelism": parallelism_label(args, world, mode)}
+            rb = getattr(p2, "rowbags", None)
+            if rb is not None:
+                st = rb.exchange_stats()
+                rec["remote_parts_per_bag"] = st["remote_parts_per_bag"]
+                rec["nvlink_bytes_per_gpu_per_step"] = st["nvlink_bytes"]
+            extras[mode] = rec
+            close(p2)
+            del p2
+            torch.cuda.empty_cache()
+        if rank == 0:
+            line["extras"] = extras
+
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline and recsys:
             from oracle import oracle
             threads = oracle.host_threads()
             t = recsys_cpu_timed(args, threads, 2)
@@ -396,23 +557,18 @@ def run_gpu(args):
                                               "min(threads, tables); fp32 MLP on the full batch"
                                               % (args.tables, args.tables)}
         elif world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle
-            threads = oracle.host_threads()
-            t = cpu_forward_timed(model, threads, 3)
-            cpu_ms = 1e3 * sum(t) / len(t)
-            line["cpu_baseline"] = {"value": args.batch / (cpu_ms / 1e3), "unit": UNIT, "cores": threads,
-                                    "kind": "port", "ms_per_step": cpu_ms,
-                                    "sample": "3 full batches of %d samples (C restatement of the "
-                                              "reference kernels, one table per thread, + OpenBLAS sgemm)"
-                                              % args.batch}
+            base, one, parity = cpu_baselines(args, model, pipe_out)
+            line["cpu_baseline"] = base
+            line["cpu_baseline_1thread"] = one
+            line["parity_max_abs_err"] = parity
+            line["parity_note"] = ("max |p_gpu - p_cpu| over the %d predictions of the timed batch "
+                                   "(TF32 tensor-core MLP against fp32 OpenBLAS; bound 2e-3)" % args.batch)
+            assert parity <= 2e-3, "GPU predictions differ from the CPU reference path by %g" % parity
+        if world == 1 and not recsys and not args.no_ops:
+            from annc_b200 import opbench
+            line["ops"] = opbench.ops_record()
         print(json.dumps(line), flush=True)
-    if args.workload == "recsys":
-        pipe.close()
-        dist.destroy_process_group()
-    elif world > 1:
-        if hasattr(pipe, "peer"):
-            torch.cuda.synchronize()
-            pipe.peer.close()
+    if recsys or world > 1:
         dist.destroy_process_group()
 
 
