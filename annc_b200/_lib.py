@@ -86,6 +86,8 @@ def _load() -> C.CDLL:
                                              C.c_int64, C.c_int64, C.c_void_p]
     lib.annc_synth_fill_row_list_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint64,
                                                  C.c_int64, C.c_void_p]
+    lib.annc_set_operand_cache.argtypes = [C.c_int, C.c_size_t]
+    lib.annc_staging_counters.argtypes = [C.POINTER(C.c_uint64)] * 3
     lib.annc_register_constant.argtypes = [C.c_void_p, C.c_size_t]
     lib.annc_unregister_constant.argtypes = [C.c_void_p]
     return lib

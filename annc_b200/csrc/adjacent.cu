@@ -208,7 +208,7 @@ int annc_KPFusedEmbeddingActionIdGather(const annc_tensor* indices1, const annc_
   g.idx2_64 = indices2->dtype == ANNC_I64;
   // both gathers run (and range-check every index) before pack_size is looked at
   auto* d_err = static_cast<int*>(call.scratch(sizeof(int)));
-  g.params = call.in((const float*)params->data, (size_t)numel(*params));
+  g.params = call.in_constant((const float*)params->data, (size_t)numel(*params));
   g.idx1 = call.in(indices1->data, (size_t)numel(*indices1) * dtype_size(indices1->dtype));
   g.idx2 = call.in(indices2->data, (size_t)g.n2 * dtype_size(indices2->dtype));
   if (call.status() != ANNC_OK) return call.status();

@@ -1,6 +1,15 @@
-// Status, stream, staging arena and constant registry of libannc_b200.
+// Status, stream, scratch arena and the host-operand mirrors of libannc_b200.
+//
+// Entry points of groups (1) and (2) accept host pointers, as the reference's callers pass
+// them.  Every host operand gets a device mirror keyed by (pointer, bytes, device) that
+// persists between calls: callers of this ABI reuse their buffers (XLA buffer assignment, TF
+// variables), so a steady workload allocates nothing.  Before an upload the host contents are
+// compared, by a sampled fingerprint, with what the mirror holds; when they agree the upload is
+// skipped.  That makes weights and tables upload once, and an output of one call that comes
+// back as an input of the next (the host copy untouched in between) upload not at all.
 #include "common.h"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -14,15 +23,13 @@ namespace {
 thread_local char g_error[512] = "";
 thread_local cudaStream_t g_stream = nullptr;
 
+// ---- scratch arena: bump allocator over cudaMalloc'd blocks, one per thread and device.
+// Blocks are kept: a call that outgrows them adds one, reset() only rewinds.
 struct Block {
   char* base;
   size_t cap;
   size_t used;
 };
-
-// Bump allocator over cudaMalloc'd blocks.  A call that outgrows the current
-// block gets an extra block; the next call starts from one block of the
-// combined size, so a steady workload settles on a single allocation.
 struct Arena {
   std::vector<Block> blocks;
   ~Arena() { release(); }
@@ -31,21 +38,12 @@ struct Arena {
     blocks.clear();
   }
   void reset() {
-    if (blocks.size() > 1) {
-      size_t total = 0;
-      for (auto& b : blocks) total += b.cap;
-      release();
-      char* p = nullptr;
-      if (cudaMalloc(&p, total) == cudaSuccess) blocks.push_back({p, total, 0});
-    } else if (blocks.size() == 1) {
-      blocks[0].used = 0;
-    }
+    for (auto& b : blocks) b.used = 0;
   }
   void* alloc(size_t bytes) {
     bytes = (bytes + 255) & ~size_t(255);
     if (bytes == 0) bytes = 256;
-    if (!blocks.empty()) {
-      Block& b = blocks.back();
+    for (auto& b : blocks) {
       if (b.used + bytes <= b.cap) {
         void* p = b.base + b.used;
         b.used += bytes;
@@ -59,15 +57,104 @@ struct Arena {
     return p;
   }
 };
-
-thread_local Arena g_arena;
-
-struct Constant {
-  void* dev;
-  size_t bytes;
+struct Arenas {
+  Arena per_device[kMaxDevices];
 };
-std::mutex g_const_mu;
-std::unordered_map<const void*, Constant> g_constants;
+thread_local Arenas g_arenas;
+thread_local cudaStream_t g_last_stream[kMaxDevices] = {nullptr};
+thread_local cudaEvent_t g_last_event[kMaxDevices] = {nullptr};
+thread_local bool g_unsynced[kMaxDevices] = {false};
+
+// ---- mirrors
+struct Key {
+  const void* host;
+  size_t bytes;
+  int device;
+  bool operator==(const Key& o) const { return host == o.host && bytes == o.bytes && device == o.device; }
+};
+struct KeyHash {
+  size_t operator()(const Key& k) const {
+    size_t h = reinterpret_cast<size_t>(k.host) * 0x9E3779B97F4A7C15ull;
+    h ^= k.bytes + 0x7F4A7C15ull + (h << 6) + (h >> 2);
+    return h ^ (size_t)k.device;
+  }
+};
+struct Mirror {
+  void* dev = nullptr;
+  size_t bytes = 0;
+  unsigned long long print = 0;  // fingerprint of the host contents the mirror holds
+  bool valid = false;            // the mirror holds those contents
+  bool pinned = false;           // registered with annc_register_constant: never evicted, never re-checked
+  unsigned long long tick = 0;
+  cudaEvent_t ready = nullptr;   // after the last write of the mirror
+  cudaEvent_t used = nullptr;    // after the last read of the mirror
+  std::unordered_map<int, std::pair<void*, size_t>> derived;  // re-laid forms of a constant, by tag
+};
+std::mutex g_mu;
+std::unordered_map<Key, Mirror, KeyHash> g_mirrors;
+size_t g_mirror_bytes = 0;
+size_t g_mirror_cap = size_t(24) << 30;
+unsigned long long g_tick = 0;
+int g_mode = 2;  // 0: no mirror reuse, 1: constants (weight positions) only, 2: every operand
+std::atomic<unsigned long long> g_staged_h2d{0}, g_staged_d2h{0}, g_skipped_h2d{0};
+
+// One 8-byte word per 4 KiB page (at most `max_samples` of them, evenly spread), the first and
+// the last 64 bytes, and the length.  Operands in weight positions are sampled more thinly
+// (512 words): they change when a model is reloaded, not between two steps.
+unsigned long long fingerprint(const void* p, size_t bytes, size_t max_samples = 16384) {
+  const unsigned char* b = static_cast<const unsigned char*>(p);
+  unsigned long long h = 0xcbf29ce484222325ull ^ bytes;
+  auto mix = [&](unsigned long long v) {
+    h ^= v;
+    h *= 0x100000001b3ull;
+    h ^= h >> 29;
+  };
+  auto word = [&](size_t off) {
+    unsigned long long v = 0;
+    const size_t n = bytes - off < 8 ? bytes - off : 8;
+    memcpy(&v, b + off, n);
+    return v;
+  };
+  if (bytes <= 4096) {
+    for (size_t o = 0; o < bytes; o += 8) mix(word(o));
+    return h;
+  }
+  for (size_t o = 0; o < 64; o += 8) mix(word(o));
+  for (size_t o = bytes - 64; o < bytes; o += 8) mix(word(o));
+  size_t pages = bytes / 4096;
+  size_t step = 4096;
+  if (pages > max_samples) step = (bytes / max_samples) & ~size_t(7);
+  // the sampled word moves inside its page with the page number, so that a regular pattern
+  // (one changed column of a matrix) does not hide between the samples
+  size_t k = 0;
+  for (size_t o = 0; o + 8 <= bytes; o += step, ++k) mix(word(o + ((k * 520) & 4088 & (step - 8))));
+  return h;
+}
+
+void free_mirror(Mirror& m) {
+  if (m.dev) cudaFree(m.dev);
+  for (auto& d : m.derived) cudaFree(d.second.first);
+  if (m.ready) cudaEventDestroy(m.ready);
+  if (m.used) cudaEventDestroy(m.used);
+  g_mirror_bytes -= m.bytes;
+  for (auto& d : m.derived) g_mirror_bytes -= d.second.second;
+}
+
+// Drops least recently used mirrors until `need` more bytes fit under the cap (called with g_mu held).
+void make_room(size_t need, const Key* keep) {
+  while (g_mirror_bytes + need > g_mirror_cap && !g_mirrors.empty()) {
+    auto victim = g_mirrors.end();
+    for (auto it = g_mirrors.begin(); it != g_mirrors.end(); ++it) {
+      if (it->second.pinned || (keep && it->first == *keep)) continue;
+      if (victim == g_mirrors.end() || it->second.tick < victim->second.tick) victim = it;
+    }
+    if (victim == g_mirrors.end()) break;
+    if (victim->second.used) cudaEventSynchronize(victim->second.used);
+    if (victim->second.ready) cudaEventSynchronize(victim->second.ready);
+    free_mirror(victim->second);
+    g_mirrors.erase(victim);
+  }
+}
 
 }  // namespace
 
@@ -107,8 +194,23 @@ size_t dtype_size(int32_t dtype) {
   }
 }
 
-Call::Call() : stream_(g_stream) { g_arena.reset(); }
-Call::~Call() {}
+Call::Call() : stream_(g_stream), device_(device_slot()) {
+  g_arenas.per_device[device_].reset();
+  // A previous call of this thread that returned without synchronising (device pointers only)
+  // may still use the arena's scratch on another stream: order this call's stream after it.
+  if (g_unsynced[device_] && g_last_event[device_] && g_last_stream[device_] != stream_)
+    cudaStreamWaitEvent(stream_, g_last_event[device_], 0);
+}
+Call::~Call() {
+  if (used_scratch_ && !synced_) {
+    if (!g_last_event[device_]) cudaEventCreateWithFlags(&g_last_event[device_], cudaEventDisableTiming);
+    if (g_last_event[device_]) cudaEventRecord(g_last_event[device_], stream_);
+    g_last_stream[device_] = stream_;
+    g_unsynced[device_] = true;
+  } else if (synced_) {
+    g_unsynced[device_] = false;
+  }
+}
 
 bool Call::is_device(const void* p) {
   cudaPointerAttributes attr;
@@ -121,46 +223,102 @@ bool Call::is_device(const void* p) {
   return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
 }
 
-const void* Call::in(const void* p, size_t bytes) {
+// Device mirror of host operand p.  upload: the host contents are needed on the device.
+// role_constant: the operand sits in a weight / table position.
+void* Call::mirror(const void* p, size_t bytes, bool upload, bool role_constant, bool is_output) {
+  if (bytes == 0) bytes = 1;
+  const Key key{p, bytes, device_};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_mirrors.find(key);
+  if (it == g_mirrors.end()) {
+    make_room(bytes, nullptr);
+    Mirror m;
+    cudaError_t e = cudaMalloc(&m.dev, bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      make_room(g_mirror_cap, nullptr);  // drop everything evictable and try once more
+      e = cudaMalloc(&m.dev, bytes);
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      status_ = fail(ANNC_ERR_CUDA, "device allocation of %zu bytes for a host operand failed", bytes);
+      return nullptr;
+    }
+    m.bytes = bytes;
+    cudaEventCreateWithFlags(&m.ready, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&m.used, cudaEventDisableTiming);
+    g_mirror_bytes += bytes;
+    it = g_mirrors.emplace(key, m).first;
+  }
+  Mirror& m = it->second;
+  m.tick = ++g_tick;
+  const bool may_reuse = !m.pinned && (g_mode == 2 || (g_mode == 1 && role_constant));
+  if (upload) {
+    bool need = true;
+    unsigned long long fp = 0;
+    if (m.pinned && m.valid) {
+      need = false;
+    } else if (may_reuse) {
+      fp = fingerprint(p, bytes, role_constant ? 512 : 16384);
+      need = !(m.valid && m.print == fp);
+    }
+    if (need) {
+      // writers wait for the readers and the writer before them
+      cudaStreamWaitEvent(stream_, m.used, 0);
+      cudaStreamWaitEvent(stream_, m.ready, 0);
+      cudaError_t e = cudaMemcpyAsync(m.dev, p, bytes, cudaMemcpyHostToDevice, stream_);
+      if (e != cudaSuccess) {
+        status_ = cuda_fail(e, "cudaMemcpyAsync(H2D)");
+        return nullptr;
+      }
+      cudaEventRecord(m.ready, stream_);
+      g_staged_h2d += bytes;
+      m.valid = may_reuse;
+      m.print = fp;
+      for (auto& d : m.derived) {  // re-laid forms are stale now
+        cudaFree(d.second.first);
+        g_mirror_bytes -= d.second.second;
+      }
+      m.derived.clear();
+      staged_ = true;
+    } else {
+      cudaStreamWaitEvent(stream_, m.ready, 0);
+      g_skipped_h2d += bytes;
+    }
+    touched_.push_back({key.host, key.bytes, key.device});
+  } else if (is_output) {
+    cudaStreamWaitEvent(stream_, m.used, 0);
+    cudaStreamWaitEvent(stream_, m.ready, 0);
+    m.valid = false;  // becomes valid again in finish(), once the host copy exists
+    for (auto& d : m.derived) {
+      cudaFree(d.second.first);
+      g_mirror_bytes -= d.second.second;
+    }
+    m.derived.clear();
+  }
+  return m.dev;
+}
+
+const void* Call::in(const void* p, size_t bytes) { return in_role(p, bytes, false); }
+const void* Call::in_constant(const void* p, size_t bytes) { return in_role(p, bytes, true); }
+
+const void* Call::in_role(const void* p, size_t bytes, bool role_constant) {
   if (p == nullptr || status_ != ANNC_OK) return nullptr;
   if (is_device(p)) return p;
   if (status_ != ANNC_OK) return nullptr;
-  {
-    std::lock_guard<std::mutex> lk(g_const_mu);
-    auto it = g_constants.find(p);
-    if (it != g_constants.end() && it->second.bytes >= bytes) return it->second.dev;
-  }
-  void* d = g_arena.alloc(bytes);
-  if (!d) {
-    status_ = fail(ANNC_ERR_CUDA, "device staging allocation of %zu bytes failed", bytes);
-    return nullptr;
-  }
-  if (bytes) {
-    cudaError_t e = cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, stream_);
-    if (e != cudaSuccess) {
-      status_ = cuda_fail(e, "cudaMemcpyAsync(H2D)");
-      return nullptr;
-    }
-  }
-  staged_ = true;
-  return d;
+  return mirror(p, bytes, true, role_constant, false);
 }
 
 void* Call::out(void* p, size_t bytes, bool preload) {
   if (p == nullptr || status_ != ANNC_OK) return nullptr;
   if (is_device(p)) return p;
   if (status_ != ANNC_OK) return nullptr;
-  void* d = g_arena.alloc(bytes);
-  if (!d) {
-    status_ = fail(ANNC_ERR_CUDA, "device staging allocation of %zu bytes failed", bytes);
-    return nullptr;
-  }
-  if (preload && bytes) {
-    cudaError_t e = cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, stream_);
-    if (e != cudaSuccess) {
-      status_ = cuda_fail(e, "cudaMemcpyAsync(H2D)");
-      return nullptr;
-    }
+  void* d = preload ? mirror(p, bytes, true, false, false) : mirror(p, bytes, false, false, true);
+  if (!d) return nullptr;
+  if (preload) {  // the call overwrites what was uploaded
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_mirrors.find(Key{p, bytes ? bytes : 1, device_});
+    if (it != g_mirrors.end()) it->second.valid = false;
   }
   pending_.push_back({p, d, bytes});
   staged_ = true;
@@ -169,9 +327,33 @@ void* Call::out(void* p, size_t bytes, bool preload) {
 
 void* Call::scratch(size_t bytes) {
   if (status_ != ANNC_OK) return nullptr;
-  void* d = g_arena.alloc(bytes);
+  void* d = g_arenas.per_device[device_].alloc(bytes);
   if (!d) status_ = fail(ANNC_ERR_CUDA, "device scratch allocation of %zu bytes failed", bytes);
+  used_scratch_ = true;
   return d;
+}
+
+// A re-laid form (`tag`) of constant host operand p, kept with its mirror: returns the cached
+// device buffer, or allocates `out_bytes` and sets *fresh so that the caller fills it.
+void* Call::derived(const void* p, size_t bytes, int tag, size_t out_bytes, bool* fresh) {
+  *fresh = false;
+  if (status_ != ANNC_OK) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_mirrors.find(Key{p, bytes ? bytes : 1, device_});
+  if (it == g_mirrors.end() || !it->second.valid) return nullptr;  // not a mirrored, reusable operand
+  Mirror& m = it->second;
+  auto d = m.derived.find(tag);
+  if (d != m.derived.end() && d->second.second == out_bytes) return d->second.first;
+  make_room(out_bytes, &it->first);
+  void* buf = nullptr;
+  if (cudaMalloc(&buf, out_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  m.derived[tag] = {buf, out_bytes};
+  g_mirror_bytes += out_bytes;
+  *fresh = true;
+  return buf;
 }
 
 int Call::read_host(const void* p, size_t bytes, void* dst) {
@@ -184,6 +366,7 @@ int Call::read_host(const void* p, size_t bytes, void* dst) {
   cudaError_t e = cudaMemcpyAsync(dst, p, bytes, cudaMemcpyDeviceToHost, stream_);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
   if (e != cudaSuccess) status_ = cuda_fail(e, "read_host");
+  synced_ = true;
   return status_;
 }
 
@@ -193,12 +376,36 @@ int Call::finish() {
     if (!o.bytes) continue;
     cudaError_t e = cudaMemcpyAsync(o.host, o.dev, o.bytes, cudaMemcpyDeviceToHost, stream_);
     if (e != cudaSuccess) return status_ = cuda_fail(e, "cudaMemcpyAsync(D2H)");
+    g_staged_d2h += o.bytes;
   }
-  pending_.clear();
+  {  // this call's reads and writes of the mirrors end here on its stream
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto& k : touched_) {
+      auto it = g_mirrors.find(Key{k.host, k.bytes, k.device});
+      if (it != g_mirrors.end()) cudaEventRecord(it->second.used, stream_);
+    }
+    for (auto& o : pending_) {
+      auto it = g_mirrors.find(Key{o.host, o.bytes ? o.bytes : 1, device_});
+      if (it != g_mirrors.end()) cudaEventRecord(it->second.ready, stream_);
+    }
+  }
   if (staged_) {
     cudaError_t e = cudaStreamSynchronize(stream_);
     if (e != cudaSuccess) return status_ = cuda_fail(e, "cudaStreamSynchronize");
+    synced_ = true;
+    // the host copies exist now: an output mirror holds exactly what the host buffer holds
+    if (g_mode == 2 && !pending_.empty()) {
+      std::lock_guard<std::mutex> lk(g_mu);
+      for (auto& o : pending_) {
+        auto it = g_mirrors.find(Key{o.host, o.bytes ? o.bytes : 1, device_});
+        if (it == g_mirrors.end() || !o.bytes) continue;
+        it->second.print = fingerprint(o.host, o.bytes);
+        it->second.valid = true;
+      }
+    }
   }
+  pending_.clear();
+  touched_.clear();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return status_ = cuda_fail(e, "kernel launch");
   return ANNC_OK;
@@ -210,34 +417,64 @@ extern "C" {
 
 const char* annc_last_error(void) { return annc::g_error; }
 
-const char* annc_version(void) { return "annc_b200 0.1.0 sm_100a"; }
+const char* annc_version(void) { return "annc_b200 0.2.0 sm_100a"; }
 
 void annc_set_stream(void* s) { annc::g_stream = static_cast<cudaStream_t>(s); }
 void* annc_get_stream(void) { return annc::g_stream; }
 
 int annc_register_constant(const void* ptr, size_t bytes) {
   if (!ptr || !bytes) return annc::fail(ANNC_ERR_INVALID_ARGUMENT, "null constant");
-  void* d = nullptr;
-  ANNC_CUDA(cudaMalloc(&d, bytes));
-  cudaError_t e = cudaMemcpy(d, ptr, bytes, cudaMemcpyHostToDevice);
-  if (e != cudaSuccess) {
-    cudaFree(d);
-    return annc::cuda_fail(e, "cudaMemcpy(constant)");
+  using namespace annc;
+  const Key key{ptr, bytes, device_slot()};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_mirrors.find(key);
+  if (it == g_mirrors.end()) {
+    Mirror m;
+    ANNC_CUDA(cudaMalloc(&m.dev, bytes));
+    m.bytes = bytes;
+    cudaEventCreateWithFlags(&m.ready, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&m.used, cudaEventDisableTiming);
+    g_mirror_bytes += bytes;
+    it = g_mirrors.emplace(key, m).first;
   }
-  std::lock_guard<std::mutex> lk(annc::g_const_mu);
-  auto it = annc::g_constants.find(ptr);
-  if (it != annc::g_constants.end()) cudaFree(it->second.dev);
-  annc::g_constants[ptr] = {d, bytes};
+  Mirror& m = it->second;
+  if (m.used) cudaEventSynchronize(m.used);
+  cudaError_t e = cudaMemcpy(m.dev, ptr, bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(constant)");
+  g_staged_h2d += bytes;
+  m.valid = true;
+  m.pinned = true;
+  m.print = fingerprint(ptr, bytes);
   return ANNC_OK;
 }
 
 int annc_unregister_constant(const void* ptr) {
-  std::lock_guard<std::mutex> lk(annc::g_const_mu);
-  auto it = annc::g_constants.find(ptr);
-  if (it == annc::g_constants.end()) return ANNC_ERR_INVALID_ARGUMENT;
-  cudaFree(it->second.dev);
-  annc::g_constants.erase(it);
+  using namespace annc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  const int dev = device_slot();
+  for (auto it = g_mirrors.begin(); it != g_mirrors.end(); ++it) {
+    if (it->first.host == ptr && it->first.device == dev && it->second.pinned) {
+      cudaDeviceSynchronize();
+      free_mirror(it->second);
+      g_mirrors.erase(it);
+      return ANNC_OK;
+    }
+  }
+  return ANNC_ERR_INVALID_ARGUMENT;
+}
+
+int annc_set_operand_cache(int mode, size_t max_bytes) {
+  if (mode < 0 || mode > 2) return annc::fail(ANNC_ERR_INVALID_ARGUMENT, "operand cache mode must be 0, 1 or 2");
+  std::lock_guard<std::mutex> lk(annc::g_mu);
+  annc::g_mode = mode;
+  if (max_bytes) annc::g_mirror_cap = max_bytes;
   return ANNC_OK;
+}
+
+void annc_staging_counters(uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint64_t* h2d_skipped_bytes) {
+  if (h2d_bytes) *h2d_bytes = annc::g_staged_h2d.load();
+  if (d2h_bytes) *d2h_bytes = annc::g_staged_d2h.load();
+  if (h2d_skipped_bytes) *h2d_skipped_bytes = annc::g_skipped_h2d.load();
 }
 
 void* annc_timer_create(void) {
@@ -259,10 +496,13 @@ void annc_embed_bag_set_timing_events(void* start, void* stop) {
 }
 
 void annc_release_device_memory(void) {
-  annc::g_arena.release();
-  std::lock_guard<std::mutex> lk(annc::g_const_mu);
-  for (auto& kv : annc::g_constants) cudaFree(kv.second.dev);
-  annc::g_constants.clear();
+  using namespace annc;
+  cudaDeviceSynchronize();
+  for (auto& a : g_arenas.per_device) a.release();
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (auto& kv : g_mirrors) free_mirror(kv.second);
+  g_mirrors.clear();
+  g_mirror_bytes = 0;
 }
 
 }  // extern "C"

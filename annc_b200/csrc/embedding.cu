@@ -30,7 +30,34 @@ static void launch_bag(const BagParams& p, BagHeader* hdr, int* offsets, cudaStr
   else bag_reduce_kernel<LANES, VPL, false><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
 }
 
-// Launches prepass + bag kernels (+ the atomic route) for up to kMaxTables tables.
+template <int LANES, int VPL, int TILES, int INFLIGHT, int MINB>
+static void launch_stream(const BagParams& p, BagHeader* hdr, cudaStream_t s) {
+  static int per_sm[kMaxDevices] = {0};
+  const int slot = device_slot();
+  if (!per_sm[slot]) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, bag_stream_kernel<LANES, VPL, TILES, INFLIGHT, MINB>,
+                                                      256, 0) != cudaSuccess || n < 1)
+      n = 2;
+    per_sm[slot] = n;
+  }
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, slot);
+  StreamChunks sc;
+  long long total = 0;
+  for (int t = 0; t < p.num_tables; ++t) {
+    sc.first[t] = (int)total;
+    const long long n = p.t[t].nnz;
+    total += n > 0 ? (n + LANES * TILES - 1) / (LANES * TILES) : (p.batch + 1023) / 1024;
+  }
+  sc.first[p.num_tables] = (int)total;
+  // a persistent grid, no larger than the chunks there are
+  const long long groups_per_block = (256 / 32) * (32 / LANES);
+  long long blocks = std::min<long long>((long long)sms * per_sm[slot], (total + groups_per_block - 1) / groups_per_block);
+  bag_stream_kernel<LANES, VPL, TILES, INFLIGHT, MINB><<<(unsigned)std::max<long long>(blocks, 1), 256, 0, s>>>(p, sc, hdr);
+}
+
+// Launches the bag kernels (+ the atomic route) for up to kMaxTables tables.
 static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, int id_kind,
                     int64_t ncols, int32_t col, int combiner, int64_t batch, int64_t out_stride,
                     BagHeader* hdr, int* offsets, cudaStream_t s, int shard_count = 1,
@@ -72,21 +99,53 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
   if (batch <= 0) return ANNC_OK;
 
   dim3 pre_grid(grid_for(max_nnz + 1, 256), num_tables);
-  bool seg16 = ncols == 2, need_prepass = false;
+  bool seg16 = ncols == 2, need_prepass = false, any_offsets = false;
   for (int t = 0; t < num_tables; ++t) {
-    if (tables[t].offsets) continue;
+    if (tables[t].offsets) {
+      any_offsets = true;
+      continue;
+    }
     need_prepass = true;
     seg16 = seg16 && aligned16(tables[t].slice_input);
   }
+  const int vecs = vec_ok ? (int)(dim / 4) : 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  timing_events(&ev0, &ev1);
+
+  // Lookup-granular route: no prepass, one pass over ids and segment ids.  Taken when every
+  // table comes with its index matrix (no caller-supplied offsets), unsharded, 16-byte rows.
+  const bool stream = !any_offsets && shard_count == 1 && vecs >= 4 && batch < (1LL << 31) - 1 &&
+                      (vecs == 4 || vecs == 8 || vecs == 16 || vecs == 32 || vecs == 64 || vecs == 128);
+  if (stream) {
+    if (ev0) cudaEventRecord(ev0, s);
+    switch (vecs) {
+      case 4: launch_stream<4, 1, 8, 4, 5>(p, hdr, s); break;
+      case 8: launch_stream<8, 1, 8, 4, 5>(p, hdr, s); break;
+      case 16: launch_stream<16, 1, 8, 4, 5>(p, hdr, s); break;
+      case 32: launch_stream<32, 1, 8, 4, 5>(p, hdr, s); break;
+      case 64: launch_stream<32, 2, 8, 4, 4>(p, hdr, s); break;
+      default: launch_stream<32, 4, 8, 2, 3>(p, hdr, s); break;
+    }
+    if (ev1) cudaEventRecord(ev1, s);
+    dim3 rs_grid(148, num_tables);
+    bag_stream_reset_kernel<<<rs_grid, 256, 0, s>>>(p, hdr, offsets);  // returns at once for sorted tables
+    dim3 sc_grid(grid_for(max_nnz, 8, 148), num_tables);
+    bag_scatter_kernel<<<sc_grid, 256, 0, s>>>(p, hdr, offsets);
+    if (combiner == 1) {
+      dim3 mean_grid(grid_for(batch * dim, 256, 148), num_tables);
+      bag_scatter_mean_kernel<<<mean_grid, 256, 0, s>>>(p, hdr, offsets);
+    }
+    cudaError_t es = cudaGetLastError();
+    if (es != cudaSuccess) return cuda_fail(es, "embedding bag launch");
+    return ANNC_OK;
+  }
+
   if (need_prepass) {  // tables that brought their offsets are skipped inside the kernel
     if (seg16) bag_prepass2_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
     else bag_prepass_kernel<<<pre_grid, 256, 0, s>>>(p, hdr, offsets);
   }
 
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-  timing_events(&ev0, &ev1);
   if (ev0) cudaEventRecord(ev0, s);
-  const int vecs = vec_ok ? (int)(dim / 4) : 0;
   switch (vecs) {
     case 1: launch_bag<1, 1>(p, hdr, offsets, s); break;
     case 2: launch_bag<2, 1>(p, hdr, offsets, s); break;
@@ -392,7 +451,9 @@ int annc_embed_bags_static_dev(const annc_bag_table* tables, int num_tables, int
   auto* hdr = static_cast<BagHeader*>(ws);
   int* offsets = reinterpret_cast<int*>(static_cast<char*>(ws) + kHeaderBytes);
   // The array keeps the previous call's contents: the header (error word, unsorted
-  // marks) must start at zero; the offsets are fully rewritten by the prepass.
+  // marks) must start at zero.  The offsets are written before they are read: by the
+  // prepass on the offsets route, and as per-bag counters cleared by the reset kernel for a
+  // table whose segment ids turn out unsorted.
   ANNC_CUDA(cudaMemsetAsync(hdr, 0, kHeaderBytes, s));
   for (int t0 = 0; t0 < num_tables; t0 += kMaxTables) {
     const int nt = std::min(kMaxTables, num_tables - t0);
@@ -432,7 +493,7 @@ int annc_KPFusedSparseSegmentReduce(const annc_tensor* data, const annc_tensor* 
                "indices and slice_input.dim_zie(0) should have same size");
 
   cudaStream_t s = call.stream();
-  const float* d_data = call.in((const float*)data->data, (size_t)numel(*data));
+  const float* d_data = call.in_constant((const float*)data->data, (size_t)numel(*data));
   const void* d_idx = call.in(indices->data, (size_t)nnz * dtype_size(indices->dtype));
   const int64_t* d_seg = call.in((const int64_t*)slice_input->data, (size_t)(nnz * ncols));
   auto* d_max = static_cast<long long*>(call.scratch(sizeof(long long)));
@@ -510,7 +571,7 @@ int annc_KPFusedSparseSegmentReduceNonzero(const annc_tensor* data, const annc_t
   const int64_t dim = rank == 2 ? data->dims[1] : 1;
 
   cudaStream_t s = call.stream();
-  const float* d_data = call.in((const float*)data->data, (size_t)numel(*data));
+  const float* d_data = call.in_constant((const float*)data->data, (size_t)numel(*data));
   const void* d_idx = call.in(indices->data, (size_t)nnz * dtype_size(indices->dtype));
   const int64_t* d_seg = call.in((const int64_t*)slice_input->data, (size_t)(nnz * ncols));
   auto* d_max = static_cast<long long*>(call.scratch(sizeof(long long)));
@@ -607,7 +668,7 @@ int annc_KPFusedGather(const annc_tensor* data, const annc_tensor* keys, const a
   const int64_t idx_dims[1] = {nnz};
   int32_t* out_inv = static_cast<int32_t*>(alloc(ctx, 1, ANNC_I32, 1, idx_dims));
   ANNC_REQUIRE(out_inv || nnz == 0, ANNC_ERR_INTERNAL, "output allocation failed");
-  const float* d_data = call.in((const float*)data->data, (size_t)numel(*data));
+  const float* d_data = call.in_constant((const float*)data->data, (size_t)numel(*data));
   const int64_t* d_keys = call.in((const int64_t*)keys->data, (size_t)(nnz * ncols));
   int32_t* d_inv = nnz > 0 ? call.out(out_inv, (size_t)nnz) : nullptr;
   auto* d_unique = static_cast<long long*>(call.scratch(std::max<int64_t>(nnz, 1) * sizeof(long long)));
@@ -667,7 +728,7 @@ int annc_KPFusedSparseDynamicStitch(const annc_tensor* x, const annc_tensor* tab
   std::vector<const float*> ptrs(num_tables);
   std::vector<long long> rows(num_tables);
   for (int i = 0; i < num_tables; ++i) {
-    ptrs[i] = call.in((const float*)tables[i].data, (size_t)numel(tables[i]));
+    ptrs[i] = call.in_constant((const float*)tables[i].data, (size_t)numel(tables[i]));
     rows[i] = tables[i].dims[0];
   }
   auto* d_ptrs = static_cast<const float**>(call.scratch(num_tables * sizeof(float*)));
@@ -711,7 +772,7 @@ int annc_KPFusedEmbeddingWithHashBucket(const annc_tensor* fingerprints, const a
   if (n * dim == 0) return ANNC_OK;
   GatherParams g;
   memset(&g, 0, sizeof(g));
-  g.table = call.in((const float*)variable->data, (size_t)numel(*variable));
+  g.table = call.in_constant((const float*)variable->data, (size_t)numel(*variable));
   g.ids = call.in(fingerprints->data, (size_t)n * 8);
   g.empty = (empty && empty->data) ? call.in((const unsigned char*)empty->data, (size_t)n) : nullptr;
   g.out = call.out(out, (size_t)(n * dim));
@@ -744,7 +805,7 @@ int annc_sparse_embedding2(const annc_tensor* ids, const annc_tensor* table, int
   if (n * dim == 0) return ANNC_OK;
   GatherParams g;
   memset(&g, 0, sizeof(g));
-  g.table = call.in((const float*)table->data, (size_t)numel(*table));
+  g.table = call.in_constant((const float*)table->data, (size_t)numel(*table));
   g.ids = call.in(ids->data, (size_t)n * dtype_size(ids->dtype));
   g.out = call.out(out, (size_t)(n * dim));
   g.n = n;

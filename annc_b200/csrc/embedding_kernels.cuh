@@ -330,6 +330,199 @@ bag_reduce_generic_kernel(BagParams p, BagHeader* hdr, int* offsets) {
   }
 }
 
+// ---- lookup-granular bag kernel ------------------------------------------------------
+// The same pooling without a prepass: blockIdx.y = table; a group of LANES lanes takes a chunk
+// of TILES * LANES consecutive lookups of the table (tile by tile: one lookup per lane, ids and
+// segment ids read with coalesced loads, the hash-bucket modulo applied by the lane that read
+// the id) and owns the bags whose first lookup lies in the chunk; it follows its last bag past
+// the chunk until the segment id changes.  Bag boundaries inside a tile are one ballot; rows are
+// added in lookup order into a zero accumulator (the reference's order, bit-identical sums),
+// INFLIGHT row loads in flight per group.  Work per group does not depend on the bag lengths and
+// short bags leave no lanes idle.  Bags without lookups are zero-filled by the group that owns
+// the next bag (the first bag's owner fills from 0, the last bag's owner to the end).  A
+// decrease of the segment ids marks the table unsorted: bag_stream_reset_kernel then clears its
+// output and the atomic route below redoes it.
+// Chunk numbering of bag_stream_kernel over all tables of a launch: table t owns the chunks
+// [first[t], first[t + 1]); a table without lookups gets one chunk per 1024 bags to zero.
+struct StreamChunks {
+  int first[kMaxTables + 1];
+};
+
+template <int LANES, int VPL, int TILES, int INFLIGHT_, int MINB>
+__global__ void __launch_bounds__(256, MINB)
+bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
+  constexpr int GROUPS_PER_WARP = 32 / LANES;
+  constexpr int CHUNK = LANES * TILES;
+  constexpr int INFLIGHT = LANES < INFLIGHT_ ? LANES : INFLIGHT_;
+  constexpr int ROW4 = LANES * VPL;
+  constexpr unsigned kLaneMask = LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u);
+  constexpr int kNoBag = -3;  // a lookup whose segment id is out of range is added nowhere
+  __shared__ int s_first[kMaxTables + 1];
+  for (int i = threadIdx.x; i <= p.num_tables; i += blockDim.x) s_first[i] = sc.first[i];
+  __syncthreads();
+  const int batch = (int)p.batch;
+  const int lane_in_warp = threadIdx.x & 31;
+  const int lane = lane_in_warp % LANES;
+  const int shift = (lane_in_warp / LANES) * LANES;
+  const unsigned gmask = kLaneMask << shift;
+  const unsigned group = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GROUPS_PER_WARP +
+                         lane_in_warp / LANES;
+  const unsigned num_groups = gridDim.x * (blockDim.x >> 5) * GROUPS_PER_WARP;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const unsigned total_chunks = (unsigned)s_first[p.num_tables];
+
+  // Consecutive groups take consecutive chunks, so the whole grid works through one table
+  // after the other and ends together.
+  for (unsigned gc = group; gc < total_chunks; gc += num_groups) {
+    int lo = 0, hi = p.num_tables - 1;  // table of chunk gc: last t with first[t] <= gc
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((unsigned)s_first[mid] <= gc) lo = mid;
+      else hi = mid - 1;
+    }
+    const int t = lo;
+    const unsigned chunk = gc - (unsigned)s_first[t];
+    const BagTableDev& T = p.t[t];
+    const int n = T.nnz;
+    const float4* __restrict__ tab = reinterpret_cast<const float4*>(T.table);
+    float* __restrict__ outp = T.out;
+
+    // rows [a, b) of the output <- 0 (bags without lookups)
+    auto zero_fill = [&](int a, int b) {
+      for (int s = a; s < b; ++s) {
+        float4* o = reinterpret_cast<float4*>(outp + (long long)s * p.out_stride);
+#pragma unroll
+        for (int w = 0; w < VPL; ++w) o[w * LANES + lane] = zero4;
+      }
+    };
+    if (n == 0) {  // a table without lookups: every bag is empty
+      zero_fill((int)min((long long)chunk * 1024, (long long)batch), (int)min((long long)(chunk + 1) * 1024, (long long)batch));
+      continue;
+    }
+    {
+    float4 acc[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) acc[v] = zero4;
+    int cur = kNoBag;   // bag being summed
+    int count = 0;      // its lookups so far (for the mean)
+    bool open = false;
+    const int chunk_end = min(n, (int)(chunk + 1) * CHUNK);
+
+    auto flush = [&]() {
+      if (open && cur >= 0) {
+        if (p.combiner == 1 && count > 0) {
+          const float inv = __fdiv_rn(1.0f, (float)count);
+#pragma unroll
+          for (int w = 0; w < VPL; ++w) {
+            acc[w].x = __fmul_rn(acc[w].x, inv);
+            acc[w].y = __fmul_rn(acc[w].y, inv);
+            acc[w].z = __fmul_rn(acc[w].z, inv);
+            acc[w].w = __fmul_rn(acc[w].w, inv);
+          }
+        }
+        float4* o = reinterpret_cast<float4*>(outp + (long long)cur * p.out_stride);
+#pragma unroll
+        for (int w = 0; w < VPL; ++w) o[w * LANES + lane] = acc[w];
+      }
+    };
+
+    for (int base = (int)chunk * CHUNK; base < n; base += LANES) {
+      const int i = base + lane;
+      int key = kNoBag, row = -1;
+      if (i < n) {
+        const long long seg = T.seg[(long long)i * p.ncols + p.col];
+        const long long r64 = load_row_id(T.ids, p.id_kind, i, T.num_buckets, T.magic);
+        if (seg < 0 || seg >= batch) atomicOr(&hdr->err_bits, kErrSegment);
+        else key = (int)seg;
+        if (r64 < 0 || r64 >= T.rows) atomicOr(&hdr->err_bits, kErrRow);
+        else row = (int)r64;
+      }
+      int prev_key = __shfl_up_sync(gmask, key, 1, LANES);
+      if (lane == 0) {
+        prev_key = -1;  // before the first lookup: bags 0 .. key-1 are empty
+        if (base > 0) {
+          const long long ps = T.seg[(long long)(base - 1) * p.ncols + p.col];
+          prev_key = (ps < 0 || ps >= batch) ? kNoBag : (int)ps;
+        }
+      }
+      const bool starts = (i < n) && (key != prev_key);
+      if (starts && key >= 0 && prev_key >= 0 && key < prev_key) hdr->unsorted[t] = 1;
+      const unsigned smask = (__ballot_sync(gmask, starts) >> shift) & kLaneMask;
+      const int tile_n = min(LANES, n - base);
+      int from = 0, to = tile_n;
+      const bool inside = base < chunk_end;
+      if (!open) {
+        if (!inside) break;
+        if (smask == 0) continue;
+        from = __ffs(smask) - 1;
+      } else if (!inside) {
+        if (smask != 0) to = __ffs(smask) - 1;
+      }
+      for (int j0 = from; j0 < to; j0 += INFLIGHT) {
+        float4 v[INFLIGHT][VPL];
+        bool has[INFLIGHT];
+#pragma unroll
+        for (int k = 0; k < INFLIGHT; ++k) {
+          const int j = j0 + k;
+          has[k] = false;
+          if (j < to) {
+            const int rw = __shfl_sync(gmask, row, j, LANES);
+            has[k] = rw >= 0;
+            if (has[k]) {
+              const float4* src = tab + (long long)rw * ROW4 + lane;
+#pragma unroll
+              for (int w = 0; w < VPL; ++w) v[k][w] = __ldg(src + w * LANES);
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < INFLIGHT; ++k) {
+          const int j = j0 + k;
+          if (j < to) {
+            if ((smask >> j) & 1u) {
+              flush();
+#pragma unroll
+              for (int w = 0; w < VPL; ++w) acc[w] = zero4;
+              cur = __shfl_sync(gmask, key, j, LANES);
+              const int before = __shfl_sync(gmask, prev_key, j, LANES);
+              // empty bags between the previous lookup's bag and this one (sorted input only)
+              if (cur >= 0 && before >= -1 && before < cur - 1) zero_fill(before + 1, cur);
+              count = 0;
+              open = true;
+            }
+            ++count;
+            if (has[k]) {
+#pragma unroll
+              for (int w = 0; w < VPL; ++w) add4(acc[w], v[k][w]);
+            }
+          }
+        }
+      }
+      if (!inside && to < tile_n) break;
+      // the table's last lookup: bags after its bag are empty
+      if (base + tile_n >= n && to == tile_n && open && cur >= 0) zero_fill(cur + 1, batch);
+    }
+    flush();
+    }
+  }
+}
+
+// Tables marked unsorted: zero the output and the per-bag counters for the atomic route.
+__global__ void __launch_bounds__(256)
+bag_stream_reset_kernel(BagParams p, BagHeader* hdr, int* offsets) {
+  const int t = blockIdx.y;
+  if (!hdr->unsorted[t]) return;
+  const BagTableDev& T = p.t[t];
+  int* counts = offsets + (long long)t * (p.batch + 1);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long total = p.batch * p.dim;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const long long s = e / p.dim, c = e - s * p.dim;
+    T.out[s * p.out_stride + c] = 0.f;
+    if (c == 0) counts[s] = 0;
+  }
+}
+
 // ---- unsorted route: atomic scatter (sum order not defined; within 1e-5 rel) ----
 __global__ void __launch_bounds__(256)
 bag_scatter_kernel(BagParams p, BagHeader* hdr, int* offsets) {

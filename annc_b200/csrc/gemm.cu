@@ -127,36 +127,50 @@ bf16_weight_kernel(const float* __restrict__ src, long long ldb, __nv_bfloat16* 
 
 }  // namespace
 
-// Unpacks a kn4 B into `ws` when that pays off; returns true and fills `plain` with the
-// descriptor of the equivalent plain-layout GEMM.
-static bool unpack_kn4_into_workspace(const annc_gemm_desc& d, cudaStream_t s, annc_gemm_desc* plain) {
-  if (d.b_format != ANNC_B_KN4 || !d.workspace || d.batch != 1) return false;
-  if (d.workspace_bytes < (size_t)d.k * (size_t)d.n * sizeof(float)) return false;
-  if ((reinterpret_cast<uintptr_t>(d.workspace) & 15) || (d.n & 3) || d.m < 512) return false;
-  if (d.k >= (1LL << 31) || d.n >= (1LL << 31)) return false;
+// Re-laying a kn4 B into a workspace of 4*K*N bytes.  relaid_desc() says whether that pays off
+// for this descriptor and returns the descriptor of the equivalent plain-layout GEMM over `ws`
+// together with the form the weight has to take there (1 = [N,K], 2 = [K,N]); relay_kn4() runs
+// the conversion.  Kept apart so that a caller that owns a cache of constants converts once.
+int relaid_desc(const annc_gemm_desc& d, void* ws, size_t ws_bytes, annc_gemm_desc* plain) {
+  if (d.b_format != ANNC_B_KN4 || !ws || d.batch != 1) return 0;
+  if (ws_bytes < (size_t)d.k * (size_t)d.n * sizeof(float)) return 0;
+  if ((reinterpret_cast<uintptr_t>(ws) & 15) || (d.n & 3) || d.m < 64) return 0;
+  if (d.k >= (1LL << 31) || d.n >= (1LL << 31)) return 0;
   *plain = d;
-  plain->b = static_cast<const float*>(d.workspace);
+  plain->b = static_cast<const float*>(ws);
   plain->b_format = ANNC_B_PLAIN;
   plain->ldb = d.n;
   plain->workspace = nullptr;
   plain->workspace_bytes = 0;
-  // Re-laid as [N,K] the weight takes the K-major TMA route of the CTA-pair kernel (one 16 KB
-  // box per stage), the fastest one; [K,N] is the fallback when K rows would not be 16-byte pitched.
+  // Re-laid as [N,K] the weight takes the K-major TMA route (one 16 KB box per stage), the
+  // fastest one; [K,N] is the fallback when K rows would not be 16-byte pitched.
   if ((d.k & 3) == 0 && (d.k + 31) / 32 <= 65535) {
     annc_gemm_desc t = *plain;
     t.trans_b = 1;
     t.ldb = d.k;
     if (pair_supported(t, ANNC_MATH_TF32) && use_pair(t, ANNC_MATH_TF32)) {
-      dim3 grid((unsigned)((d.n + 31) / 32), (unsigned)((d.k + 31) / 32));
-      kn4_unpack_transposed_kernel<<<grid, 256, 0, s>>>(d.b, static_cast<float*>(d.workspace), d.k, d.n);
       *plain = t;
-      return true;
+      return 1;
     }
   }
-  if (!tc_supported(*plain, ANNC_MATH_TF32)) return false;
-  dim3 grid((unsigned)((d.n / 4 + 255) / 256), (unsigned)(d.k < 1024 ? d.k : 1024));
-  kn4_unpack_chunks_kernel<<<grid, 256, 0, s>>>(d.b, static_cast<float*>(d.workspace), (int)d.k,
-                                                (int)d.n);
+  if (!tc_supported(*plain, ANNC_MATH_TF32)) return 0;
+  return 2;
+}
+
+void relay_kn4(const float* packed, float* ws, long long k, long long n, int form, cudaStream_t s) {
+  if (form == 1) {
+    dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k + 31) / 32));
+    kn4_unpack_transposed_kernel<<<grid, 256, 0, s>>>(packed, ws, k, n);
+  } else {
+    dim3 grid((unsigned)((n / 4 + 255) / 256), (unsigned)(k < 1024 ? k : 1024));
+    kn4_unpack_chunks_kernel<<<grid, 256, 0, s>>>(packed, ws, (int)k, (int)n);
+  }
+}
+
+static bool unpack_kn4_into_workspace(const annc_gemm_desc& d, cudaStream_t s, annc_gemm_desc* plain) {
+  const int form = relaid_desc(d, d.workspace, d.workspace_bytes, plain);
+  if (!form) return false;
+  relay_kn4(d.b, static_cast<float*>(d.workspace), d.k, d.n, form, s);
   return true;
 }
 

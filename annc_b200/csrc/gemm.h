@@ -25,6 +25,14 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s);
 bool pair_supported(const annc_gemm_desc& d, int math);
 int run_pair(const annc_gemm_desc& d, int math, cudaStream_t s);
 
+// A kn4-packed B re-laid into `ws` (4*K*N bytes): relaid_desc returns 0 when that does not
+// pay off, else the form the weight takes in ws (1 = [N,K], 2 = [K,N]) and fills `plain`
+// with the equivalent plain-layout descriptor; relay_kn4 runs the conversion.
+int relaid_desc(const annc_gemm_desc& d, void* ws, size_t ws_bytes, annc_gemm_desc* plain);
+void relay_kn4(const float* packed, float* ws, long long k, long long n, int form, cudaStream_t s);
+// Device-side error word of the tensor-core kernels (a bounded wait that ran out).
+int read_error_flag(int* flag);
+
 // Picks the route the way annc_gemm_run does; returns a static name.
 const char* route_name(const annc_gemm_desc& d);
 

@@ -467,6 +467,14 @@ int read_error_flag(int* flag) {
 
 namespace annc { int dot_interaction_error_flag(int* flag); }
 
+// Sets the device-side error word of the tensor-core kernels (what a CTA does when a bounded
+// wait runs out), so that the host-side reporting can be exercised without a kernel that
+// actually gives up.  annc_gemm_check and the custom calls report it; 0 clears it.
+extern "C" int annc_gemm_debug_set_error_word(int value) {
+  ANNC_CUDA(cudaMemcpyToSymbol(annc::gemm::g_gemm_error, &value, sizeof(int)));
+  return ANNC_OK;
+}
+
 extern "C" int annc_gemm_check(void* stream, int* timed_out) {
   if (!timed_out) return annc::fail(ANNC_ERR_INVALID_ARGUMENT, "null argument");
   ANNC_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));

@@ -67,7 +67,7 @@ struct Exchange {
   long long pos_n = 0;
   int epoch = 0;
   unsigned long long limit_ns = 2000000000ull;
-  int pool_blocks = 148 * 4;
+  int variant = 0;
   bool profiling = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   bool ev_valid = false;
@@ -85,31 +85,38 @@ static void exclusive_scan_inplace(int* data, long long n, int* tile_scratch, cu
   emb::scan_apply_kernel<<<(unsigned)tiles, emb::kScanThreads, 0, s>>>(data, n, tile_scratch, data);
 }
 
-template <int LANES, int VPL>
-static int pool_blocks_per_sm() {
-  int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pool_kernel<LANES, VPL>, 256, 0) != cudaSuccess || n < 1) n = 2;
-  return n;
-}
-
-template <int LANES, int VPL>
+template <int LANES, int VPL, int TILES, int INFLIGHT, int MINB>
 static void launch_pool(const Exchange& x, cudaStream_t s) {
   static int per_sm[kMaxDevices] = {0};
   const int slot = device_slot();
-  if (!per_sm[slot]) per_sm[slot] = pool_blocks_per_sm<LANES, VPL>();
+  if (!per_sm[slot]) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pool_kernel<LANES, VPL, TILES, INFLIGHT, MINB>, 256, 0) !=
+            cudaSuccess || n < 1)
+      n = 2;
+    per_sm[slot] = n;
+  }
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, slot);
-  pool_kernel<LANES, VPL><<<(unsigned)(sms * per_sm[slot]), 256, 0, s>>>(x.pool, x.err);
+  pool_kernel<LANES, VPL, TILES, INFLIGHT, MINB><<<(unsigned)(sms * per_sm[slot]), 256, 0, s>>>(x.pool, x.err);
 }
 
 static int run_pool(const Exchange& x, cudaStream_t s) {
   switch ((int)(x.dim / 4)) {
-    case 4: launch_pool<4, 1>(x, s); break;
-    case 8: launch_pool<8, 1>(x, s); break;
-    case 16: launch_pool<16, 1>(x, s); break;
-    case 32: launch_pool<32, 1>(x, s); break;
-    case 64: launch_pool<32, 2>(x, s); break;
-    case 128: launch_pool<32, 4>(x, s); break;
+    case 4: launch_pool<4, 1, 8, 4, 5>(x, s); break;
+    case 8: launch_pool<8, 1, 8, 4, 5>(x, s); break;
+    case 16:
+      switch (x.variant) {
+        case 1: launch_pool<16, 1, 16, 4, 5>(x, s); break;
+        case 2: launch_pool<16, 1, 32, 4, 5>(x, s); break;
+        case 3: launch_pool<16, 1, 8, 2, 6>(x, s); break;
+        case 4: launch_pool<16, 1, 4, 4, 5>(x, s); break;
+        default: launch_pool<16, 1, 8, 4, 5>(x, s); break;
+      }
+      break;
+    case 32: launch_pool<32, 1, 8, 4, 5>(x, s); break;
+    case 64: launch_pool<32, 2, 8, 4, 4>(x, s); break;
+    case 128: launch_pool<32, 4, 8, 2, 3>(x, s); break;
     default: return fail(ANNC_ERR_UNSUPPORTED, "row exchange: dim must be 16, 32, 64, 128, 256 or 512");
   }
   return ANNC_OK;
@@ -212,8 +219,9 @@ int annc_row_exchange_create(const annc_row_exchange_config* c, void* const* pee
   for (int t = 0; t < x->T && e == cudaSuccess; ++t) {
     const annc_row_shard_table& tb = x->tables[t];
     const bool bad = tb.rows < 1 || tb.rows >= (1LL << 31) || tb.local_rows < 0 || tb.hot_count < 0 ||
-                     tb.hot_count > tb.rows || (tb.hot_count > 0 && !tb.hot) ||
-                     (tb.local_rows > 0 && !tb.shard) || tb.local_rows + tb.hot_count >= (1LL << 31);
+                     tb.hot_count > tb.rows || (tb.local_rows + tb.hot_count > 0 && !tb.shard) ||
+                     tb.local_rows + tb.hot_count >= (1LL << 31) ||
+                     (reinterpret_cast<uintptr_t>(tb.shard) & 15) != 0;
     if (bad) {
       destroy(x);
       return fail(ANNC_ERR_INVALID_ARGUMENT, "row exchange: bad table description");
@@ -253,9 +261,14 @@ int annc_row_exchange_create(const annc_row_exchange_config* c, void* const* pee
   memset(&x->bar, 0, sizeof(x->bar));
   for (int t = 0; t < x->T; ++t) {
     x->pool.tab[t] = x->tables[t].shard;
-    x->pool.hot[t] = x->tables[t].hot;
-    x->pool.rows[t] = (int)x->tables[t].local_rows;
-    x->pool.hot_rows[t] = (int)x->tables[t].hot_count;
+    x->pool.rows[t] = (int)(x->tables[t].local_rows + x->tables[t].hot_count);
+  }
+  {  // key / batch by multiplication: exact for every key below 2^31
+    int lg = 0;
+    while ((1LL << lg) < x->batch) ++lg;
+    x->pool.batch_shift = 31 + lg;
+    x->pool.batch_magic = ((1ull << x->pool.batch_shift) + (unsigned long long)x->batch - 1) /
+                          (unsigned long long)x->batch;
   }
   for (int q = 0; q < x->world; ++q) {
     x->pool.list[q] = reinterpret_cast<const int2*>(x->peer[q] + x->lay.records);
@@ -283,6 +296,11 @@ int annc_row_exchange_destroy(annc_row_exchange* ex) {
 int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms) {
   ANNC_REQUIRE(ex && ms >= 1, ANNC_ERR_INVALID_ARGUMENT, "row exchange: bad timeout");
   reinterpret_cast<Exchange*>(ex)->limit_ns = (unsigned long long)ms * 1000000ull;
+  return ANNC_OK;
+}
+
+int annc_row_exchange_set_variant(annc_row_exchange* ex, int v) {
+  reinterpret_cast<Exchange*>(ex)->variant = v;
   return ANNC_OK;
 }
 

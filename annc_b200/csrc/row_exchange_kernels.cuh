@@ -262,35 +262,37 @@ __global__ void wait_kernel(BarrierParams b, int epoch, unsigned long long limit
 }
 
 // ---- pooling + exchange ----------------------------------------------------------------
-// Lookup-granular: a group of LANES lanes takes CHUNK = LANES consecutive records of one
-// source's list (one record per lane, one coalesced load) and owns the bags whose first record
-// lies in that chunk; it follows its last bag into the next chunks until the key changes.  Rows
-// are added in record order (= lookup order) into a zero accumulator, eight row loads in flight
-// per group, and each finished partial sum is stored at once into the receive slab of the rank
-// that owns the sample.  A chunk of 16 records keeps every lane busy whatever the bag lengths
-// (1.3 lookups per (bag, owner) pair at eight ranks).
+// Lookup-granular: a group of LANES lanes takes a chunk of TILES * LANES consecutive records
+// of one source's list (read tile by tile: one record per lane, one coalesced load) and owns
+// the bags whose first record lies in that chunk; it follows its last bag past the chunk until
+// the key changes.  Rows are added in record order (= lookup order) into a zero accumulator,
+// several row loads in flight per group, and each finished partial sum is stored at once into
+// the receive slab of the rank that owns the sample.  Work per group does not depend on the
+// bag lengths (1.3 lookups per (bag, owner) pair at eight ranks).
 struct PoolParams {
-  const float* tab[kMaxTables];   // this rank's shard of table t
-  const float* hot[kMaxTables];   // replicated hot rows of table t (local row >= rows[t])
-  int rows[kMaxTables];
-  int hot_rows[kMaxTables];
+  const float* tab[kMaxTables];   // table t on this rank: its shard's rows, then the hot rows
+  int rows[kMaxTables];           // rows held (shard + hot)
   const int2* list[kMaxWorld];    // source q's record buffer as seen from here
   float* out[kMaxWorld];          // this rank's slab in source q's receive buffer
   const int* meta;                // (first, count) per source, written by wait_kernel
+  unsigned long long batch_magic; // key / batch = (key * batch_magic) >> batch_shift for key < 2^31
   unsigned batch;
+  int batch_shift;
   int num_tables;
   int world;
   int rank;
   int rounds;                     // interleave factor of the sources
 };
 
-template <int LANES, int VPL>
-__global__ void __launch_bounds__(256)
+template <int LANES, int VPL, int TILES, int INFLIGHT_, int MINB>
+__global__ void __launch_bounds__(256, MINB)
 pool_kernel(PoolParams p, int* __restrict__ err) {
   constexpr int GROUPS_PER_WARP = 32 / LANES;
-  constexpr int CHUNK = LANES;
-  constexpr int INFLIGHT = LANES < 8 ? LANES : 8;
+  constexpr int CHUNK = LANES * TILES;  // records per group: TILES tiles of one record per lane
+  constexpr int INFLIGHT = LANES < INFLIGHT_ ? LANES : INFLIGHT_;
   constexpr int ROW4 = LANES * VPL;  // float4 per row
+  constexpr unsigned kLaneMask = LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u);
+  constexpr unsigned kNoSlot = 0xfffffffeu;  // a record without a valid key is added nowhere
   __shared__ int s_first[kMaxWorld], s_chunks[kMaxWorld], s_quota[kMaxWorld], s_qpre[kMaxWorld + 1];
   if (threadIdx.x == 0) {
     // sources in the order rank+1, rank+2, ..., rank: at any moment the ranks of a node store
@@ -309,25 +311,25 @@ pool_kernel(PoolParams p, int* __restrict__ err) {
     s_qpre[p.world] = pre;
   }
   __syncthreads();
-  const int per_round = s_qpre[p.world];
+  const unsigned per_round = (unsigned)s_qpre[p.world];
   if (per_round == 0) return;
   const int lane_in_warp = threadIdx.x & 31;
   const int lane = lane_in_warp % LANES;
   const int shift = (lane_in_warp / LANES) * LANES;
-  const unsigned gmask = (LANES == 32) ? 0xffffffffu : (((1u << LANES) - 1u) << shift);
-  const long long group = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GROUPS_PER_WARP +
-                          lane_in_warp / LANES;
-  const long long num_groups = (long long)gridDim.x * (blockDim.x >> 5) * GROUPS_PER_WARP;
-  const long long virtual_chunks = (long long)per_round * p.rounds;
+  const unsigned gmask = kLaneMask << shift;
+  const unsigned group = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GROUPS_PER_WARP +
+                         lane_in_warp / LANES;
+  const unsigned num_groups = gridDim.x * (blockDim.x >> 5) * GROUPS_PER_WARP;
+  const unsigned virtual_chunks = per_round * (unsigned)p.rounds;
   const unsigned T = (unsigned)p.num_tables;
 
-  for (long long vc = group; vc < virtual_chunks; vc += num_groups) {
-    const int round = (int)(vc / per_round);
-    const int rem = (int)(vc - (long long)round * per_round);
+  for (unsigned vc = group; vc < virtual_chunks; vc += num_groups) {
+    const unsigned round = vc / per_round;
+    const int rem = (int)(vc - round * per_round);
     int j = 0;
     while (rem >= s_qpre[j + 1]) ++j;
-    const int chunk = round * s_quota[j] + (rem - s_qpre[j]);
-    if (chunk >= s_chunks[j] || rem - s_qpre[j] >= s_quota[j]) continue;
+    const int chunk = (int)round * s_quota[j] + (rem - s_qpre[j]);
+    if (chunk >= s_chunks[j]) continue;
     const int q = (p.rank + 1 + j) % p.world;
     const int2* __restrict__ rec = p.list[q] + s_first[j];
     const int n = p.meta[2 * q + 1];
@@ -336,89 +338,91 @@ pool_kernel(PoolParams p, int* __restrict__ err) {
     float4 acc[VPL];
 #pragma unroll
     for (int v = 0; v < VPL; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-    unsigned cur = 0xffffffffu;  // output slot (in float4 rows) of the bag being summed
-    bool open = false;           // a bag of this group is being summed
-    int base = chunk * CHUNK;
-    bool first_tile = true;
-    while (base < n) {
-      // one record per lane; slot = where its bag's partial sum goes, tsel = table (+ hot flag)
+    unsigned cur = kNoSlot;              // output slot (float4 units) of the bag being summed
+    const float4* tbase = nullptr;       // table of the bag whose rows are being loaded
+    bool open = false;                   // a bag of this group is being summed
+    const int chunk_end = min(n, (chunk + 1) * CHUNK);
+    for (int base = chunk * CHUNK; base < n; base += LANES) {
+      // one record per lane: slot = where its bag's partial sum goes, tsel = its table,
+      // row = its row in that table (-1: not to be read)
       int2 r = make_int2(-1, -1);
       if (base + lane < n) r = __ldg(rec + base + lane);
       int prev_key = __shfl_up_sync(gmask, r.y, 1, LANES);
       if (lane == 0) prev_key = base > 0 ? __ldg(rec + base - 1).y : -2;
-      unsigned slot = 0xfffffffeu;  // a record without a valid key is added nowhere
+      unsigned slot = kNoSlot;
       int tsel = -1, row = -1;
       if (r.y >= 0) {
-        const unsigned t = (unsigned)r.y / p.batch;
+        const unsigned t = (unsigned)(((unsigned long long)(unsigned)r.y * p.batch_magic) >> p.batch_shift);
         const unsigned s = (unsigned)r.y - t * p.batch;
-        slot = (s * T + t) * (unsigned)ROW4;
         if (t < T) {
-          if (r.x >= 0 && r.x < p.rows[t]) {
-            tsel = (int)t;
-            row = r.x;
-          } else if (r.x >= p.rows[t] && r.x - p.rows[t] < p.hot_rows[t]) {
-            tsel = (int)t | 0x100;
-            row = r.x - p.rows[t];
-          } else {
-            atomicOr(err, kErrRow);
-          }
+          slot = (s * T + t) * (unsigned)ROW4;
+          tsel = (int)t;
+          if (r.x >= 0 && r.x < p.rows[t]) row = r.x;
+          else atomicOr(err, kErrRow);
         }
       }
       const bool starts = (base + lane < n) && (r.y != prev_key);
-      const unsigned smask = (__ballot_sync(gmask, starts) >> shift) & (LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u));
-      int from = 0, to = min(CHUNK, n - base);
-      if (first_tile) {
-        // bags that began in an earlier chunk belong to the group of that chunk
-        if (smask == 0) break;
+      const unsigned smask = (__ballot_sync(gmask, starts) >> shift) & kLaneMask;
+      const int tile_n = min(LANES, n - base);
+      int from = 0, to = tile_n;
+      const bool inside = base < chunk_end;
+      if (!open) {
+        // nothing of this group is open yet: its first bag starts at the first start inside
+        // the chunk; bags that began earlier belong to the group of that chunk
+        if (!inside) break;
+        if (smask == 0) continue;
         from = __ffs(smask) - 1;
-        first_tile = false;
-      } else {
-        // a following tile: only the rest of the bag that is still open
+      } else if (!inside) {
+        // past the chunk: only the rest of the bag that is still open
         if (smask != 0) to = __ffs(smask) - 1;
       }
+      // Bag boundaries inside the tile are the bits of smask, the same for every lane of the
+      // group: no per-record comparison.  A bag's table and slot are fetched once, at its start.
       for (int j0 = from; j0 < to; j0 += INFLIGHT) {
-        unsigned sl[INFLIGHT];
         float4 v[INFLIGHT][VPL];
         bool has[INFLIGHT];
 #pragma unroll
         for (int k = 0; k < INFLIGHT; ++k) {
-          const int src_lane = (j0 + k) % LANES;
-          sl[k] = __shfl_sync(gmask, slot, src_lane, LANES);
-          const int ts = __shfl_sync(gmask, tsel, src_lane, LANES);
-          const int rw = __shfl_sync(gmask, row, src_lane, LANES);
-          has[k] = (j0 + k < to) && ts >= 0;
-          if (j0 + k >= to) sl[k] = 0xffffffffu;
-          if (has[k]) {
-            const float* src = ((ts & 0x100) ? p.hot[ts & 0xff] : p.tab[ts]) + (long long)rw * (ROW4 * 4);
+          const int i = j0 + k;
+          has[k] = false;
+          if (i < to) {
+            if ((smask >> i) & 1u) {
+              const int ts = __shfl_sync(gmask, tsel, i, LANES);
+              tbase = ts >= 0 ? reinterpret_cast<const float4*>(p.tab[ts]) : nullptr;
+            }
+            const int rw = __shfl_sync(gmask, row, i, LANES);
+            has[k] = rw >= 0 && tbase != nullptr;
+            if (has[k]) {
+              const float4* src = tbase + (long long)rw * ROW4 + lane;
 #pragma unroll
-            for (int w = 0; w < VPL; ++w) v[k][w] = emb::ldg4(src + (w * LANES + lane) * 4);
+              for (int w = 0; w < VPL; ++w) v[k][w] = __ldg(src + w * LANES);
+            }
           }
         }
 #pragma unroll
         for (int k = 0; k < INFLIGHT; ++k) {
-          if (sl[k] == 0xffffffffu) continue;  // past the end of this tile's share
-          if (sl[k] != cur) {
-            if (open && cur < 0xfffffffeu) {
+          const int i = j0 + k;
+          if (i < to) {
+            if ((smask >> i) & 1u) {
+              if (open && cur != kNoSlot) {
 #pragma unroll
-              for (int w = 0; w < VPL; ++w) out[cur + w * LANES + lane] = acc[w];
+                for (int w = 0; w < VPL; ++w) out[cur + w * LANES + lane] = acc[w];
+              }
+#pragma unroll
+              for (int w = 0; w < VPL; ++w) acc[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+              cur = __shfl_sync(gmask, slot, i, LANES);
+              open = true;
             }
+            if (has[k]) {
 #pragma unroll
-            for (int w = 0; w < VPL; ++w) acc[w] = make_float4(0.f, 0.f, 0.f, 0.f);
-            cur = sl[k];
-            open = true;
-          }
-          if (has[k]) {
-#pragma unroll
-            for (int w = 0; w < VPL; ++w) emb::add4(acc[w], v[k][w]);
+              for (int w = 0; w < VPL; ++w) emb::add4(acc[w], v[k][w]);
+            }
           }
         }
       }
-      if (to < min(CHUNK, n - base)) break;  // the open bag ended inside this tile
-      base += CHUNK;
-      // the next tile is only needed while the last bag may continue
-      if (base >= n) break;
+      if (!inside && to < tile_n) break;  // the open bag ended past the chunk
     }
-    if (open && cur < 0xfffffffeu) {
+    if (open && cur != kNoSlot) {
 #pragma unroll
       for (int w = 0; w < VPL; ++w) out[cur + w * LANES + lane] = acc[w];
     }

@@ -19,10 +19,14 @@ void report(const char* who, int rc) {
   if (rc != ANNC_OK) fprintf(stderr, "[annc_b200] %s failed (%d): %s\n", who, rc, annc_last_error());
 }
 
+// Operand roles: in the dots the reference's matchers rewrite, rhs is the weight and the addend
+// is the broadcast bias; they are constants of the executable, so they are looked up as such
+// (reused even when only constants are cached).  A kn4-packed constant weight is re-laid once
+// into the form the TMA-fed route wants and that copy is kept with the weight's mirror: no
+// per-call workspace traffic.  Strided-batch operands are activations.
 int gemm_host(const char* who, float* out, const float* a, const float* b, const float* addend,
               int64_t batch, int64_t m, int64_t n, int64_t k, bool trA, bool trB, float alpha,
-              float beta, int act, int b_format) {
-  (void)who;
+              float beta, int act, int b_format, bool weights = true) {
   if (batch * m * n <= 0) return ANNC_OK;
   Call call;
   annc_gemm_desc d;
@@ -43,22 +47,34 @@ int gemm_host(const char* who, float* out, const float* a, const float* b, const
   d.stride_addend = m * n;
   d.alpha = alpha;
   d.beta = beta;
+  const size_t b_count = (size_t)(batch * k * n);
   d.a = call.in(a, (size_t)(batch * m * k));
-  d.b = call.in(b, (size_t)(batch * k * n));
-  d.addend = addend ? call.in(addend, (size_t)(batch * m * n)) : nullptr;
+  d.b = weights ? call.in_constant(b, b_count) : call.in(b, b_count);
+  if (addend) d.addend = weights ? call.in_constant(addend, (size_t)(batch * m * n)) : call.in(addend, (size_t)(batch * m * n));
   d.c = call.out(out, (size_t)(batch * m * n), beta != 0.0f);
   d.activation = act;
   d.b_format = b_format;
   d.math = ANNC_MATH_AUTO;
-  if (b_format == ANNC_B_KN4 && m >= 512 && (n & 3) == 0) {
-    // scratch from the call's arena: the packed weight is re-laid once per call (2 x 4kn
-    // bytes of traffic against 2mnk flops) and the GEMM then runs on the TMA-fed route
-    d.workspace_bytes = (size_t)k * (size_t)n * sizeof(float);
-    d.workspace = call.scratch(d.workspace_bytes);
-  }
   if (call.status() != ANNC_OK) return call.status();
+  if (b_format == ANNC_B_KN4 && (n & 3) == 0 && batch == 1) {
+    const size_t ws_bytes = (size_t)k * (size_t)n * sizeof(float);
+    bool fresh = false;
+    void* ws = call.derived(b, b_count * sizeof(float), /*tag: re-laid kn4*/ 1, ws_bytes, &fresh);
+    annc_gemm_desc plain;
+    const int form = ws ? gemm::relaid_desc(d, ws, ws_bytes, &plain) : 0;
+    if (form) {
+      if (fresh) gemm::relay_kn4(d.b, static_cast<float*>(ws), k, n, form, call.stream());
+      d = plain;
+    }
+  }
   ANNC_TRY(annc_gemm_run(&d, call.stream()));
-  return call.finish();
+  ANNC_TRY(call.finish());
+  if (call.synced()) {  // a tensor-core CTA that gave up on a bounded wait left invalid output
+    int flag = 0;
+    if (gemm::read_error_flag(&flag) == ANNC_OK && flag)
+      return fail(ANNC_ERR_TIMEOUT, "%s: a tensor-core GEMM wait ran out; the output is not valid", who);
+  }
+  return ANNC_OK;
 }
 
 // Reads `count` leading s64 entries of a shape-info operand
@@ -103,7 +119,7 @@ void __batch_matmul(void* out, const void** in) {
   if (rc == ANNC_OK)
     rc = gemm_host("__batch_matmul", (float*)out, (const float*)in[0], (const float*)in[1],
                    nullptr, sa[0], sa[1], sb[2], sa[2], false, false, 1.0f, 0.0f, ANNC_ACT_NONE,
-                   ANNC_B_PLAIN);
+                   ANNC_B_PLAIN, /*weights=*/false);
   report("__batch_matmul", rc);
 }
 

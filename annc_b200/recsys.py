@@ -38,15 +38,28 @@ class RecsysPipeline:
         T, R, D, B = model.tables, model.rows, model.dim, model.batch
         self.T, self.D, self.batch = T, D, B
         s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
         if shard == "row":
             self.local_rows = len(range(rank, R, world))
-            # one allocation for all local shards: [T, local_rows, D]
-            self.table_mem = torch.empty((T, max(self.local_rows, 1), D), dtype=torch.float32, device=device)
+            # Replicated hot rows (generated from the same hash) sit behind each shard's rows.
+            hot_lists = [model.bags[t].popular_rows(hot_rows, R) if hot_rows > 0 else np.zeros(0, np.int64)
+                         for t in range(T)]
+            hmax = max(int(h.shape[0]) for h in hot_lists)
+            # one allocation for all local shards: [T, local_rows + hot rows, D]
+            self.table_mem = torch.empty((T, max(self.local_rows + hmax, 1), D), dtype=torch.float32, device=device)
+            self._hot = []
             for t in range(T):
                 check(lib.annc_synth_fill_rows_dev(C.c_void_p(self.table_mem[t].data_ptr()),
                                                    C.c_int64(self.local_rows), C.c_int64(D),
                                                    C.c_uint64(model.seed), C.c_int64(t), C.c_int64(rank),
                                                    C.c_int64(world), s))
+                h = int(hot_lists[t].shape[0])
+                hr = up(hot_lists[t]) if h else None
+                if h:
+                    check(lib.annc_synth_fill_row_list_dev(
+                        C.c_void_p(self.table_mem[t][self.local_rows:].data_ptr()), C.c_void_p(hr.data_ptr()),
+                        C.c_int64(h), C.c_int64(D), C.c_uint64(model.seed), C.c_int64(t), s))
+                self._hot.append((h, hr if 0 < h < R else None))
         else:
             self.owned = [int(t) for t in np.array_split(np.arange(T), world)[rank]]
             self.local_rows = R
@@ -55,7 +68,6 @@ class RecsysPipeline:
                 check(lib.annc_synth_fill_rows_dev(C.c_void_p(self.table_mem[j].data_ptr()), C.c_int64(R),
                                                    C.c_int64(D), C.c_uint64(model.seed), C.c_int64(t),
                                                    C.c_int64(0), C.c_int64(1), s))
-        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
         nnz = [int(b.raw_ids.shape[0]) for b in model.bags]
         self.nnz, self.nnz_total = nnz, int(sum(nnz))
         ids_host = np.concatenate([b.raw_ids for b in model.bags])
@@ -79,16 +91,7 @@ class RecsysPipeline:
         nnz_all = [None] * world
         dist.all_gather_object(nnz_all, nnz)
         if shard == "row":
-            hot = None
-            if hot_rows > 0:
-                hot = []
-                for t in range(T):
-                    hr = up(model.bags[t].popular_rows(hot_rows, R))
-                    tab = torch.empty((hr.shape[0], D), dtype=torch.float32, device=device)
-                    check(lib.annc_synth_fill_row_list_dev(C.c_void_p(tab.data_ptr()), C.c_void_p(hr.data_ptr()),
-                                                           C.c_int64(hr.shape[0]), C.c_int64(D),
-                                                           C.c_uint64(model.seed), C.c_int64(t), s))
-                    hot.append((tab, hr if hr.shape[0] < R else None))
+            hot = self._hot
             self.bags = RowShardedBags(world, rank, device, [self.table_mem[t] for t in range(T)],
                                        [self.local_rows] * T, [R] * T, B, D, np.array(nnz_all),
                                        [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=1,

@@ -18,7 +18,7 @@ PHASES = ("split", "barrier1", "pool_exchange", "barrier2", "sum")
 
 class ShardTable(C.Structure):
     _fields_ = [("shard", C.c_void_p), ("local_rows", C.c_int64), ("rows", C.c_int64),
-                ("hot", C.c_void_p), ("hot_rows", C.c_void_p), ("hot_count", C.c_int64)]
+                ("hot_rows", C.c_void_p), ("hot_count", C.c_int64)]
 
 
 class Config(C.Structure):
@@ -53,14 +53,13 @@ def _stream() -> C.c_void_p:
 def make_config(world: int, rank: int, tables: Sequence[dict], dim: int, batch: int,
                 max_lookups: int, max_lookups_per_table: int, combiner: int = 0,
                 id_kind: int = 2):
-    """tables: per table a dict(shard=ptr, local_rows=, rows=, hot=ptr|0, hot_rows=ptr|0,
-    hot_count=).  Returns (Config, keep-alive array)."""
+    """tables: per table a dict(shard=ptr of f32[local_rows + hot_count, D], local_rows=, rows=,
+    hot_rows=ptr|0, hot_count=).  Returns (Config, keep-alive array)."""
     arr = (ShardTable * len(tables))()
     for i, t in enumerate(tables):
         arr[i].shard = t["shard"] or None
         arr[i].local_rows = int(t["local_rows"])
         arr[i].rows = int(t["rows"])
-        arr[i].hot = t.get("hot") or None
         arr[i].hot_rows = t.get("hot_rows") or None
         arr[i].hot_count = int(t.get("hot_count", 0))
     cfg = Config(world, rank, len(tables), id_kind, combiner, 0, dim, batch, int(max_lookups),
@@ -121,6 +120,9 @@ class RowExchange:
 
     def set_timeout_ms(self, ms: int) -> None:
         check(lib.annc_row_exchange_set_timeout_ms(self.h, C.c_int64(ms)))
+
+    def set_variant(self, v: int) -> None:
+        lib.annc_row_exchange_set_variant(self.h, C.c_int(v))
 
     def set_profiling(self, on: bool) -> None:
         check(lib.annc_row_exchange_set_profiling(self.h, C.c_int(int(on))))

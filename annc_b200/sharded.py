@@ -110,8 +110,9 @@ class RowShardedBags:
     adds the parts of this rank's batch into `out` (f32, or bf16 with out_bf16) as
     [batch, tables, dim] rows of `out_stride` elements.
 
-    hot: optional per-table (hot_table f32[h, dim] tensor, hot_rows i64[h] tensor or None for
-    "all rows") of replicated rows; None or (None, None) = none."""
+    local_tables[t]: f32[local_rows[t] + h, dim], the shard's rows followed by the h replicated
+    hot rows; hot: optional per-table (h, hot_rows i64[h] tensor or None for "all rows");
+    None = no hot rows."""
 
     def __init__(self, world: int, rank: int, device, local_tables, local_rows, table_rows, batch: int,
                  dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2, hot=None):
@@ -128,12 +129,11 @@ class RowShardedBags:
         tabs = []
         self.hot_bytes = 0
         for t in range(T):
-            h_tab, h_rows = (hot[t] if hot is not None and hot[t] is not None else (None, None))
-            h_count = int(h_tab.shape[0]) if h_tab is not None else 0
+            h_count, h_rows = (hot[t] if hot is not None and hot[t] is not None else (0, None))
             self.hot_bytes += h_count * dim * 4
-            tabs.append(dict(shard=local_tables[t].data_ptr() if int(local_rows[t]) > 0 else 0,
+            assert int(local_tables[t].shape[0]) >= int(local_rows[t]) + h_count
+            tabs.append(dict(shard=local_tables[t].data_ptr() if int(local_rows[t]) + h_count > 0 else 0,
                              local_rows=int(local_rows[t]), rows=int(table_rows[t]),
-                             hot=h_tab.data_ptr() if h_count else 0,
                              hot_rows=h_rows.data_ptr() if (h_count and h_rows is not None) else 0,
                              hot_count=h_count))
         self._keep = (list(local_tables), hot)
@@ -397,21 +397,14 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
 
         def _setup_row_partitioned(self, m, plan) -> None:
             emb = m.emb
-            self.tables = [self._up(plan.local_shard(t)) for t in emb.tables]
-            hot = None
-            if hot_rows > 0:
-                # the replicated hot set: the rows of each table's most popular ids (the
-                # table's own popularity map, identical on every rank)
-                hot = []
-                for t, (tab, bag) in enumerate(zip(emb.tables, emb.bags)):
-                    rows_t = tab.shape[0]
-                    hr = bag.popular_rows(hot_rows, rows_t)
-                    if hr.shape[0] == 0:
-                        hot.append(None)
-                    elif hr.shape[0] == rows_t:
-                        hot.append((self._up(tab), None))
-                    else:
-                        hot.append((self._up(tab[hr]), self._up(hr)))
+            # Per table: this rank's shard, then the replicated hot set behind it: the rows of
+            # the table's most popular ids (its own popularity map, identical on every rank).
+            self.tables, hot = [], []
+            for t, (tab, bag) in enumerate(zip(emb.tables, emb.bags)):
+                rows_t = tab.shape[0]
+                hr = bag.popular_rows(hot_rows, rows_t) if hot_rows > 0 else np.zeros(0, np.int64)
+                self.tables.append(self._up(np.concatenate([plan.local_shard(tab), tab[hr]])))
+                hot.append((int(hr.shape[0]), self._up(hr) if 0 < hr.shape[0] < rows_t else None))
             self.rowbags = RowShardedBags(
                 world, rank, self.device, self.tables, [plan.local_rows(t) for t in range(self.T)],
                 plan.table_rows, self.batch, self.dim, plan.nnz,

@@ -71,6 +71,7 @@ def parse_args():
                          "labelled sub-records (comma list of row_k0, row_nccl, table, table_nccl, replica; "
                          "empty = none)")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operator record at N=1")
+    ap.add_argument("--no-abi", action="store_true", help="skip the host-buffer ABI leg at N=1")
     args = ap.parse_args()
     if args.batch is None:
         args.batch = 65536 if args.workload == "dlrm" else 16384
@@ -293,6 +294,44 @@ def cpu_baselines(args, model, pipe_out):
            "sample": "2 passes over the first %d samples of the batch, one thread (OMP_NUM_THREADS=1 is the "
                      "reference's deployment setting)" % n1}
     return base, one, parity
+
+
+def abi_leg(args, model, pipe_out):
+    """The same step through the reference-named entry points with HOST buffers (the drop-in
+    path itself): Σ of the time inside the library's calls per step.  Every step gets a new
+    batch in the same input buffers; weights, tables and broadcast biases upload once, and an
+    operand the host did not touch since the library wrote it is not uploaded again."""
+    import numpy as np
+    from annc_b200._lib import lib
+    from annc_b200.abi_step import AbiDlrmStep
+    import ctypes as C
+    step = AbiDlrmStep(model)
+    step.load_batch(1)
+    step.forward()
+    step.load_batch(0)
+    got = step.forward()
+    err = float(np.abs(got - pipe_out).max()) if pipe_out is not None else None
+    cnt = [C.c_uint64(0) for _ in range(3)]
+    lib.annc_staging_counters(*[C.byref(c) for c in cnt])
+    h0, d0 = cnt[0].value, cnt[1].value
+    step.call_seconds, step.calls = 0.0, 0
+    n = 3
+    for i in range(n):
+        step.load_batch(2 + i)
+        step.forward()
+    lib.annc_staging_counters(*[C.byref(c) for c in cnt])
+    ms = 1e3 * step.call_seconds / n
+    h2d, d2h = (cnt[0].value - h0) // n, (cnt[1].value - d0) // n
+    lib.annc_release_device_memory()
+    return {"value": args.batch / (ms / 1e3), "unit": UNIT, "ms_per_step": ms, "calls_per_step": step.calls // n,
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "pcie_floor_ms_at_55GBs": (h2d + d2h) / 55e9 * 1e3,
+            "max_abs_diff_vs_device_pipeline": err,
+            "what": "sum of the time inside the %d reference-named calls of one step "
+                    "(__matmul_add_relu / __matmul_add per MLP layer, KPFusedSparseSegmentReduce per "
+                    "table, __batch_matmul for the interaction) with pageable host buffers in and out; "
+                    "every intermediate returns to the host as the reference's ABI requires; the "
+                    "graph's own glue between calls is not timed" % (step.calls // n)}
 
 
 def run_gpu(args):
@@ -567,6 +606,8 @@ def run_gpu(args):
         if world == 1 and not recsys and not args.no_ops:
             from annc_b200 import opbench
             line["ops"] = opbench.ops_record()
+        if world == 1 and not recsys and not args.no_abi:
+            line["e2e_abi"] = abi_leg(args, model, pipe_out)
         print(json.dumps(line), flush=True)
     if recsys or world > 1:
         dist.destroy_process_group()

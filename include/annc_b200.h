@@ -18,12 +18,20 @@
  *      allocation, explicit stream.  The roofline figures are measured on these.
  *
  * Pointer rule for groups (1) and (2): every data pointer may be host memory or
- * device memory.  Host buffers are staged through a per-thread device arena and
- * results are copied back before the call returns; device buffers are used in
- * place on the calling thread's stream (annc_set_stream).  Constant operands
- * (weights, tables) can be registered once with annc_register_constant so that
- * they are uploaded a single time.  There is no CPU fallback anywhere: without a
- * CUDA device every compute entry point fails with ANNC_ERR_CUDA.
+ * device memory.  Device buffers are used in place on the calling thread's stream
+ * (annc_set_stream).  A host operand gets a device mirror keyed by (pointer, bytes, device)
+ * that persists between calls (the reference's callers keep their buffers: XLA buffer
+ * assignment, TF variables), results are copied back before the call returns.  An upload is
+ * skipped when a sampled fingerprint of the host contents (one 8-byte word per 4 KiB page, at
+ * most 16384 pages, plus the first and last 64 bytes) equals the one taken when the mirror was
+ * last filled: weights and tables upload once, and an output that comes back unchanged as an
+ * input of the next call is not uploaded at all.  The fingerprint is a sample, not a proof: a
+ * caller that rewrites part of a buffer in place between two calls, leaving every sampled word
+ * as it was, must select mode 0 or 1 with annc_set_operand_cache.  One thread keeps one stream,
+ * or synchronises before changing it (calls made with device pointers only do not wait for
+ * the stream; a later call on another stream is ordered after them by an event).  There is no
+ * CPU fallback anywhere: without a CUDA device every compute entry point fails with
+ * ANNC_ERR_CUDA.
  *
  * Reference citations are paths inside the ANNC project.
  */
@@ -60,13 +68,23 @@ const char* annc_version(void);
 void annc_set_stream(void* cuda_stream);
 void* annc_get_stream(void);
 
-/* Uploads `bytes` at host pointer `ptr` once; later calls that receive `ptr` use
- * the device copy (XLA constants / parameters and TF variables keep their address
- * for the lifetime of the executable).  annc_unregister_constant drops it. */
+/* Uploads `bytes` at host pointer `ptr` now and pins the mirror: later calls that receive
+ * (`ptr`, `bytes`) use the device copy without looking at the host contents again, and the
+ * mirror is never evicted (XLA constants / parameters and TF variables keep their address for
+ * the lifetime of the executable).  annc_unregister_constant drops it. */
 int annc_register_constant(const void* ptr, size_t bytes);
 int annc_unregister_constant(const void* ptr);
 
-/* Frees the calling thread's staging arena and every registered constant. */
+/* Which host operands may reuse their mirror's contents: 0 = none (every call uploads),
+ * 1 = operands in weight / table positions only (rhs and addend of the dots, embedding tables),
+ * 2 = every operand (default).  max_bytes (0 = keep) caps the device memory the mirrors may
+ * take (24 GiB by default); the least recently used ones are freed beyond it. */
+int annc_set_operand_cache(int mode, size_t max_bytes);
+/* Bytes copied host-to-device and device-to-host by the calls of this process so far, and
+ * host-to-device bytes that were not copied because the mirror already held them. */
+void annc_staging_counters(uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint64_t* h2d_skipped_bytes);
+
+/* Frees the calling thread's scratch arena and every mirror (synchronises the device). */
 void annc_release_device_memory(void);
 
 /* ---------------------------------------------------------------- gating
@@ -348,8 +366,9 @@ int annc_peer_buffer_destroy(void* dev_ptr);
  *
  * Hot rows: a table may come with a replicated set of rows (every rank holds a copy).  A lookup
  * of such a row is pooled by the rank that owns the sample and sends nothing; with skewed ids
- * this removes most (bag, owner) pairs from the exchange.  hot_count == rows with hot_rows NULL
- * replicates the whole table (`hot` is then the whole table).
+ * this removes most (bag, owner) pairs from the exchange.  The hot rows are stored behind the
+ * shard's own rows in the same allocation.  hot_count == rows with hot_rows NULL replicates the
+ * whole table.
  *
  * Set-up: every rank allocates annc_row_exchange_peer_bytes() with annc_peer_buffer_create,
  * exchanges the handles over any host channel, maps the peers' buffers (annc_peer_buffer_open)
@@ -358,11 +377,13 @@ int annc_peer_buffer_destroy(void* dev_ptr);
  * or with other work of the same stream between them.  Sorted segment ids are required
  * (ANNC_ROWX_ERR_UNSORTED otherwise). */
 typedef struct annc_row_shard_table {
-  const float* shard;       /* f32[local_rows, D]: rows r with r % world == rank, at r / world */
+  const float* shard;       /* f32[local_rows + hot_count, D], 16-byte aligned: first the rows r
+                               with r % world == rank, at r / world; then the replicated hot rows
+                               in ascending row order                                           */
   int64_t local_rows;
-  int64_t rows;             /* rows of the whole table (the modulus for id_kind 2)            */
-  const float* hot;         /* f32[hot_count, D] replicated rows in ascending row order, or NULL */
-  const int64_t* hot_rows;  /* device i64[hot_count], strictly ascending rows of the table      */
+  int64_t rows;             /* rows of the whole table (the modulus for id_kind 2)              */
+  const int64_t* hot_rows;  /* device i64[hot_count], strictly ascending rows of the table; NULL
+                               when hot_count is 0 or equals rows (the whole table replicated)   */
   int64_t hot_count;
 } annc_row_shard_table;
 
@@ -490,6 +511,10 @@ int annc_gemm_run(const annc_gemm_desc* desc, void* stream);
 /* Synchronises `stream` and reports whether a tensor-core GEMM CTA has given up on one of
  * its bounded mbarrier waits since the library was loaded (its output is then invalid). */
 int annc_gemm_check(void* stream, int* timed_out);
+/* Test aid: sets (non-zero) or clears (0) that device-side word by hand, the way a CTA whose
+ * wait ran out does, so that the reporting path can be exercised without a kernel giving up.
+ * While it is set the tensor-core GEMM kernels return at once. */
+int annc_gemm_debug_set_error_word(int value);
 /* Name of the kernel family annc_gemm_run would pick: "tcgen05_pair_tf32" / "tcgen05_pair_bf16"
  * (persistent CTA-pair kernel), "tcgen05_tf32" (single-CTA tiles, also the kn4 loader),
  * "simt_fp32" (CUDA cores). */

@@ -43,14 +43,13 @@ class Emulated:
         for r in range(world):
             tabs = []
             for t in range(self.T):
-                shard = _dev(tables_np[t][r::world]) if tables_np[t][r::world].shape[0] else None
+                held = np.concatenate([tables_np[t][r::world], tables_np[t][hot_rows[t]]])  # shard, then hot rows
+                shard = _dev(held) if held.shape[0] else None
                 full = hot_rows[t].shape[0] == rows[t]
-                hot = _dev(tables_np[t][hot_rows[t]]) if hot_rows[t].shape[0] else None
                 hr = _dev(hot_rows[t]) if (hot_rows[t].shape[0] and not full) else None
-                self.keep += [shard, hot, hr]
+                self.keep += [shard, hr]
                 tabs.append(dict(shard=shard.data_ptr() if shard is not None else 0,
                                  local_rows=len(range(r, rows[t], world)), rows=rows[t],
-                                 hot=hot.data_ptr() if hot is not None else 0,
                                  hot_rows=hr.data_ptr() if hr is not None else 0,
                                  hot_count=int(hot_rows[t].shape[0])))
             cfgs.append(rx.make_config(world, r, tabs, dim, batch, nnz_max, per_table, combiner=combiner))
