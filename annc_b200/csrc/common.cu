@@ -127,7 +127,11 @@ unsigned long long fingerprint(const void* p, size_t bytes, size_t max_samples =
   // the sampled word moves inside its page with the page number, so that a regular pattern
   // (one changed column of a matrix) does not hide between the samples
   size_t k = 0;
-  for (size_t o = 0; o + 8 <= bytes; o += step, ++k) mix(word(o + ((k * 520) & 4088 & (step - 8))));
+  for (size_t o = 0; o + 8 <= bytes; o += step, ++k) {
+    size_t at = o + ((k * 520) & 4088 & (step - 8));
+    if (at + 8 > bytes) at = bytes - 8;
+    mix(word(at));
+  }
   return h;
 }
 

@@ -33,7 +33,11 @@ static bool use_pair(const annc_gemm_desc& d, int math) {
   if (!pair_supported(d, math)) return false;
   if (math == ANNC_MATH_BF16 || (d.io_flags & (ANNC_IO_SOFTMAX | ANNC_IO_PAIR))) return true;
   if (!tc_supported(d, math)) return true;
-  return d.m >= 256 && d.n >= 192 && d.k >= 1024;
+  // 256 x 256 pair tiles pay off when there are enough of them to occupy the SM pairs; a
+  // smaller product runs on the single-CTA kernel (128 x 128 tiles, split K inside a cluster
+  // when even those are few).
+  const long long pair_tiles = ((d.m + 255) / 256) * ((d.n + 255) / 256) * d.batch;
+  return d.m >= 256 && d.n >= 192 && d.k >= 1024 && pair_tiles >= 74;
 }
 
 // AUTO: tensor cores (TF32) when the shape fits a tcgen05 kernel, else CUDA cores.

@@ -70,6 +70,7 @@ struct TcParams {
   int batched;    // A (and B when b_batched) are rank-3 tensor maps, batch = blockIdx.z
   int b_batched;
   long long stride_c, stride_addend;
+  int split;      // > 1: the CTAs of a cluster (1, 1, split) share one tile and split its K range
 };
 
 __device__ int g_gemm_error = 0;  // 1: an mbarrier wait ran out
@@ -97,12 +98,21 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + 16 * STAGES + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  // A CTA of an earlier wave (or launch) gave up on a wait: do not start, fail fast.
-  if (*reinterpret_cast<volatile int*>(&g_gemm_error) != 0) return;
+  // A CTA of an earlier wave (or launch) gave up on a wait: do not start, fail fast.  (The
+  // CTAs of a split-K cluster always run to their cluster barriers.)
+  if (p.split <= 1 && *reinterpret_cast<volatile int*>(&g_gemm_error) != 0) return;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int KT = (p.K + BK - 1) / BK;
+  // Split K: cluster rank c of `split` takes the k-steps [it0, it0 + KT); every CTA keeps its
+  // partial tile in shared memory and the ranks add them, each for its share of the rows, in
+  // rank order (deterministic) through distributed shared memory before the epilogue.
+  const int KT_all = (p.K + BK - 1) / BK;
+  const int crank = p.split > 1 ? (int)cluster_ctarank() : 0;
+  const int per = (KT_all + p.split - 1) / (p.split > 1 ? p.split : 1);
+  const int it0 = p.split > 1 ? min(KT_all, crank * per) : 0;
+  const int KT = p.split > 1 ? min(KT_all, it0 + per) - it0 : KT_all;
+  const int zb = p.split > 1 ? 0 : (int)blockIdx.z;  // batch index (no batches under split K)
   const bool b_by_loader = p.b_mode == B_KN4;
   const bool b_n_major = p.b_mode != B_TMA_NK;
 
@@ -127,16 +137,19 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  bool done = false;  // warps 2..5: the accumulator is complete and sits in shared memory
+  constexpr int LD = BN + 4;
   if (warp == 0) {
     // ---------------- TMA producer
     if (lane == 0) {
-      for (int it = 0; it < KT; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+      for (int li = 0; li < KT; ++li) {
+        const int it = it0 + li;
+        const int s = li % STAGES;
+        const uint32_t ph = (uint32_t)(li / STAGES) & 1u;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, &g_gemm_error)) break;
         const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
         mbar_expect_tx(bar_full + 8 * s, b_by_loader ? A_BYTES : STAGE_BYTES);
-        const int bz = blockIdx.z;
+        const int bz = zb;
         if (p.batched) tma_load_3d(sa, &tmap_a, it * BK, m0, bz, bar_full + 8 * s);
         else tma_load_2d(sa, &tmap_a, it * BK, m0, bar_full + 8 * s);
         if (p.b_mode == B_TMA_NK) {
@@ -160,7 +173,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((b_n_major ? 1u : 0u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       bool ok = true;
-      for (int it = 0; it < KT && ok; ++it) {
+      for (int it = 0; it < KT && ok; ++it) {  // local k-step
         const int s = it % STAGES;
         const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
         ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, &g_gemm_error);
@@ -247,9 +260,10 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (res - first > first + 1) first += 12;
         k_split = k_uniform + first;
       }
-      for (int it = 0; it < KT; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+      for (int li = 0; li < KT; ++li) {
+        const int it = it0 + li;
+        const int s = li % STAGES;
+        const uint32_t ph = (uint32_t)(li / STAGES) & 1u;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, &g_gemm_error)) break;
         const uint32_t sb = base + s * STAGE_BYTES + A_BYTES;
 #pragma unroll
@@ -280,19 +294,22 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     // epilogue: warp w may touch TMEM lanes 32 (w % 4) .. 32 (w % 4) + 31
     const int q = warp & 3;
-    const int row = m0 + q * 32 + lane;
-    const bool done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag, &g_gemm_error)) != 0;
+    done = __all_sync(0xffffffffu, mbar_wait(bar_done, 0, abort_flag, &g_gemm_error)) != 0;
     tc_fence_after();
     if (done) {
       // Phase 1: this warp's 32 x 128 accumulator slab, scaled by alpha, goes to shared
       // memory (the stage ring is idle once `done` has fired), rows padded to 132 floats.
-      constexpr int LD = BN + 4;
       float* slab = reinterpret_cast<float*>(gen_base) + (size_t)q * 32 * LD;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-        tmem_ld_wait();
+        if (KT > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+          tmem_ld_wait();
+        } else {  // a split-K rank without k-steps contributes zeros
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           float4 v;
@@ -304,8 +321,23 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       __syncwarp();
+    }
+    tc_fence_before();
+  }
+  // Split K: every rank's partial tile is in its shared memory now.
+  if (p.split > 1) {
+    __syncwarp();
+    cluster_sync_all();
+  }
+  if (warp >= 2) {
+    const int q = warp & 3;
+    if (done) {
+      const float* slab = reinterpret_cast<const float*>(gen_base) + (size_t)q * 32 * LD;
+      const uint32_t slab_s = base + (uint32_t)((size_t)q * 32 * LD * sizeof(float));
       // Phase 2: one output row per step, the 32 lanes cover its 128 columns with
       // 16-byte accesses, so C, the addend and the bias are read and written coalesced.
+      // Under split K rank c takes the rows rr with rr % split == c and adds the ranks'
+      // partial rows in rank order.
       const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
       const bool add_vec = p.addend && ((p.ld_addend & 3) == 0) &&
                            ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
@@ -317,14 +349,30 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (col + e < p.N) bias4[e] = __ldg(p.bias + col + e);
       }
       const int rows_here = min(32, p.M - (m0 + q * 32));
-      for (int rr = 0; rr < rows_here; ++rr) {
+      const int rstep = p.split > 1 ? p.split : 1;
+      for (int rr = crank; rr < rows_here; rr += rstep) {
         if (col >= p.N) break;
         const long long grow = (long long)(m0 + q * 32 + rr);
-        const float4 a4 = *reinterpret_cast<const float4*>(slab + rr * LD + lane * 4);
-        float v[4] = {a4.x, a4.y, a4.z, a4.w};
-        float* crow = p.C + blockIdx.z * p.stride_c + grow * p.ldc + col;
+        float v[4];
+        if (p.split > 1) {
+          v[0] = v[1] = v[2] = v[3] = 0.f;
+          const uint32_t off = slab_s + (uint32_t)((rr * LD + lane * 4) * sizeof(float));
+          for (int r = 0; r < p.split; ++r) {
+            float4 a4;
+            const uint32_t ra = mapa_u32(off, (uint32_t)r);
+            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(a4.x), "=f"(a4.y), "=f"(a4.z), "=f"(a4.w)
+                         : "r"(ra)
+                         : "memory");
+            v[0] += a4.x; v[1] += a4.y; v[2] += a4.z; v[3] += a4.w;
+          }
+        } else {
+          const float4 a4 = *reinterpret_cast<const float4*>(slab + rr * LD + lane * 4);
+          v[0] = a4.x; v[1] = a4.y; v[2] = a4.z; v[3] = a4.w;
+        }
+        float* crow = p.C + zb * p.stride_c + grow * p.ldc + col;
         const float* arow =
-            p.addend ? p.addend + blockIdx.z * p.stride_addend + grow * p.ld_addend + col : nullptr;
+            p.addend ? p.addend + zb * p.stride_addend + grow * p.ld_addend + col : nullptr;
         if (vec && col + 3 < p.N) {
           if (p.beta != 0.f) {
             const float4 o = *reinterpret_cast<const float4*>(crow);
@@ -358,7 +406,11 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    tc_fence_before();
+  }
+  // Nobody leaves while a peer may still read its partial tile.
+  if (p.split > 1) {
+    __syncwarp();
+    cluster_sync_all();
   }
   __syncthreads();
   if (warp == 1) {
@@ -438,7 +490,31 @@ int run_tc(const annc_gemm_desc& d, int math, cudaStream_t s) {
   p.act = d.activation;
   dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM), (unsigned)d.batch);
   const long long ctas = (long long)grid.x * grid.y * grid.z;
-  if (ctas <= 148 * 3 / 2) {
+  // Few tiles and a long K: a cluster of 2, 4 or 8 CTAs shares each tile and splits its K range,
+  // so that a 512 x 1024 x 1024 product occupies 128 SMs instead of 32.
+  const int kt_all = (int)((d.k + BK - 1) / BK);
+  int split = 1;
+  if (d.batch == 1 && ctas * 2 <= 148 && kt_all >= 8) {
+    while (split < 8 && ctas * split * 2 <= 148 && kt_all / (split * 2) >= 2) split *= 2;
+  }
+  p.split = split;
+  if (split > 1) {
+    grid.z = (unsigned)split;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes(6);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)split;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ANNC_CUDA(cudaLaunchKernelEx(&cfg, gemm_tf32_tcgen05_kernel<6>, ta, tb, p));
+  } else if (ctas <= 148 * 3 / 2) {
     gemm_tf32_tcgen05_kernel<6><<<grid, NUM_THREADS, smem_bytes(6), s>>>(ta, tb, p);
   } else {
     gemm_tf32_tcgen05_kernel<3><<<grid, NUM_THREADS, smem_bytes(3), s>>>(ta, tb, p);

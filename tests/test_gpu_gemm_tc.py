@@ -143,9 +143,10 @@ def test_kn4_with_workspace_matches_direct_route():
 
 
 def test_kn4_with_workspace_takes_the_k_major_route_for_long_k():
-    """K >= 1024 and K % 4 == 0: the packed weight is re-laid as [N,K] and the CTA-pair kernel
-    runs its K-major TMA route; the workspace then holds the transposed weight."""
-    m, n, k = 1024, 520, 1032
+    """K >= 1024, K % 4 == 0 and enough 256 x 256 tiles to occupy the SM pairs: the packed weight
+    is re-laid as [N,K] and the CTA-pair kernel runs its K-major TMA route; the workspace then
+    holds the transposed weight."""
+    m, n, k = 4096, 1300, 1032
     rng = np.random.default_rng(4)
     a = rng.standard_normal((m, k)).astype(np.float32)
     w = rng.standard_normal((k, n)).astype(np.float32)
@@ -156,3 +157,33 @@ def test_kn4_with_workspace_takes_the_k_major_route_for_long_k():
     assert not device.gemm_timed_out()
     assert torch.equal(ws, _dev(w).t().contiguous())
     assert nerr(c, a @ w) <= TF32_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 1024), (128, 256, 1000), (100, 132, 2052), (192, 384, 4100),
+                                   (128, 4096, 2048), (256, 512, 288), (64, 128, 8192)])
+@pytest.mark.parametrize("bsrc", ["nk_tma", "kn", "kn4"])
+def test_split_k_cluster_route(m, n, k, bsrc):
+    """Few output tiles and a long K: the CTAs of a cluster share a tile, split its K range and
+    add their partial tiles through distributed shared memory (k-step counts that do not
+    divide by the split, ragged M and N, every epilogue).  The result must be the same from
+    run to run (ranks are added in a fixed order)."""
+    rng = np.random.default_rng(m + 7 * n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    addend = rng.standard_normal((m, n)).astype(np.float32)
+    want = np.maximum(oracle.matmul(a, b) * np.float32(0.5) + addend + bias, 0)
+    kw = dict(m=m, n=n, k=k, math=MATH_TF32, alpha=0.5, bias=_dev(bias), addend=_dev(addend), activation=ACT_RELU)
+    if bsrc == "nk_tma":
+        bd, kw2 = _dev(b.T), dict(trans_b=True)
+    elif bsrc == "kn":
+        bd, kw2 = _dev(b), {}
+    else:
+        bd, kw2 = _dev(oracle.kn4_pack(b)), dict(b_format=B_KN4)
+    c1 = torch.full((m, n), float("nan"), device="cuda")
+    c2 = torch.full((m, n), float("nan"), device="cuda")
+    device.gemm(_dev(a), bd, c1, **kw, **kw2)
+    device.gemm(_dev(a), bd, c2, **kw, **kw2)
+    assert not device.gemm_timed_out()
+    assert nerr(c1, want) <= TF32_TOL
+    assert torch.equal(c1, c2)
