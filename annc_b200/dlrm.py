@@ -8,6 +8,13 @@ the way an ANNC-rewritten graph would call them:
 
 torch holds the device buffers and the stream; all kernels are from libannc_b200.so.
 Buffers are allocated once in __init__, a step allocates nothing.
+
+forward() runs one step and leaves its result ordered on the current stream.
+forward_pipelined() is the throughput form for back-to-back batches: the embedding part of a
+step (gather-latency bound, tensor cores idle) runs on the current stream while the dense part
+of the previous step (interaction + top MLP, tensor-core work) runs on a second stream; two
+sets of intermediate buffers alternate.  Results are the same; sync_pipeline() orders the
+current stream after the last step.
 """
 from __future__ import annotations
 
@@ -75,10 +82,16 @@ class DlrmPipeline:
 
         f32 = dict(dtype=torch.float32, device=device)
         self.acts_b = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.bottom[:-1]]
-        self.z = torch.empty((B, F, D), **f32)
-        self.inter_buf = torch.empty((B, self.inter_pad), **f32)
-        self.acts_t = [torch.empty((B, w.shape[1]), **f32) for w, _ in self.top]
-        self.out = self.acts_t[-1]
+        # two sets of step buffers: forward() uses set 0, forward_pipelined() alternates
+        self._bufs = [dict(z=torch.empty((B, F, D), **f32),
+                           inter=torch.empty((B, self.inter_pad), **f32),
+                           acts_t=[torch.empty((B, w.shape[1]), **f32) for w, _ in self.top])
+                      for _ in range(2)]
+        self._buf = 0
+        self._select(0)
+        self.dense_stream = torch.cuda.Stream(device=device)
+        self._dense_done = [torch.cuda.Event() for _ in range(2)]
+        self._pstep = 0
         self.kernel_names: List[str] = []
         self.launches_per_step = 0
         # The bottom MLP does not depend on the embeddings: it runs on a second stream beside the
@@ -88,21 +101,30 @@ class DlrmPipeline:
         self.embed_launches = 3  # prepass + bag + atomic route
         self._setup_embedding(model)
 
+    def _select(self, buf: int) -> None:
+        """Makes buffer set `buf` the one the next step writes (z, interaction, top activations)."""
+        b = self._bufs[buf]
+        self._buf = buf
+        self.z, self.inter_buf, self.acts_t = b["z"], b["inter"], b["acts_t"]
+        self.out = self.acts_t[-1]
+        if getattr(self, "cur", None) is not None and "plans" in self.sets[self.cur]:
+            self.plan = self.sets[self.cur]["plans"][buf]
+
     def _use(self, i: int) -> None:
         """Makes input set i the one the next forward() reads."""
         st = self.sets[i]
         self.cur = i
         self.ids_all, self.seg_all, self.dense = st["ids_all"], st["seg_all"], st["dense"]
         self.ids, self.segs = st["ids"], st["segs"]
-        if "plan" in st:
-            self.plan = st["plan"]
+        if "plans" in st:
+            self.plan = st["plans"][self._buf]
 
     def _setup_embedding(self, model: DlrmModel) -> None:
         """Single GPU: every table resident, one grouped bag launch writes slots 1.. of z."""
         self.tables = [self._up(t) for t in model.emb.tables]
         for st in self.sets:
-            st["plan"] = dev.BagPlan(self.tables, st["ids"], st["segs"], self.z, 1, self.batch,
-                                     id_kind=2, col=0, combiner=0)
+            st["plans"] = [dev.BagPlan(self.tables, st["ids"], st["segs"], b["z"], 1, self.batch,
+                                       id_kind=2, col=0, combiner=0) for b in self._bufs]
         self._use(self.cur)
 
     def embed_prefetch(self) -> None:
@@ -112,16 +134,20 @@ class DlrmPipeline:
         self.plan.run()
 
     def embed_error_bits(self) -> int:
-        return self.plan.error_bits()
+        bits = 0
+        for st in self.sets:
+            for p in st.get("plans", []):
+                bits |= p.error_bits()
+        return bits
 
     # ------------------------------------------------------------------ one step
-    def forward(self) -> torch.Tensor:
-        names = []
+    def _sparse_part(self, names) -> None:
+        """Bottom MLP (second stream) beside the embedding pooling; z is complete afterwards."""
         B, F, D = self.batch, self.F, self.dim
         x = self.dense
         nb = len(self.bottom)
         main = torch.cuda.current_stream()
-        self.side_stream.wait_stream(main)  # this step's inputs, and the previous step's readers of z
+        self.side_stream.wait_stream(main)  # this step's inputs, and the previous readers of z
         with torch.cuda.stream(self.side_stream):
             for i, (w, b) in enumerate(self.bottom):
                 last = i == nb - 1
@@ -133,6 +159,10 @@ class DlrmPipeline:
         self.embed_prefetch()
         self.embed()
         main.wait_stream(self.side_stream)
+
+    def _dense_part(self, names) -> None:
+        """Interaction + top MLP on the current stream."""
+        B = self.batch
         dev.dot_interaction(self.z, self.inter_buf, self.math)
         x = self.inter_buf
         nt = len(self.top)
@@ -143,9 +173,37 @@ class DlrmPipeline:
                                   math=self.math))
             x = y
         self.kernel_names = names
-        # prepass + bag + scatter route + interaction + one kernel per MLP layer
+        # embedding launches + interaction + one kernel per MLP layer
         self.launches_per_step = self.embed_launches + 1 + len(names)
+
+    def forward(self) -> torch.Tensor:
+        self.sync_pipeline()
+        self._select(0)
+        names = []
+        self._sparse_part(names)
+        self._dense_part(names)
         return self.out
+
+    def forward_pipelined(self) -> torch.Tensor:
+        """One step of a back-to-back sequence: its dense part is queued on `dense_stream` and
+        overlaps the next step's embedding part.  The returned tensor is valid after
+        sync_pipeline() (or a device synchronize)."""
+        buf = self._pstep % 2
+        self._pstep += 1
+        self._select(buf)
+        main = torch.cuda.current_stream()
+        main.wait_event(self._dense_done[buf])  # the step before last has finished with this set
+        names = []
+        self._sparse_part(names)
+        self.dense_stream.wait_stream(main)
+        with torch.cuda.stream(self.dense_stream):
+            self._dense_part(names)
+            self._dense_done[buf].record(self.dense_stream)
+        return self.out
+
+    def sync_pipeline(self) -> None:
+        """Orders the current stream after every queued dense part."""
+        torch.cuda.current_stream().wait_stream(self.dense_stream)
 
     def _issue_copy(self, i: int) -> None:
         st = self.sets[i]

@@ -428,13 +428,19 @@ def run_gpu(args):
              for _ in range(args.steps)]
     it = iter(pairs)
 
+    # Back-to-back batches: the dense part of a step (interaction + top MLP) runs on a second
+    # stream under the next step's embedding part (DlrmPipeline.forward_pipelined).
+    step_fn = getattr(pipe, "forward_pipelined", pipe.forward)
+
     def step_with_hooks():
         a, b = next(it)
         lib.annc_embed_bag_set_timing_events(a, b)
-        pipe.forward()
+        step_fn()
 
     hooks = world == 1 and not recsys
-    ms_total = timed(step_with_hooks if hooks else pipe.forward, args.steps)
+    for _ in range(3):
+        step_fn()
+    ms_total = timed(step_with_hooks if hooks else step_fn, args.steps)
     lib.annc_embed_bag_set_timing_events(None, None)
     bag_ms = []
     for a, b in pairs:
@@ -446,6 +452,8 @@ def run_gpu(args):
         lib.annc_timer_destroy(b)
     ms_step = ms_total / args.steps
     assert pipe.embed_error_bits() == 0, "embedding kernels flagged an error in the timed steps"
+    # one step alone, nothing of a neighbouring step under it (latency rather than throughput)
+    ms_alone = timed(pipe.forward, args.steps) / args.steps
 
     # end-to-end pass: host buffers in, host result out
     for _ in range(2):
@@ -547,6 +555,11 @@ def run_gpu(args):
                         # the end-to-end step is bound by the host-to-device copy of the ids and
                         # index matrices (the operands' own format): GB/s this rank's copies reach
                         "h2d_gbs": pipe.h2d_bytes / (ms_e2e / 1e3) / 1e9},
+                "ms_per_step_unpipelined": ms_alone,
+                "pipelining": "the timed steps are issued back to back; the interaction and top MLP of "
+                              "step i run on a second stream under the embedding part of step i + 1 "
+                              "(two sets of intermediate buffers); ms_per_step_unpipelined is one step "
+                              "with nothing overlapping it" if step_fn is not pipe.forward else "none",
                 "gpu_launches": pipe.launches_per_step * args.steps,
                 "gemm_kernels": sorted(set(pipe.kernel_names)),
                 "roofline": roofline, "clocks": sampler.summary()}
@@ -565,11 +578,12 @@ def run_gpu(args):
             if mode == "row_k0" and args.hot_rows == 0:
                 continue
             p2 = build(mode)
+            f2 = getattr(p2, "forward_pipelined", p2.forward)
             for _ in range(3):
-                p2.forward()
+                f2()
             torch.cuda.synchronize()
             assert p2.embed_error_bits() == 0
-            ms2 = timed(p2.forward, args.steps) / args.steps
+            ms2 = timed(f2, args.steps) / args.steps
             rec = {"value": args.batch * world / (ms2 / 1e3), "unit": UNIT, "ms_per_step": ms2,
                    "parallelism": parallelism_label(args, world, mode)}
             rb = getattr(p2, "rowbags", None)

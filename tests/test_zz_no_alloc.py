@@ -75,3 +75,63 @@ def test_static_scratch_rejects_oversize():
                                              C.c_int32(0), C.c_int(0), C.c_int64(131072),
                                              C.c_int64(64), None, None))
     assert e.value.code == 102 and "exceeds the built-in scratch" in e.value.message
+
+
+def test_static_scratch_allocates_nothing_and_reports_bad_rows():
+    """The property the entry point exists for: once the library is warm, calls leave the
+    device's free memory where it was.  Also: a row outside its table is reported through
+    error_bits_dev, and a sorted call right after an unsorted one on the shared array is exact."""
+    batch = 2048
+    w = synth.embedding_workload(31, [3000, 50], 64, batch, 12, 1.05)
+    tabs = [_dev(t) for t in w.tables]
+    ids = [_dev(b.raw_ids) for b in w.bags]
+    segs = [_dev(b.slice_input) for b in w.bags]
+    want = torch.zeros((batch, 2, 64), device="cuda")
+    plan = BagPlan(tabs, ids, segs, want, 0, batch, id_kind=2, col=0, combiner=0)
+    plan.run()
+    got = torch.zeros_like(want)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # an unsorted call first, so that the shared array holds counters, not offsets
+    rsegs = [_dev(b.slice_input[::-1].copy()) for b in w.bags]
+    rids = [_dev(b.raw_ids[::-1].copy()) for b in w.bags]
+    rplan = BagPlan(tabs, rids, rsegs, want.clone(), 0, batch, id_kind=2, col=0, combiner=0)
+    _run_static(rplan, torch.zeros_like(want), 0, err)
+    _run_static(plan, got, 0, err)  # warm: symbol address looked up, kernels loaded
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        _run_static(plan, got, 0, err)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "annc_embed_bags_static_dev changed the device's free memory"
+    assert torch.equal(got, want) and int(err.item()) == 0
+    # row ids instead of fingerprints, one of them outside its table
+    rows = [_dev((b.raw_ids.view(np.uint64) % np.uint64(t.shape[0])).astype(np.int64)) for b, t in zip(w.bags, w.tables)]
+    rows[1][7] = 50
+    bad = BagPlan(tabs, rows, segs, torch.zeros_like(want), 0, batch, id_kind=1, col=0, combiner=0)
+    _run_static(bad, torch.zeros_like(want), 0, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) & 1
+
+
+def test_static_scratch_more_tables_than_one_launch_takes():
+    """More than 120 tables (the limit of one grouped launch) inside the scratch limit: the entry
+    point walks them in groups on the shared array."""
+    n, batch, dim = 130, 64, 16
+    rng = np.random.default_rng(5)
+    tabs = [_dev(rng.standard_normal((40, dim)).astype(np.float32)) for _ in range(n)]
+    lens = rng.integers(0, 4, (n, batch))
+    ids, segs = [], []
+    for t in range(n):
+        seg = np.repeat(np.arange(batch, dtype=np.int64), lens[t])
+        ids.append(_dev(rng.integers(0, 1 << 40, seg.shape[0]).astype(np.int64)))
+        segs.append(_dev(np.stack([seg, np.zeros_like(seg)], axis=1).reshape(-1, 2)))
+    want = torch.full((batch, n, dim), 5.0, device="cuda")
+    plan = BagPlan(tabs, ids, segs, want, 0, batch, id_kind=2, col=0, combiner=0)
+    plan.run()
+    got = torch.full((batch, n, dim), -5.0, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _run_static(plan, got, 0, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0 and torch.equal(got, want)
