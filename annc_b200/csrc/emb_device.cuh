@@ -44,6 +44,38 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) {
   a.w = __fadd_rn(a.w, b.w);
 }
 
+// A lane's share of a row: VW consecutive floats (16, 8 or 4 bytes), loaded through the
+// read-only path and added with round-to-nearest adds (no contraction).
+template <int VW> struct RowVec;
+template <> struct RowVec<4> {
+  float4 v;
+  __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ void add(const RowVec& o) {
+    v.x = __fadd_rn(v.x, o.v.x); v.y = __fadd_rn(v.y, o.v.y); v.z = __fadd_rn(v.z, o.v.z); v.w = __fadd_rn(v.w, o.v.w);
+  }
+  __device__ __forceinline__ void scale(float f) {
+    v.x = __fmul_rn(v.x, f); v.y = __fmul_rn(v.y, f); v.z = __fmul_rn(v.z, f); v.w = __fmul_rn(v.w, f);
+  }
+};
+template <> struct RowVec<2> {
+  float2 v;
+  __device__ __forceinline__ void zero() { v = make_float2(0.f, 0.f); }
+  __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float2*>(p)); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float2*>(p) = v; }
+  __device__ __forceinline__ void add(const RowVec& o) { v.x = __fadd_rn(v.x, o.v.x); v.y = __fadd_rn(v.y, o.v.y); }
+  __device__ __forceinline__ void scale(float f) { v.x = __fmul_rn(v.x, f); v.y = __fmul_rn(v.y, f); }
+};
+template <> struct RowVec<1> {
+  float v;
+  __device__ __forceinline__ void zero() { v = 0.f; }
+  __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
+  __device__ __forceinline__ void store(float* p) const { *p = v; }
+  __device__ __forceinline__ void add(const RowVec& o) { v = __fadd_rn(v, o.v); }
+  __device__ __forceinline__ void scale(float f) { v = __fmul_rn(v, f); }
+};
+
 // ---- exclusive scan of int32 (three passes, 2048 items per block) ---------------
 constexpr int kScanThreads = 512;
 constexpr int kScanItems = 4;

@@ -30,13 +30,13 @@ static void launch_bag(const BagParams& p, BagHeader* hdr, int* offsets, cudaStr
   else bag_reduce_kernel<LANES, VPL, false><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
 }
 
-template <int LANES, int VPL, int TILES, int INFLIGHT, int MINB>
+template <int LANES, int VW, int VPL, int TILES, int INFLIGHT, int MINB>
 static void launch_stream(const BagParams& p, BagHeader* hdr, cudaStream_t s) {
   static int per_sm[kMaxDevices] = {0};
   const int slot = device_slot();
   if (!per_sm[slot]) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, bag_stream_kernel<LANES, VPL, TILES, INFLIGHT, MINB>,
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, bag_stream_kernel<LANES, VW, VPL, TILES, INFLIGHT, MINB>,
                                                       256, 0) != cudaSuccess || n < 1)
       n = 2;
     per_sm[slot] = n;
@@ -54,7 +54,7 @@ static void launch_stream(const BagParams& p, BagHeader* hdr, cudaStream_t s) {
   // a persistent grid, no larger than the chunks there are
   const long long groups_per_block = (256 / 32) * (32 / LANES);
   long long blocks = std::min<long long>((long long)sms * per_sm[slot], (total + groups_per_block - 1) / groups_per_block);
-  bag_stream_kernel<LANES, VPL, TILES, INFLIGHT, MINB><<<(unsigned)std::max<long long>(blocks, 1), 256, 0, s>>>(p, sc, hdr);
+  bag_stream_kernel<LANES, VW, VPL, TILES, INFLIGHT, MINB><<<(unsigned)std::max<long long>(blocks, 1), 256, 0, s>>>(p, sc, hdr);
 }
 
 // Launches the bag kernels (+ the atomic route) for up to kMaxTables tables.
@@ -119,12 +119,14 @@ static int run_bags(const annc_bag_table* tables, int num_tables, int64_t dim, i
   if (stream) {
     if (ev0) cudaEventRecord(ev0, s);
     switch (vecs) {
-      case 4: launch_stream<4, 1, 8, 4, 5>(p, hdr, s); break;
-      case 8: launch_stream<8, 1, 8, 4, 5>(p, hdr, s); break;
-      case 16: launch_stream<16, 1, 8, 4, 5>(p, hdr, s); break;
-      case 32: launch_stream<32, 1, 8, 4, 5>(p, hdr, s); break;
-      case 64: launch_stream<32, 2, 8, 4, 4>(p, hdr, s); break;
-      default: launch_stream<32, 4, 8, 2, 3>(p, hdr, s); break;
+      // 16 bytes per lane: a row of dim 64 is a half warp (measured faster than a whole warp
+      // with 8 bytes per lane: twice the row loads in flight per warp)
+      case 4: launch_stream<4, 4, 1, 8, 4, 5>(p, hdr, s); break;
+      case 8: launch_stream<8, 4, 1, 8, 4, 5>(p, hdr, s); break;
+      case 16: launch_stream<16, 4, 1, 8, 4, 5>(p, hdr, s); break;
+      case 32: launch_stream<32, 4, 1, 4, 4, 5>(p, hdr, s); break;
+      case 64: launch_stream<32, 4, 2, 4, 4, 4>(p, hdr, s); break;
+      default: launch_stream<32, 4, 4, 4, 2, 3>(p, hdr, s); break;
     }
     if (ev1) cudaEventRecord(ev1, s);
     dim3 rs_grid(148, num_tables);

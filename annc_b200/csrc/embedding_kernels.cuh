@@ -348,13 +348,14 @@ struct StreamChunks {
   int first[kMaxTables + 1];
 };
 
-template <int LANES, int VPL, int TILES, int INFLIGHT_, int MINB>
+template <int LANES, int VW, int VPL, int TILES, int INFLIGHT_, int MINB>
 __global__ void __launch_bounds__(256, MINB)
 bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
   constexpr int GROUPS_PER_WARP = 32 / LANES;
   constexpr int CHUNK = LANES * TILES;
   constexpr int INFLIGHT = LANES < INFLIGHT_ ? LANES : INFLIGHT_;
-  constexpr int ROW4 = LANES * VPL;
+  constexpr int ROWF = LANES * VW * VPL;  // floats per row
+  using Vec = RowVec<VW>;
   constexpr unsigned kLaneMask = LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u);
   constexpr int kNoBag = -3;  // a lookup whose segment id is out of range is added nowhere
   __shared__ int s_first[kMaxTables + 1];
@@ -368,7 +369,6 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
   const unsigned group = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GROUPS_PER_WARP +
                          lane_in_warp / LANES;
   const unsigned num_groups = gridDim.x * (blockDim.x >> 5) * GROUPS_PER_WARP;
-  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const unsigned total_chunks = (unsigned)s_first[p.num_tables];
 
   // Consecutive groups take consecutive chunks, so the whole grid works through one table
@@ -384,15 +384,17 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
     const unsigned chunk = gc - (unsigned)s_first[t];
     const BagTableDev& T = p.t[t];
     const int n = T.nnz;
-    const float4* __restrict__ tab = reinterpret_cast<const float4*>(T.table);
+    const float* __restrict__ tab = T.table;
     float* __restrict__ outp = T.out;
 
     // rows [a, b) of the output <- 0 (bags without lookups)
     auto zero_fill = [&](int a, int b) {
+      Vec z;
+      z.zero();
       for (int s = a; s < b; ++s) {
-        float4* o = reinterpret_cast<float4*>(outp + (long long)s * p.out_stride);
+        float* o = outp + (long long)s * p.out_stride;
 #pragma unroll
-        for (int w = 0; w < VPL; ++w) o[w * LANES + lane] = zero4;
+        for (int w = 0; w < VPL; ++w) z.store(o + (w * LANES + lane) * VW);
       }
     };
     if (n == 0) {  // a table without lookups: every bag is empty
@@ -400,9 +402,9 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
       continue;
     }
     {
-    float4 acc[VPL];
+    Vec acc[VPL];
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) acc[v] = zero4;
+    for (int v = 0; v < VPL; ++v) acc[v].zero();
     int cur = kNoBag;   // bag being summed
     int count = 0;      // its lookups so far (for the mean)
     bool open = false;
@@ -413,16 +415,11 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
         if (p.combiner == 1 && count > 0) {
           const float inv = __fdiv_rn(1.0f, (float)count);
 #pragma unroll
-          for (int w = 0; w < VPL; ++w) {
-            acc[w].x = __fmul_rn(acc[w].x, inv);
-            acc[w].y = __fmul_rn(acc[w].y, inv);
-            acc[w].z = __fmul_rn(acc[w].z, inv);
-            acc[w].w = __fmul_rn(acc[w].w, inv);
-          }
+          for (int w = 0; w < VPL; ++w) acc[w].scale(inv);
         }
-        float4* o = reinterpret_cast<float4*>(outp + (long long)cur * p.out_stride);
+        float* o = outp + (long long)cur * p.out_stride;
 #pragma unroll
-        for (int w = 0; w < VPL; ++w) o[w * LANES + lane] = acc[w];
+        for (int w = 0; w < VPL; ++w) acc[w].store(o + (w * LANES + lane) * VW);
       }
     };
 
@@ -459,7 +456,7 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
         if (smask != 0) to = __ffs(smask) - 1;
       }
       for (int j0 = from; j0 < to; j0 += INFLIGHT) {
-        float4 v[INFLIGHT][VPL];
+        Vec v[INFLIGHT][VPL];
         bool has[INFLIGHT];
 #pragma unroll
         for (int k = 0; k < INFLIGHT; ++k) {
@@ -469,9 +466,9 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
             const int rw = __shfl_sync(gmask, row, j, LANES);
             has[k] = rw >= 0;
             if (has[k]) {
-              const float4* src = tab + (long long)rw * ROW4 + lane;
+              const float* src = tab + (long long)rw * ROWF + lane * VW;
 #pragma unroll
-              for (int w = 0; w < VPL; ++w) v[k][w] = __ldg(src + w * LANES);
+              for (int w = 0; w < VPL; ++w) v[k][w].load(src + w * LANES * VW);
             }
           }
         }
@@ -482,7 +479,7 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
             if ((smask >> j) & 1u) {
               flush();
 #pragma unroll
-              for (int w = 0; w < VPL; ++w) acc[w] = zero4;
+              for (int w = 0; w < VPL; ++w) acc[w].zero();
               cur = __shfl_sync(gmask, key, j, LANES);
               const int before = __shfl_sync(gmask, prev_key, j, LANES);
               // empty bags between the previous lookup's bag and this one (sorted input only)
@@ -493,7 +490,7 @@ bag_stream_kernel(BagParams p, StreamChunks sc, BagHeader* hdr) {
             ++count;
             if (has[k]) {
 #pragma unroll
-              for (int w = 0; w < VPL; ++w) add4(acc[w], v[k][w]);
+              for (int w = 0; w < VPL; ++w) acc[w].add(v[k][w]);
             }
           }
         }

@@ -47,7 +47,7 @@ class BagPlan:
             d.nnz = int(ids[t].shape[0])
             d.out = out.data_ptr() + (out_slot0 + t) * self.dim * esz
         self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
-        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=out.device)
+        self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=out.device)
 
     def run(self) -> None:
         check(lib.annc_embed_bags_dev(self.desc, C.c_int(self.n), C.c_int64(self.dim),
@@ -176,7 +176,7 @@ class BagLaunch:
                 tp, int(rows), int(nb), ip, sp, int(nnz), op
             d.offsets = e[7] if len(e) > 7 else None
         self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
-        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
+        self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=device)
 
     def run(self) -> None:
         if self.exchange:
