@@ -36,10 +36,13 @@ if ROOT not in sys.path:
 METRIC = "dlrm_inference_samples_per_s"
 UNIT = "samples/s"
 
-# DRAM bytes (read + write) of one bag-kernel launch: a constant from an earlier single-pass
-# profiler capture of this command's default workload, not measured by this run.
-# Keyed by (batch, max_rows, seed); any other workload reports null.
-NCU_BAG_TRAFFIC_BYTES = {(65536, 1e7, 0): 1.573e9}
+# DRAM bytes (read + write) of one bag-kernel launch: a constant, not measured by this run.  It is
+# the dram__bytes_read.sum + dram__bytes_write.sum of a profiler capture of the small case
+# (batch 16384, rows <= 1e6: 0.5465 GB for 4,472,660 lookups) scaled to this workload by the lookups
+# per launch; traffic grows in proportion (the same scaling of the previous kernel's small-case
+# figure matched a full-size capture within 2 %).  Keyed by (batch, max_rows, seed); any other
+# workload reports null.
+NCU_BAG_TRAFFIC_BYTES = {(65536, 1e7, 0): 0.5465e9 * 17883957 / 4472660}
 
 
 def parse_args():
@@ -404,7 +407,7 @@ def run_gpu(args):
                                  input_seed=(1000 + rank) if world > 1 else None)
         emb_bytes = model.emb.algorithmic_bytes()
         nnz = model.emb.nnz
-        bag_kernel = "bag_reduce_kernel<16,1> (hash-bucket + gather + segment sum, 26 tables in one launch)"
+        bag_kernel = "bag_stream_kernel<16,4,1,8,4,5> (hash-bucket + gather + segment sum, 26 tables in one launch)"
 
         def build(mode):
             if world == 1:
@@ -522,12 +525,12 @@ def run_gpu(args):
                     "peak_source": peak_source,
                     "label": "algorithmic GB/s (L2-assisted): algorithmic bytes per launch / kernel time; "
                              "Zipf-hot rows are served by L2, so DRAM moves less (dram_frac)",
-                    "limited_by": "L2 / row-gather latency, not DRAM bandwidth",
+                    "limited_by": "instruction issue and L2 / row-gather latency, not DRAM bandwidth",
                     "algorithmic_bytes_per_launch": emb_bytes, "lookups_per_launch": nnz,
                     "kernel_ms": bag_avg_ms, "traffic": traffic,
-                    "traffic_source": "constant from an offline single-pass ncu capture of this workload "
-                                      "(dram__bytes_read.sum + dram__bytes_write.sum), not measured by this run"
-                                      if traffic else None,
+                    "traffic_source": "constant, not measured by this run: ncu dram__bytes_read.sum + "
+                                      "dram__bytes_write.sum of the small case (batch 16384, rows <= 1e6) scaled "
+                                      "by the lookups per launch" if traffic else None,
                     "dram_gbs": traffic / (bag_avg_ms / 1e3) / 1e9 if traffic else None,
                     "dram_frac": traffic / (bag_avg_ms / 1e3) / 1e9 / hbm_peak if traffic else None}
     else:
