@@ -25,19 +25,29 @@ namespace rowx {
 
 static size_t up256(size_t n) { return (n + 255) & ~size_t(255); }
 
+// The peer-visible buffer of a rank.  Lists, bounds and receive slabs exist twice: a rank may
+// publish the lists of step i + 1 while its peers still pool step i and while it still adds the
+// parts of step i, so consecutive steps alternate between the two sets.
 struct Layout {
-  size_t flags, bounds, records, recv, total;
+  size_t flags, bounds, records[2], recv[2], total;
   size_t slab_floats;
 };
+constexpr int kFlagWordsA = 0;    // barrier "lists published"
+constexpr int kFlagWordsB = 16;   // barrier "parts stored"
+constexpr int kBoundsInts = 32;   // ints per set of published bounds
 
 static Layout layout_of(int world, int num_tables, int64_t batch, int64_t dim, int64_t max_lookups) {
   Layout l;
   l.flags = 0;
   l.bounds = 256;
-  l.records = 512;
-  l.recv = l.records + up256((size_t)std::max<int64_t>(max_lookups, 1) * sizeof(int2));
+  const size_t rec = up256((size_t)std::max<int64_t>(max_lookups, 1) * sizeof(int2));
+  l.records[0] = 512;
+  l.records[1] = l.records[0] + rec;
   l.slab_floats = (size_t)batch * (size_t)num_tables * (size_t)dim;
-  l.total = l.recv + up256((size_t)world * l.slab_floats * sizeof(float));
+  const size_t slabs = up256((size_t)world * l.slab_floats * sizeof(float));
+  l.recv[0] = l.records[1] + rec;
+  l.recv[1] = l.recv[0] + slabs;
+  l.total = l.recv[1] + slabs;
   return l;
 }
 
@@ -59,19 +69,17 @@ struct Exchange {
   int* local = nullptr;
   int* pos = nullptr;         // counts, then positions: world * T * blocks_x + 1
   int* scan_tiles = nullptr;
-  unsigned* mask = nullptr;   // [T * batch]
+  unsigned* mask[2] = {nullptr, nullptr};   // [T * batch], one per step in flight
   int* meta = nullptr;        // (first, count) per source
   int* err = nullptr;
-  void* offsets_ws = nullptr; // bag offsets for mean pooling
+  void* offsets_ws[2] = {nullptr, nullptr};  // bag offsets for mean pooling
   size_t offsets_ws_bytes = 0;
   long long pos_n = 0;
-  int epoch = 0;
+  long long begun = 0, pooled = 0, finished = 0;  // steps that passed each phase
   unsigned long long limit_ns = 2000000000ull;
-  int variant = 0;
   bool profiling = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   bool ev_valid = false;
-  int phase = 0;  // 0 idle, 1 after begin, 2 after pool
   PoolParams pool;
   BarrierParams bar;
 };
@@ -105,16 +113,11 @@ static int run_pool(const Exchange& x, cudaStream_t s) {
   switch ((int)(x.dim / 4)) {
     case 4: launch_pool<4, 1, 8, 4, 5>(x, s); break;
     case 8: launch_pool<8, 1, 8, 4, 5>(x, s); break;
-    case 16:
-      switch (x.variant) {
-        case 1: launch_pool<16, 1, 16, 4, 5>(x, s); break;
-        case 2: launch_pool<16, 1, 32, 4, 5>(x, s); break;
-        case 3: launch_pool<16, 1, 8, 2, 6>(x, s); break;
-        case 4: launch_pool<16, 1, 4, 4, 5>(x, s); break;
-        default: launch_pool<16, 1, 8, 4, 5>(x, s); break;
-      }
-      break;
-    case 32: launch_pool<32, 1, 8, 4, 5>(x, s); break;
+    // dim 64 and 128: half as many lanes per row as 16-byte pieces, two pieces per lane, two row
+    // loads in flight (fewer lanes repeat the per-record control instructions: 0.67 ms against
+    // 0.76 ms for the 17.9 M lookups of the DLRM batch)
+    case 16: launch_pool<8, 2, 16, 2, 5>(x, s); break;
+    case 32: launch_pool<16, 2, 8, 2, 5>(x, s); break;
     case 64: launch_pool<32, 2, 8, 4, 4>(x, s); break;
     case 128: launch_pool<32, 4, 8, 2, 3>(x, s); break;
     default: return fail(ANNC_ERR_UNSUPPORTED, "row exchange: dim must be 16, 32, 64, 128, 256 or 512");
@@ -128,10 +131,12 @@ static void destroy(Exchange* x) {
   cudaFree(x->local);
   cudaFree(x->pos);
   cudaFree(x->scan_tiles);
-  cudaFree(x->mask);
+  cudaFree(x->mask[0]);
+  cudaFree(x->mask[1]);
   cudaFree(x->meta);
   cudaFree(x->err);
-  cudaFree(x->offsets_ws);
+  cudaFree(x->offsets_ws[0]);
+  cudaFree(x->offsets_ws[1]);
   for (auto& h : x->hot) {
     cudaFree(h.words);
     cudaFree(h.prefix);
@@ -203,14 +208,18 @@ int annc_row_exchange_create(const annc_row_exchange_config* c, void* const* pee
   alloc((void**)&x->local, (size_t)c->max_lookups * sizeof(int));
   alloc((void**)&x->pos, (size_t)x->pos_n * sizeof(int));
   alloc((void**)&x->scan_tiles, (size_t)scan_tiles * sizeof(int));
-  alloc((void**)&x->mask, (size_t)x->T * (size_t)x->batch * sizeof(unsigned));
+  alloc((void**)&x->mask[0], (size_t)x->T * (size_t)x->batch * sizeof(unsigned));
+  alloc((void**)&x->mask[1], (size_t)x->T * (size_t)x->batch * sizeof(unsigned));
   alloc((void**)&x->meta, 2 * kMaxWorld * sizeof(int));
   alloc((void**)&x->err, 256);
   if (c->combiner == 1) {
     x->offsets_ws_bytes = annc_embed_bag_workspace_bytes(x->T, x->batch);
-    alloc(&x->offsets_ws, x->offsets_ws_bytes);
+    alloc(&x->offsets_ws[0], x->offsets_ws_bytes);
+    alloc(&x->offsets_ws[1], x->offsets_ws_bytes);
   }
   if (e == cudaSuccess) e = cudaMemset(x->err, 0, 256);
+  for (int b = 0; b < 2 && e == cudaSuccess; ++b)
+    if (x->offsets_ws[b]) e = cudaMemset(x->offsets_ws[b], 0, 512);  // header: error word, marks
   if (e == cudaSuccess) e = cudaMemset(x->pos, 0, (size_t)x->pos_n * sizeof(int));
   // this rank's flags and bounds start at zero; the caller orders create() on all ranks
   // before the first step (a host barrier), so no peer's flag can be wiped here
@@ -271,8 +280,6 @@ int annc_row_exchange_create(const annc_row_exchange_config* c, void* const* pee
                           (unsigned long long)x->batch;
   }
   for (int q = 0; q < x->world; ++q) {
-    x->pool.list[q] = reinterpret_cast<const int2*>(x->peer[q] + x->lay.records);
-    x->pool.out[q] = reinterpret_cast<float*>(x->peer[q] + x->lay.recv) + (size_t)x->rank * x->lay.slab_floats;
     x->bar.flags[q] = reinterpret_cast<int*>(x->peer[q] + x->lay.flags);
     x->bar.bounds[q] = reinterpret_cast<const int*>(x->peer[q] + x->lay.bounds);
   }
@@ -299,11 +306,6 @@ int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms) {
   return ANNC_OK;
 }
 
-int annc_row_exchange_set_variant(annc_row_exchange* ex, int v) {
-  reinterpret_cast<Exchange*>(ex)->variant = v;
-  return ANNC_OK;
-}
-
 int annc_row_exchange_set_profiling(annc_row_exchange* ex, int on) {
   ANNC_REQUIRE(ex, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null object");
   reinterpret_cast<Exchange*>(ex)->profiling = on != 0;
@@ -314,9 +316,11 @@ int annc_row_exchange_begin(annc_row_exchange* ex, const annc_bag_table* inputs,
                             int32_t col, void* stream) {
   auto* x = reinterpret_cast<Exchange*>(ex);
   ANNC_REQUIRE(x && inputs, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null argument");
-  ANNC_REQUIRE(x->phase == 0, ANNC_ERR_INVALID_ARGUMENT, "row exchange: begin called inside a step");
+  ANNC_REQUIRE(x->begun - x->finished <= 1, ANNC_ERR_INVALID_ARGUMENT,
+               "row exchange: begin may run at most one step ahead of finish");
   ANNC_REQUIRE(col >= 0 && col < ncols, ANNC_ERR_INVALID_ARGUMENT, "Column index out of range");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int buf = (int)(x->begun & 1);
   ClassifyParams p;
   memset(&p, 0, sizeof(p));
   long long flat = 0;
@@ -350,40 +354,47 @@ int annc_row_exchange_begin(annc_row_exchange* ex, const annc_bag_table* inputs,
   p.col = col;
   p.blocks_x = x->blocks_x;
   char* mine = x->peer[x->rank];
-  if (x->profiling) cudaEventRecord(x->ev[0], s);
+  const bool prof = x->profiling && x->begun == x->finished;  // phase times of steps run one at a time
+  if (prof) cudaEventRecord(x->ev[0], s);
   if (x->combiner == 1)  // bag lengths for the mean
-    ANNC_TRY(annc_embed_bag_prepass_dev(inputs, x->T, ncols, col, x->batch, x->offsets_ws,
+    ANNC_TRY(annc_embed_bag_prepass_dev(inputs, x->T, ncols, col, x->batch, x->offsets_ws[buf],
                                         x->offsets_ws_bytes, s));
-  ANNC_CUDA(cudaMemsetAsync(x->mask, 0, (size_t)x->T * (size_t)x->batch * sizeof(unsigned), s));
+  ANNC_CUDA(cudaMemsetAsync(x->mask[buf], 0, (size_t)x->T * (size_t)x->batch * sizeof(unsigned), s));
   ANNC_CUDA(cudaMemsetAsync(x->pos + (x->pos_n - 1), 0, sizeof(int), s));  // closing entry
   dim3 grid((unsigned)x->blocks_x, (unsigned)x->T);
   classify_kernel<<<grid, kClassifyThreads, 0, s>>>(p, x->owner, x->local, x->pos, x->err);
   exclusive_scan_inplace(x->pos, x->pos_n, x->scan_tiles, s);
   scatter_kernel<<<grid, kClassifyThreads, 0, s>>>(p, x->owner, x->local, x->pos,
-                                                   reinterpret_cast<int2*>(mine + x->lay.records),
-                                                   x->mask, x->err);
-  if (x->profiling) cudaEventRecord(x->ev[1], s);
-  x->epoch += 1;
-  arrive_kernel<<<1, 32, 0, s>>>(x->bar, x->epoch, x->pos, (long long)x->T * x->blocks_x,
-                                 reinterpret_cast<int*>(mine + x->lay.bounds));
+                                                   reinterpret_cast<int2*>(mine + x->lay.records[buf]),
+                                                   x->mask[buf], x->err);
+  if (prof) cudaEventRecord(x->ev[1], s);
+  x->begun += 1;
+  arrive_kernel<<<1, 32, 0, s>>>(x->bar, kFlagWordsA, (int)x->begun, x->pos, (long long)x->T * x->blocks_x,
+                                 reinterpret_cast<int*>(mine + x->lay.bounds) + buf * kBoundsInts);
   ANNC_CUDA(cudaGetLastError());
-  x->phase = 1;
   return ANNC_OK;
 }
 
 int annc_row_exchange_pool(annc_row_exchange* ex, void* stream) {
   auto* x = reinterpret_cast<Exchange*>(ex);
   ANNC_REQUIRE(x, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null object");
-  ANNC_REQUIRE(x->phase == 1, ANNC_ERR_INVALID_ARGUMENT, "row exchange: pool needs a begin before it");
+  ANNC_REQUIRE(x->begun > x->pooled && x->pooled == x->finished, ANNC_ERR_INVALID_ARGUMENT,
+               "row exchange: pool needs a begin before it and the previous step finished");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  wait_kernel<<<1, 32, 0, s>>>(x->bar, x->epoch, x->limit_ns, x->meta, (int)x->max_lookups, x->err);
-  if (x->profiling) cudaEventRecord(x->ev[2], s);
+  const int buf = (int)(x->pooled & 1);
+  const bool prof = x->profiling && x->begun == x->pooled + 1;
+  wait_kernel<<<1, 32, 0, s>>>(x->bar, kFlagWordsA, (int)(x->pooled + 1), x->limit_ns, x->meta,
+                               buf * kBoundsInts, (int)x->max_lookups, x->err);
+  if (prof) cudaEventRecord(x->ev[2], s);
+  for (int q = 0; q < x->world; ++q) {
+    x->pool.list[q] = reinterpret_cast<const int2*>(x->peer[q] + x->lay.records[buf]);
+    x->pool.out[q] = reinterpret_cast<float*>(x->peer[q] + x->lay.recv[buf]) + (size_t)x->rank * x->lay.slab_floats;
+  }
   ANNC_TRY(run_pool(*x, s));
-  if (x->profiling) cudaEventRecord(x->ev[3], s);
-  x->epoch += 1;
-  arrive_kernel<<<1, 32, 0, s>>>(x->bar, x->epoch, nullptr, 0, nullptr);
+  if (prof) cudaEventRecord(x->ev[3], s);
+  x->pooled += 1;
+  arrive_kernel<<<1, 32, 0, s>>>(x->bar, kFlagWordsB, (int)x->pooled, nullptr, 0, nullptr);
   ANNC_CUDA(cudaGetLastError());
-  x->phase = 2;
   return ANNC_OK;
 }
 
@@ -391,18 +402,20 @@ int annc_row_exchange_finish(annc_row_exchange* ex, void* out, int64_t out_strid
                              void* stream) {
   auto* x = reinterpret_cast<Exchange*>(ex);
   ANNC_REQUIRE(x && out, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null argument");
-  ANNC_REQUIRE(x->phase == 2, ANNC_ERR_INVALID_ARGUMENT, "row exchange: finish needs a pool before it");
+  ANNC_REQUIRE(x->pooled > x->finished, ANNC_ERR_INVALID_ARGUMENT, "row exchange: finish needs a pool before it");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  wait_kernel<<<1, 32, 0, s>>>(x->bar, x->epoch, x->limit_ns, nullptr, 0, x->err);
-  if (x->profiling) cudaEventRecord(x->ev[4], s);
-  const float* recv = reinterpret_cast<const float*>(x->peer[x->rank] + x->lay.recv);
+  const int buf = (int)(x->finished & 1);
+  const bool prof = x->profiling && x->begun == x->finished + 1;
+  wait_kernel<<<1, 32, 0, s>>>(x->bar, kFlagWordsB, (int)(x->finished + 1), x->limit_ns, nullptr, 0, 0, x->err);
+  if (prof) cudaEventRecord(x->ev[4], s);
+  const float* recv = reinterpret_cast<const float*>(x->peer[x->rank] + x->lay.recv[buf]);
   const int32_t* mean_off = x->combiner == 1
-                                ? reinterpret_cast<const int32_t*>(static_cast<char*>(x->offsets_ws) + 512)  // header of the bag workspace
+                                ? reinterpret_cast<const int32_t*>(static_cast<char*>(x->offsets_ws[buf]) + 512)  // header of the bag workspace
                                 : nullptr;
-  x->phase = 0;
-  ANNC_TRY(annc_sum_partials_masked_dev(recv, x->mask, x->world, (int64_t)x->lay.slab_floats, x->batch,
+  x->finished += 1;
+  ANNC_TRY(annc_sum_partials_masked_dev(recv, x->mask[buf], x->world, (int64_t)x->lay.slab_floats, x->batch,
                                         x->T, x->dim, mean_off, out, out_stride, out_bf16, s));
-  if (x->profiling) {
+  if (prof) {
     cudaEventRecord(x->ev[5], s);
     x->ev_valid = true;
   }
@@ -411,7 +424,9 @@ int annc_row_exchange_finish(annc_row_exchange* ex, void* out, int64_t out_strid
 
 int annc_row_exchange_step(annc_row_exchange* ex, const annc_bag_table* inputs, int64_t ncols,
                            int32_t col, void* out, int64_t out_stride, int out_bf16, void* stream) {
-  ANNC_TRY(annc_row_exchange_begin(ex, inputs, ncols, col, stream));
+  auto* x = reinterpret_cast<Exchange*>(ex);
+  ANNC_REQUIRE(x, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null object");
+  if (x->begun == x->finished) ANNC_TRY(annc_row_exchange_begin(ex, inputs, ncols, col, stream));
   ANNC_TRY(annc_row_exchange_pool(ex, stream));
   return annc_row_exchange_finish(ex, out, out_stride, out_bf16, stream);
 }
@@ -423,9 +438,11 @@ int annc_row_exchange_check(annc_row_exchange* ex, void* stream, int* error_bits
   ANNC_CUDA(cudaMemcpyAsync(error_bits, x->err, sizeof(int), cudaMemcpyDeviceToHost, s));
   ANNC_CUDA(cudaStreamSynchronize(s));
   if (x->combiner == 1) {  // segment errors seen by the prepass
-    int pre = 0;
-    ANNC_CUDA(cudaMemcpy(&pre, x->offsets_ws, sizeof(int), cudaMemcpyDeviceToHost));
-    *error_bits |= pre & (kErrRow | kErrSegment);
+    for (int b = 0; b < 2; ++b) {
+      int pre = 0;
+      ANNC_CUDA(cudaMemcpy(&pre, x->offsets_ws[b], sizeof(int), cudaMemcpyDeviceToHost));
+      *error_bits |= pre & (kErrRow | kErrSegment);
+    }
   }
   if (*error_bits & kErrTimeout)
     return fail(ANNC_ERR_TIMEOUT, "row exchange: a peer's flag did not arrive within the limit");
@@ -459,7 +476,8 @@ int annc_row_exchange_stats(annc_row_exchange* ex, void* stream, int64_t* record
   int meta[2 * kMaxWorld];
   ANNC_CUDA(cudaMemcpyAsync(meta, x->meta, sizeof(meta), cudaMemcpyDeviceToHost, s));
   std::vector<unsigned> mask((size_t)x->T * (size_t)x->batch);
-  ANNC_CUDA(cudaMemcpyAsync(mask.data(), x->mask, mask.size() * 4, cudaMemcpyDeviceToHost, s));
+  const int last = (int)((x->finished + 1) & 1);  // buffer of the last finished step
+  ANNC_CUDA(cudaMemcpyAsync(mask.data(), x->mask[last], mask.size() * 4, cudaMemcpyDeviceToHost, s));
   ANNC_CUDA(cudaStreamSynchronize(s));
   for (int q = 0; q < x->world; ++q) {
     records_per_source[q] = meta[2 * q + 1];

@@ -197,10 +197,11 @@ scatter_kernel(ClassifyParams p, const unsigned char* __restrict__ owner_in,
 }
 
 // ---- flag barrier between the ranks ---------------------------------------------------
-// Every rank owns flags[kMaxWorld] in its peer-visible buffer; flags[q] is written by rank q
-// only and only grows (the step's epoch).  arrive: publishes this rank's list bounds, then
-// stores the epoch into flags[rank] of every rank.  wait: spins on the own flags until all
-// have reached the epoch, for at most `limit_ns`; a time-out sets kErrTimeout and returns.
+// Every rank owns two sets of flag words in its peer-visible buffer (one per barrier of a
+// step: "lists published" and "parts stored"); word q of a set is written by rank q only and
+// only grows (the step number).  arrive: publishes this rank's list bounds, then stores the
+// epoch into its word of every rank's set.  wait: spins on the own set until all words have
+// reached the epoch, for at most `limit_ns`; a time-out sets kErrTimeout and returns.
 struct BarrierParams {
   int* flags[kMaxWorld];         // rank q's flag array as seen from here ([rank] is local)
   const int* bounds[kMaxWorld];  // rank q's published list bounds int[world + 1]
@@ -208,26 +209,27 @@ struct BarrierParams {
   int rank;
 };
 
-__global__ void arrive_kernel(BarrierParams b, int epoch, const int* __restrict__ pos,
+__global__ void arrive_kernel(BarrierParams b, int word0, int epoch, const int* __restrict__ pos,
                               long long pos_stride, int* __restrict__ my_bounds) {
   const int lane = threadIdx.x;
   if (pos && lane <= b.world) my_bounds[lane] = pos[(long long)lane * pos_stride];
   __threadfence_system();
   __syncwarp();
   if (lane < b.world) {
-    volatile int* f = b.flags[lane] + b.rank;
+    volatile int* f = b.flags[lane] + word0 + b.rank;
     *f = epoch;
   }
 }
 
 // meta[2 q] = first record, meta[2 q + 1] = number of records of source q's list for this rank
-// (zero when the source timed out or published bounds outside [0, capacity]).
-__global__ void wait_kernel(BarrierParams b, int epoch, unsigned long long limit_ns,
-                            int* __restrict__ meta, int capacity, int* __restrict__ err) {
+// (zero when the source timed out or published bounds outside [0, capacity]).  word0 selects the
+// barrier's flag words, bounds_off the set of published bounds (steps alternate between two).
+__global__ void wait_kernel(BarrierParams b, int word0, int epoch, unsigned long long limit_ns,
+                            int* __restrict__ meta, int bounds_off, int capacity, int* __restrict__ err) {
   const int lane = threadIdx.x;
   bool ok = true;
   if (lane < b.world) {
-    volatile const int* f = b.flags[b.rank] + lane;
+    volatile const int* f = b.flags[b.rank] + word0 + lane;
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     while (*f < epoch) {
@@ -246,7 +248,7 @@ __global__ void wait_kernel(BarrierParams b, int epoch, unsigned long long limit
   if (meta && lane < b.world) {
     int lo = 0, n = 0;
     if (ok) {
-      volatile const int* bd = b.bounds[lane];
+      volatile const int* bd = b.bounds[lane] + bounds_off;
       lo = bd[b.rank];
       const int hi = bd[b.rank + 1];
       n = hi - lo;

@@ -130,6 +130,10 @@ class DlrmPipeline:
     def embed_prefetch(self) -> None:
         """Hook called before the bottom MLP (multi-GPU variants start their exchange here)."""
 
+    def embed_prefetch_next(self) -> None:
+        """Hook of the pipelined form, called on the second stream after the bottom MLP: work of
+        the NEXT step that may run under this step's pooling (row sharding: its split)."""
+
     def embed(self) -> None:
         self.plan.run()
 
@@ -141,12 +145,13 @@ class DlrmPipeline:
         return bits
 
     # ------------------------------------------------------------------ one step
-    def _sparse_part(self, names) -> None:
+    def _sparse_part(self, names, lookahead: bool = False) -> None:
         """Bottom MLP (second stream) beside the embedding pooling; z is complete afterwards."""
         B, F, D = self.batch, self.F, self.dim
         x = self.dense
         nb = len(self.bottom)
         main = torch.cuda.current_stream()
+        self.embed_prefetch()
         self.side_stream.wait_stream(main)  # this step's inputs, and the previous readers of z
         with torch.cuda.stream(self.side_stream):
             for i, (w, b) in enumerate(self.bottom):
@@ -156,7 +161,8 @@ class DlrmPipeline:
                                       activation=ACT_RELU, ldc=(F * D if last else None),
                                       math=self.math))
                 x = y
-        self.embed_prefetch()
+            if lookahead:
+                self.embed_prefetch_next()
         self.embed()
         main.wait_stream(self.side_stream)
 
@@ -194,7 +200,7 @@ class DlrmPipeline:
         main = torch.cuda.current_stream()
         main.wait_event(self._dense_done[buf])  # the step before last has finished with this set
         names = []
-        self._sparse_part(names)
+        self._sparse_part(names, lookahead=True)
         self.dense_stream.wait_stream(main)
         with torch.cuda.stream(self.dense_stream):
             self._dense_part(names)

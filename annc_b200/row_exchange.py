@@ -121,9 +121,6 @@ class RowExchange:
     def set_timeout_ms(self, ms: int) -> None:
         check(lib.annc_row_exchange_set_timeout_ms(self.h, C.c_int64(ms)))
 
-    def set_variant(self, v: int) -> None:
-        lib.annc_row_exchange_set_variant(self.h, C.c_int(v))
-
     def set_profiling(self, on: bool) -> None:
         check(lib.annc_row_exchange_set_profiling(self.h, C.c_int(int(on))))
 

@@ -149,18 +149,36 @@ class RowShardedBags:
         self.ncols = int(id_sets[0]["segs"][0].shape[1])
         self.launches_per_step = 12 + (1 if combiner == 1 else 0)
         self.exchange_bytes = 0  # measured: see exchange_stats()
-        self._begun = False
+        self._begun_set = None   # input set whose lists are published for the next run()
+        self._ahead_set = None   # input set published one step further ahead
 
     def prefetch(self, set_index: int) -> None:
+        """Splits and publishes input set `set_index` for the next run() unless that has been
+        done ahead of time."""
+        if self._begun_set is None:
+            self.ex.begin(self.inputs[set_index], self.ncols, 0)
+            self._begun_set = set_index
+
+    def prefetch_next(self, set_index: int) -> None:
+        """One step of lookahead: splits and publishes the input set of the step AFTER the one
+        whose run() comes next (whose prefetch has been issued), typically from a second stream,
+        so that the split of step i + 1 runs under the pooling of step i."""
+        assert self._begun_set is not None and self._ahead_set is None
         self.ex.begin(self.inputs[set_index], self.ncols, 0)
-        self._begun = True
+        self._ahead_set = set_index
 
     def run(self, set_index: int, out_ptr: int, out_stride: int, out_bf16: bool = False) -> None:
-        if not self._begun:
-            self.prefetch(set_index)
-        self._begun = False
+        if self._begun_set is not None and self._begun_set != set_index:
+            # a step was published for another input set: it has to be completed (the peers
+            # have seen it); its result is overwritten below
+            self.ex.pool()
+            self.ex.finish(out_ptr, out_stride, out_bf16)
+            self._begun_set, self._ahead_set = self._ahead_set, None
+            return self.run(set_index, out_ptr, out_stride, out_bf16)
+        self.prefetch(set_index)
         self.ex.pool()
         self.ex.finish(out_ptr, out_stride, out_bf16)
+        self._begun_set, self._ahead_set = self._ahead_set, None
 
     def exchange_stats(self) -> dict:
         """Last step: records pooled per source, parts received per owner, and the bytes that
@@ -471,6 +489,12 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             self.sets[self.cur]["prepass"].run(self.off_ws)
             self._works = [dist.all_gather_into_tensor(self.ids_g, self.ids_pad, async_op=True),
                            dist.all_gather_into_tensor(self.off_g, self.off_ws, async_op=True)]
+
+        def embed_prefetch_next(self) -> None:
+            """Lookahead for back-to-back steps on the same input set (row mode): the split of
+            the next step, issued on the stream the bottom MLP runs on."""
+            if mode == "row":
+                self.rowbags.prefetch_next(self.cur)
 
         def embed_error_bits(self) -> int:
             if mode == "replica":

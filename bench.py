@@ -168,6 +168,26 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons)}
 
 
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Restricts this process to the CPU cores NVML names as local to its GPU (intersected with
+    the cores it may use), before any pinned host buffer is allocated: with one process per GPU
+    the pinned step inputs then sit on the GPU's own NUMA node and the host-to-device copies of
+    eight ranks do not all cross one socket.  Returns the number of cores kept, or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        local = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        keep = local & os.sched_getaffinity(0)
+        if keep and keep != os.sched_getaffinity(0):
+            os.sched_setaffinity(0, keep)
+        return len(keep) if keep else None
+    except Exception:
+        return None
+
+
 def physical_gpu_index(local_rank: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -349,6 +369,7 @@ def run_gpu(args):
         raise SystemExit("bench.py: no CUDA device (annc_b200 has no CPU fallback)")
     torch.cuda.set_device(local_rank)
     devi = torch.device("cuda", local_rank)
+    numa_cores = bind_to_gpu_numa_node(physical_gpu_index(local_rank)) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=devi)
 
@@ -431,9 +452,19 @@ def run_gpu(args):
              for _ in range(args.steps)]
     it = iter(pairs)
 
-    # Back-to-back batches: the dense part of a step (interaction + top MLP) runs on a second
-    # stream under the next step's embedding part (DlrmPipeline.forward_pipelined).
-    step_fn = getattr(pipe, "forward_pipelined", pipe.forward)
+    # Back-to-back batches may be issued in two orders: one step after the other (forward), or
+    # with the dense part of a step (interaction + top MLP) on a second stream under the next
+    # step's embedding part and, under row sharding, the split of the next step under this
+    # step's pooling (DlrmPipeline.forward_pipelined).  Which one is faster depends on how much
+    # of the GPU the embedding part leaves free; five steps of each decide, the same on all ranks.
+    step_fn = pipe.forward
+    if hasattr(pipe, "forward_pipelined"):
+        for _ in range(3):
+            pipe.forward_pipelined()
+        t_pipe = timed(pipe.forward_pipelined, 5)
+        t_plain = timed(pipe.forward, 5)
+        if t_pipe < t_plain:
+            step_fn = pipe.forward_pipelined
 
     def step_with_hooks():
         a, b = next(it)
@@ -443,6 +474,7 @@ def run_gpu(args):
     hooks = world == 1 and not recsys
     for _ in range(3):
         step_fn()
+    torch.cuda.synchronize()
     ms_total = timed(step_with_hooks if hooks else step_fn, args.steps)
     lib.annc_embed_bag_set_timing_events(None, None)
     bag_ms = []
@@ -557,7 +589,8 @@ def run_gpu(args):
                         "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                         # the end-to-end step is bound by the host-to-device copy of the ids and
                         # index matrices (the operands' own format): GB/s this rank's copies reach
-                        "h2d_gbs": pipe.h2d_bytes / (ms_e2e / 1e3) / 1e9},
+                        "h2d_gbs": pipe.h2d_bytes / (ms_e2e / 1e3) / 1e9,
+                        "host_cores_local_to_gpu": numa_cores},
                 "ms_per_step_unpipelined": ms_alone,
                 "pipelining": "the timed steps are issued back to back; the interaction and top MLP of "
                               "step i run on a second stream under the embedding part of step i + 1 "
@@ -581,12 +614,11 @@ def run_gpu(args):
             if mode == "row_k0" and args.hot_rows == 0:
                 continue
             p2 = build(mode)
-            f2 = getattr(p2, "forward_pipelined", p2.forward)
             for _ in range(3):
-                f2()
+                p2.forward()
             torch.cuda.synchronize()
             assert p2.embed_error_bits() == 0
-            ms2 = timed(f2, args.steps) / args.steps
+            ms2 = min(timed(p2.forward, args.steps), timed(p2.forward_pipelined, args.steps)) / args.steps
             rec = {"value": args.batch * world / (ms2 / 1e3), "unit": UNIT, "ms_per_step": ms2,
                    "parallelism": parallelism_label(args, world, mode)}
             rb = getattr(p2, "rowbags", None)

@@ -32,11 +32,12 @@ def _oracle_pooled(w, rows, combiner):
 class Emulated:
     """`world` ranks of one exchange on the current device.  works[r] is rank r's batch."""
 
-    def __init__(self, world, rows, dim, batch, works, hot_k, combiner, tables_np):
+    def __init__(self, world, rows, dim, batch, works, hot_k, combiner, tables_np, also=()):
         self.world, self.T, self.B, self.D = world, len(rows), batch, dim
         self.keep = []
-        nnz_max = max(int(sum(b.raw_ids.shape[0] for b in w.bags)) for w in works)
-        per_table = max(int(b.raw_ids.shape[0]) for w in works for b in w.bags)
+        sized = list(works) + list(also)  # every batch the exchange will be given
+        nnz_max = max(int(sum(b.raw_ids.shape[0] for b in w.bags)) for w in sized)
+        per_table = max(int(b.raw_ids.shape[0]) for w in sized for b in w.bags)
         hot_rows = [works[0].bags[t].popular_rows(hot_k[t], rows[t]) for t in range(self.T)]
         self.hot_rows = hot_rows
         cfgs = []
@@ -121,6 +122,56 @@ def test_emulated_ranks_match_oracle(world, combiner, hot, dim):
         for g in range(world):
             want_parts[g] += int(np.unique(bag.slice_input[owner == g, 0]).shape[0])
     assert parts == want_parts
+    em.close()
+
+
+def test_one_step_of_lookahead():
+    """begin() of step i + 1 before pool() and finish() of step i (the split of the next batch
+    runs under the pooling of this one): lists, bounds, masks and receive slabs alternate
+    between two sets, so every step must still match the oracle although its successor's lists
+    were already published.  Two different batches alternate; mean pooling exercises the bag
+    offsets too."""
+    rows = [3000, 41, 20_000]
+    B, D, world, T = 256, 64, 4, 3
+    batches = [[synth.embedding_workload(8, rows, D, B, 30, 1.05, input_seed=500 + 10 * v + r) for r in range(world)]
+               for v in range(2)]
+    em = Emulated(world, rows, D, B, batches[0], [50, 0, 500], 1, batches[0][0].tables, also=batches[1])
+    inputs = [em.inputs]
+    ids2 = [[_dev(b.raw_ids) for b in w.bags] for w in batches[1]]
+    segs2 = [[_dev(b.slice_input) for b in w.bags] for w in batches[1]]
+    inputs.append([rx.StepInputs([i.data_ptr() for i in ids], [s.data_ptr() for s in segs],
+                                 [int(i.shape[0]) for i in ids]) for ids, segs in zip(ids2, segs2)])
+    want = [[_oracle_pooled(batches[v][r], rows, 1) for r in range(world)] for v in range(2)]
+    outs = [torch.zeros((B, T, D), device="cuda") for _ in range(world)]
+    steps = 5
+    for r in range(world):
+        em.ex[r].begin(inputs[0][r])
+    for k in range(steps):
+        if k + 1 < steps:
+            for r in range(world):
+                em.ex[r].begin(inputs[(k + 1) % 2][r])
+        for r in range(world):
+            em.ex[r].pool()
+        for r in range(world):
+            em.ex[r].finish(outs[r].data_ptr(), T * D)
+        for r in range(world):
+            assert em.ex[r].error_bits() == 0
+            got = outs[r].cpu().numpy()
+            for t in range(T):
+                w = want[k % 2][r][t]
+                assert float(np.abs(got[:, t, :] - w).max()) / max(float(np.abs(w).max()), 1e-30) <= 1e-5, (k, r, t)
+    # a third begin before the oldest step has finished is refused
+    for r in range(world):
+        em.ex[r].begin(inputs[0][r])
+        em.ex[r].begin(inputs[1][r])
+    with pytest.raises(Exception) as e:
+        em.ex[0].begin(inputs[0][0])
+    assert "one step ahead" in str(e.value)
+    for _ in range(2):
+        for r in range(world):
+            em.ex[r].pool()
+        for r in range(world):
+            em.ex[r].finish(outs[r].data_ptr(), T * D)
     em.close()
 
 
