@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256)
 sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __restrict__ mask,
                            int parts, long long part_stride, long long rows, int slots,
                            int slot_w4, const int* __restrict__ mean_off, float* __restrict__ out,
-                           long long out_stride, int out_bf16) {
+                           long long out_stride, int out_bf16, int slot_major) {
   const long long width4 = (long long)slots * slot_w4;
   const long long total = rows * width4;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -268,7 +268,9 @@ sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __rest
     const int c4 = (int)(e - r * width4);
     const int slot = c4 / slot_w4;
     unsigned m = __ldg(mask + (long long)slot * rows + r);
-    const float* s0 = src + (r * width4 + c4) * 4;
+    // a part holds [rows, slots, slot_width], or [slots, rows, slot_width] when slot_major
+    const float* s0 = src + (slot_major ? ((long long)slot * rows + r) * slot_w4 + (c4 - slot * slot_w4)
+                                        : r * width4 + c4) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     bool first = true;
     while (m) {
@@ -440,10 +442,10 @@ int annc_sum_partials_dev(const float* src, int parts, int64_t part_stride, int6
   return ANNC_OK;
 }
 
-int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
+static int sum_partials_masked(const float* src, const uint32_t* mask, int parts,
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
                                  const int32_t* mean_offsets, void* out, int64_t out_stride,
-                                 int out_bf16, void* stream) {
+                                 int out_bf16, void* stream, int slot_major) {
   ANNC_REQUIRE(src && out && mask && parts >= 1 && parts <= 32 && slots >= 1,
                ANNC_ERR_INVALID_ARGUMENT, "null or bad argument");
   ANNC_REQUIRE((slot_width & 3) == 0 && slot_width > 0 && (out_stride & 3) == 0 &&
@@ -455,9 +457,25 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
   if (g > 148 * 16) g = 148 * 16;
   sum_partials_masked_kernel<<<(unsigned)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       src, mask, parts, part_stride, rows, slots, (int)(slot_width / 4), mean_offsets,
-      static_cast<float*>(out), out_stride, out_bf16 ? 1 : 0);
+      static_cast<float*>(out), out_stride, out_bf16 ? 1 : 0, slot_major);
   ANNC_CUDA(cudaGetLastError());
   return ANNC_OK;
+}
+
+int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
+                                 int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
+                                 const int32_t* mean_offsets, void* out, int64_t out_stride,
+                                 int out_bf16, void* stream) {
+  return sum_partials_masked(src, mask, parts, part_stride, rows, slots, slot_width, mean_offsets, out,
+                             out_stride, out_bf16, stream, 0);
+}
+
+int annc_sum_partials_masked_slot_major_dev(const float* src, const uint32_t* mask, int parts,
+                                            int64_t part_stride, int64_t rows, int slots,
+                                            int64_t slot_width, const int32_t* mean_offsets, void* out,
+                                            int64_t out_stride, int out_bf16, void* stream) {
+  return sum_partials_masked(src, mask, parts, part_stride, rows, slots, slot_width, mean_offsets, out,
+                             out_stride, out_bf16, stream, 1);
 }
 
 int annc_synth_fill_rows_dev(float* table, int64_t local_rows, int64_t dim, uint64_t seed,

@@ -11,7 +11,7 @@
 #include "common.h"
 #include "row_exchange_kernels.cuh"
 
-extern "C" int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int parts,
+extern "C" int annc_sum_partials_masked_slot_major_dev(const float* src, const uint32_t* mask, int parts,
                                             int64_t part_stride, int64_t rows, int slots,
                                             int64_t slot_width, const int32_t* mean_offsets, void* out,
                                             int64_t out_stride, int out_bf16, void* stream);
@@ -30,6 +30,7 @@ static size_t up256(size_t n) { return (n + 255) & ~size_t(255); }
 // parts of step i, so consecutive steps alternate between the two sets.
 struct Layout {
   size_t flags, bounds, records[2], recv[2], total;
+  size_t rec_bytes;    // one source's region of a record buffer
   size_t slab_floats;
 };
 constexpr int kFlagWordsA = 0;    // barrier "lists published"
@@ -41,11 +42,12 @@ static Layout layout_of(int world, int num_tables, int64_t batch, int64_t dim, i
   l.flags = 0;
   l.bounds = 256;
   const size_t rec = up256((size_t)std::max<int64_t>(max_lookups, 1) * sizeof(int2));
+  l.rec_bytes = rec;
   l.records[0] = 512;
-  l.records[1] = l.records[0] + rec;
+  l.records[1] = l.records[0] + (size_t)world * rec;  // one region per source
   l.slab_floats = (size_t)batch * (size_t)num_tables * (size_t)dim;
   const size_t slabs = up256((size_t)world * l.slab_floats * sizeof(float));
-  l.recv[0] = l.records[1] + rec;
+  l.recv[0] = l.records[1] + (size_t)world * rec;
   l.recv[1] = l.recv[0] + slabs;
   l.total = l.recv[1] + slabs;
   return l;
@@ -364,9 +366,10 @@ int annc_row_exchange_begin(annc_row_exchange* ex, const annc_bag_table* inputs,
   dim3 grid((unsigned)x->blocks_x, (unsigned)x->T);
   classify_kernel<<<grid, kClassifyThreads, 0, s>>>(p, x->owner, x->local, x->pos, x->err);
   exclusive_scan_inplace(x->pos, x->pos_n, x->scan_tiles, s);
-  scatter_kernel<<<grid, kClassifyThreads, 0, s>>>(p, x->owner, x->local, x->pos,
-                                                   reinterpret_cast<int2*>(mine + x->lay.records[buf]),
-                                                   x->mask[buf], x->err);
+  RecordDest dst;
+  for (int g = 0; g < x->world; ++g)
+    dst.list[g] = reinterpret_cast<int2*>(x->peer[g] + x->lay.records[buf] + (size_t)x->rank * x->lay.rec_bytes);
+  scatter_kernel<<<grid, kClassifyThreads, 0, s>>>(p, x->owner, x->local, x->pos, dst, x->mask[buf], x->err);
   if (prof) cudaEventRecord(x->ev[1], s);
   x->begun += 1;
   arrive_kernel<<<1, 32, 0, s>>>(x->bar, kFlagWordsA, (int)x->begun, x->pos, (long long)x->T * x->blocks_x,
@@ -387,7 +390,7 @@ int annc_row_exchange_pool(annc_row_exchange* ex, void* stream) {
                                buf * kBoundsInts, (int)x->max_lookups, x->err);
   if (prof) cudaEventRecord(x->ev[2], s);
   for (int q = 0; q < x->world; ++q) {
-    x->pool.list[q] = reinterpret_cast<const int2*>(x->peer[q] + x->lay.records[buf]);
+    x->pool.list[q] = reinterpret_cast<const int2*>(x->peer[x->rank] + x->lay.records[buf] + (size_t)q * x->lay.rec_bytes);
     x->pool.out[q] = reinterpret_cast<float*>(x->peer[q] + x->lay.recv[buf]) + (size_t)x->rank * x->lay.slab_floats;
   }
   ANNC_TRY(run_pool(*x, s));
@@ -413,7 +416,7 @@ int annc_row_exchange_finish(annc_row_exchange* ex, void* out, int64_t out_strid
                                 ? reinterpret_cast<const int32_t*>(static_cast<char*>(x->offsets_ws[buf]) + 512)  // header of the bag workspace
                                 : nullptr;
   x->finished += 1;
-  ANNC_TRY(annc_sum_partials_masked_dev(recv, x->mask[buf], x->world, (int64_t)x->lay.slab_floats, x->batch,
+  ANNC_TRY(annc_sum_partials_masked_slot_major_dev(recv, x->mask[buf], x->world, (int64_t)x->lay.slab_floats, x->batch,
                                         x->T, x->dim, mean_off, out, out_stride, out_bf16, s));
   if (prof) {
     cudaEventRecord(x->ev[5], s);

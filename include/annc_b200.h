@@ -315,6 +315,12 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
                                  int64_t part_stride, int64_t rows, int slots, int64_t slot_width,
                                  const int32_t* mean_offsets, void* out, int64_t out_stride,
                                  int out_bf16, void* stream);
+/* The same with every part laid out f32[slots, rows, slot_width] (the receive slabs of
+ * annc_row_exchange_*: a part's place follows its key = slot * rows + r). */
+int annc_sum_partials_masked_slot_major_dev(const float* src, const uint32_t* mask, int parts,
+                                            int64_t part_stride, int64_t rows, int slots,
+                                            int64_t slot_width, const int32_t* mean_offsets, void* out,
+                                            int64_t out_stride, int out_bf16, void* stream);
 
 /* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
  * reduce step after the all-to-all of partial sums).  src part p starts at
@@ -353,11 +359,13 @@ int annc_peer_buffer_destroy(void* dev_ptr);
  * of every table after the hash-bucket modulo.  The reference has no multi-device code: this
  * object has no counterpart there beyond that rule.  Per step each rank
  *   begin   splits the lookups of its own batch by owner rank into one record list per owner
- *           (record = local row + bag), in lookup order, and publishes the lists;
- *   pool    reads the lists meant for it from every rank through peer-mapped pointers, pools
- *           them lookup by lookup and stores every finished partial sum straight into the
- *           receive slab of the rank that owns the sample (pooling and exchange in one kernel,
- *           ordinary 16-byte stores over NVLink, no multicast, no NCCL call);
+ *           (record = local row + bag), in lookup order, written straight into the owner's
+ *           memory, and publishes their lengths;
+ *   pool    pools the lists it received from every rank lookup by lookup and stores every
+ *           finished partial sum straight into the receive slab of the rank that owns the
+ *           sample (pooling and exchange in one kernel, ordinary 16-byte stores over NVLink,
+ *           no multicast, no NCCL call); a slab is laid out by bag key (table, then sample), so
+ *           the stores in flight stay inside a few pages of each peer;
  *   finish  adds the parts of its own batch in rank order (deterministic; within 1e-5 relative
  *           of the unsharded sum) and applies 1/len for the mean combiner.
  * Ranks are ordered by flags in peer memory; every wait is bounded (2 s by default, then the
