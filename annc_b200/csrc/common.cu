@@ -10,10 +10,12 @@
 #include "common.h"
 
 #include <atomic>
+#include <condition_variable>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <thread>
 #include <unordered_map>
 
 namespace annc {
@@ -65,6 +67,148 @@ thread_local cudaStream_t g_last_stream[kMaxDevices] = {nullptr};
 thread_local cudaEvent_t g_last_event[kMaxDevices] = {nullptr};
 thread_local bool g_unsynced[kMaxDevices] = {false};
 
+// ---- staged copies between pageable host memory and the device.
+// A large operand moves through a pinned two-half bounce buffer of the calling thread: while
+// the DMA of one half runs, the next chunk is copied between the caller's (pageable) buffer and
+// the other half, by the caller and three helper threads (a single thread copies at about a
+// fifth of what the link takes).  Small operands take the driver's own staging.
+constexpr size_t kChunk = size_t(8) << 20;
+
+class CopyPool {
+ public:
+  static CopyPool& get() {
+    static CopyPool* p = new CopyPool();  // lives for the process: helpers never outlive it
+    return *p;
+  }
+  // memcpy(dst, src, n) split over the helpers and the caller
+  void copy(char* dst, const char* src, size_t n) {
+    constexpr int kParts = kHelpers + 1;
+    if (n < (size_t(1) << 20)) {
+      memcpy(dst, src, n);
+      return;
+    }
+    std::lock_guard<std::mutex> one_at_a_time(caller_mu_);
+    const size_t part = ((n / kParts) + 63) & ~size_t(63);
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      for (int i = 0; i < kHelpers; ++i) {
+        const size_t off = (size_t)(i + 1) * part;
+        job_[i] = {dst + off, src + off, off < n ? (off + part < n && i + 1 < kHelpers ? part : n - off) : 0};
+      }
+      pending_ = kHelpers;
+      ++generation_;
+    }
+    cv_.notify_all();
+    memcpy(dst, src, part < n ? part : n);
+    std::unique_lock<std::mutex> lk(mu_);
+    done_cv_.wait(lk, [&] { return pending_ == 0; });
+  }
+
+ private:
+  static constexpr int kHelpers = 3;
+  struct Job {
+    char* dst;
+    const char* src;
+    size_t n;
+  };
+  CopyPool() {
+    for (int i = 0; i < kHelpers; ++i) std::thread([this, i] { work(i); }).detach();
+  }
+  void work(int i) {
+    unsigned long long seen = 0;
+    for (;;) {
+      Job j;
+      {
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return generation_ != seen; });
+        seen = generation_;
+        j = job_[i];
+      }
+      if (j.n) memcpy(j.dst, j.src, j.n);
+      {
+        std::lock_guard<std::mutex> lk(mu_);
+        --pending_;
+      }
+      done_cv_.notify_all();
+    }
+  }
+  std::mutex mu_, caller_mu_;
+  std::condition_variable cv_, done_cv_;
+  Job job_[kHelpers] = {};
+  int pending_ = 0;
+  unsigned long long generation_ = 0;
+};
+
+struct Bounce {
+  char* base = nullptr;
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  bool tried = false;
+};
+thread_local Bounce g_bounce;
+
+bool bounce_ready() {
+  Bounce& b = g_bounce;
+  if (b.base) return true;
+  if (b.tried) return false;
+  b.tried = true;
+  if (cudaHostAlloc(reinterpret_cast<void**>(&b.base), 2 * kChunk, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    b.base = nullptr;
+    return false;
+  }
+  cudaEventCreateWithFlags(&b.ev[0], cudaEventDisableTiming);
+  cudaEventCreateWithFlags(&b.ev[1], cudaEventDisableTiming);
+  return true;
+}
+
+cudaError_t staged_h2d(void* dev, const void* host, size_t bytes, cudaStream_t s) {
+  if (bytes < kChunk / 4 || !bounce_ready())
+    return cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, s);
+  Bounce& b = g_bounce;
+  size_t i = 0;
+  for (size_t off = 0; off < bytes; off += kChunk, ++i) {
+    const int h = (int)(i & 1);
+    const size_t n = bytes - off < kChunk ? bytes - off : kChunk;
+    cudaEventSynchronize(b.ev[h]);  // the DMA that last read this half has finished
+    CopyPool::get().copy(b.base + h * kChunk, static_cast<const char*>(host) + off, n);
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(dev) + off, b.base + h * kChunk, n,
+                                    cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return e;
+    cudaEventRecord(b.ev[h], s);
+  }
+  return cudaSuccess;
+}
+
+// Returns with the host buffer complete (waits for the stream up to its last chunk).
+cudaError_t staged_d2h(void* host, const void* dev, size_t bytes, cudaStream_t s) {
+  if (bytes < kChunk / 4 || !bounce_ready())
+    return cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, s);
+  Bounce& b = g_bounce;
+  size_t i = 0, prev_off = 0, prev_n = 0;
+  for (size_t off = 0; off < bytes; off += kChunk, ++i) {
+    const int h = (int)(i & 1);
+    const size_t n = bytes - off < kChunk ? bytes - off : kChunk;
+    cudaEventSynchronize(b.ev[h]);  // an earlier upload may still read this half
+    cudaError_t e = cudaMemcpyAsync(b.base + h * kChunk, static_cast<const char*>(dev) + off, n,
+                                    cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return e;
+    cudaEventRecord(b.ev[h], s);
+    if (i > 0) {  // the previous chunk has landed in the other half: move it out under this DMA
+      const int ph = (int)((i - 1) & 1);
+      e = cudaEventSynchronize(b.ev[ph]);
+      if (e != cudaSuccess) return e;
+      CopyPool::get().copy(static_cast<char*>(host) + prev_off, b.base + ph * kChunk, prev_n);
+    }
+    prev_off = off;
+    prev_n = n;
+  }
+  const int lh = (int)((i - 1) & 1);
+  cudaError_t e = cudaEventSynchronize(b.ev[lh]);
+  if (e != cudaSuccess) return e;
+  CopyPool::get().copy(static_cast<char*>(host) + prev_off, b.base + lh * kChunk, prev_n);
+  return cudaSuccess;
+}
+
 // ---- mirrors
 struct Key {
   const void* host;
@@ -86,6 +230,7 @@ struct Mirror {
   bool valid = false;            // the mirror holds those contents
   bool pinned = false;           // registered with annc_register_constant: never evicted, never re-checked
   unsigned long long tick = 0;
+  int users = 0;                 // calls copying into the mirror right now: not to be evicted
   cudaEvent_t ready = nullptr;   // after the last write of the mirror
   cudaEvent_t used = nullptr;    // after the last read of the mirror
   std::unordered_map<int, std::pair<void*, size_t>> derived;  // re-laid forms of a constant, by tag
@@ -149,7 +294,7 @@ void make_room(size_t need, const Key* keep) {
   while (g_mirror_bytes + need > g_mirror_cap && !g_mirrors.empty()) {
     auto victim = g_mirrors.end();
     for (auto it = g_mirrors.begin(); it != g_mirrors.end(); ++it) {
-      if (it->second.pinned || (keep && it->first == *keep)) continue;
+      if (it->second.pinned || it->second.users > 0 || (keep && it->first == *keep)) continue;
       if (victim == g_mirrors.end() || it->second.tick < victim->second.tick) victim = it;
     }
     if (victim == g_mirrors.end()) break;
@@ -232,75 +377,86 @@ bool Call::is_device(const void* p) {
 void* Call::mirror(const void* p, size_t bytes, bool upload, bool role_constant, bool is_output) {
   if (bytes == 0) bytes = 1;
   const Key key{p, bytes, device_};
-  std::lock_guard<std::mutex> lk(g_mu);
-  auto it = g_mirrors.find(key);
-  if (it == g_mirrors.end()) {
-    make_room(bytes, nullptr);
-    Mirror m;
-    cudaError_t e = cudaMalloc(&m.dev, bytes);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      make_room(g_mirror_cap, nullptr);  // drop everything evictable and try once more
-      e = cudaMalloc(&m.dev, bytes);
-    }
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      status_ = fail(ANNC_ERR_CUDA, "device allocation of %zu bytes for a host operand failed", bytes);
-      return nullptr;
-    }
-    m.bytes = bytes;
-    cudaEventCreateWithFlags(&m.ready, cudaEventDisableTiming);
-    cudaEventCreateWithFlags(&m.used, cudaEventDisableTiming);
-    g_mirror_bytes += bytes;
-    it = g_mirrors.emplace(key, m).first;
-  }
-  Mirror& m = it->second;
-  m.tick = ++g_tick;
-  const bool may_reuse = !m.pinned && (g_mode == 2 || (g_mode == 1 && role_constant));
-  if (upload) {
-    bool need = true;
-    unsigned long long fp = 0;
-    if (m.pinned && m.valid) {
-      need = false;
-    } else if (may_reuse) {
-      fp = fingerprint(p, bytes, role_constant ? 512 : 16384);
-      need = !(m.valid && m.print == fp);
-    }
-    if (need) {
-      // writers wait for the readers and the writer before them
-      cudaStreamWaitEvent(stream_, m.used, 0);
-      cudaStreamWaitEvent(stream_, m.ready, 0);
-      cudaError_t e = cudaMemcpyAsync(m.dev, p, bytes, cudaMemcpyHostToDevice, stream_);
+  Mirror* mp = nullptr;
+  bool need = false, may_reuse = false;
+  unsigned long long fp = 0;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_mirrors.find(key);
+    if (it == g_mirrors.end()) {
+      make_room(bytes, nullptr);
+      Mirror m;
+      cudaError_t e = cudaMalloc(&m.dev, bytes);
       if (e != cudaSuccess) {
-        status_ = cuda_fail(e, "cudaMemcpyAsync(H2D)");
+        cudaGetLastError();
+        make_room(g_mirror_cap, nullptr);  // drop everything evictable and try once more
+        e = cudaMalloc(&m.dev, bytes);
+      }
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        status_ = fail(ANNC_ERR_CUDA, "device allocation of %zu bytes for a host operand failed", bytes);
         return nullptr;
       }
-      cudaEventRecord(m.ready, stream_);
-      g_staged_h2d += bytes;
-      m.valid = may_reuse;
-      m.print = fp;
-      for (auto& d : m.derived) {  // re-laid forms are stale now
+      m.bytes = bytes;
+      cudaEventCreateWithFlags(&m.ready, cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&m.used, cudaEventDisableTiming);
+      g_mirror_bytes += bytes;
+      it = g_mirrors.emplace(key, m).first;
+    }
+    Mirror& m = it->second;
+    mp = &m;  // stays where it is: entries are only erased by eviction, which skips `users`
+    m.tick = ++g_tick;
+    may_reuse = !m.pinned && (g_mode == 2 || (g_mode == 1 && role_constant));
+    if (upload) {
+      need = true;
+      if (m.pinned && m.valid) {
+        need = false;
+      } else if (may_reuse) {
+        fp = fingerprint(p, bytes, role_constant ? 512 : 16384);
+        need = !(m.valid && m.print == fp);
+      }
+      if (need) {
+        ++m.users;
+        // writers wait for the readers and the writer before them
+        cudaStreamWaitEvent(stream_, m.used, 0);
+        cudaStreamWaitEvent(stream_, m.ready, 0);
+        m.valid = false;
+      } else {
+        cudaStreamWaitEvent(stream_, m.ready, 0);
+        g_skipped_h2d += bytes;
+      }
+      touched_.push_back({key.host, key.bytes, key.device});
+    } else if (is_output) {
+      cudaStreamWaitEvent(stream_, m.used, 0);
+      cudaStreamWaitEvent(stream_, m.ready, 0);
+      m.valid = false;  // becomes valid again in finish(), once the host copy exists
+      for (auto& d : m.derived) {
         cudaFree(d.second.first);
         g_mirror_bytes -= d.second.second;
       }
       m.derived.clear();
-      staged_ = true;
-    } else {
-      cudaStreamWaitEvent(stream_, m.ready, 0);
-      g_skipped_h2d += bytes;
     }
-    touched_.push_back({key.host, key.bytes, key.device});
-  } else if (is_output) {
-    cudaStreamWaitEvent(stream_, m.used, 0);
-    cudaStreamWaitEvent(stream_, m.ready, 0);
-    m.valid = false;  // becomes valid again in finish(), once the host copy exists
-    for (auto& d : m.derived) {
+  }
+  if (need) {  // the copy itself runs outside the lock: other threads' calls go on
+    const cudaError_t e = staged_h2d(mp->dev, p, bytes, stream_);
+    std::lock_guard<std::mutex> lk(g_mu);
+    --mp->users;
+    if (e != cudaSuccess) {
+      status_ = cuda_fail(e, "host-to-device copy");
+      return nullptr;
+    }
+    cudaEventRecord(mp->ready, stream_);
+    g_staged_h2d += bytes;
+    mp->valid = may_reuse;
+    mp->print = fp;
+    for (auto& d : mp->derived) {  // re-laid forms are stale now
       cudaFree(d.second.first);
       g_mirror_bytes -= d.second.second;
     }
-    m.derived.clear();
+    mp->derived.clear();
+    staged_ = true;
   }
-  return m.dev;
+  return mp->dev;
 }
 
 const void* Call::in(const void* p, size_t bytes) { return in_role(p, bytes, false); }
@@ -378,8 +534,8 @@ int Call::finish() {
   if (status_ != ANNC_OK) return status_;
   for (auto& o : pending_) {
     if (!o.bytes) continue;
-    cudaError_t e = cudaMemcpyAsync(o.host, o.dev, o.bytes, cudaMemcpyDeviceToHost, stream_);
-    if (e != cudaSuccess) return status_ = cuda_fail(e, "cudaMemcpyAsync(D2H)");
+    cudaError_t e = staged_d2h(o.host, o.dev, o.bytes, stream_);
+    if (e != cudaSuccess) return status_ = cuda_fail(e, "device-to-host copy");
     g_staged_d2h += o.bytes;
   }
   {  // this call's reads and writes of the mirrors end here on its stream

@@ -273,19 +273,30 @@ sum_partials_masked_kernel(const float* __restrict__ src, const unsigned* __rest
                                         : r * width4 + c4) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     bool first = true;
+    if (parts < 32) m &= (1u << parts) - 1u;
     while (m) {
-      const int p = __ffs(m) - 1;
-      m &= m - 1;
-      if (p >= parts) break;
-      const float4 v = __ldg(reinterpret_cast<const float4*>(s0 + p * part_stride));
-      if (first) {
-        acc = v;
-        first = false;
-      } else {
-        acc.x = __fadd_rn(acc.x, v.x);
-        acc.y = __fadd_rn(acc.y, v.y);
-        acc.z = __fadd_rn(acc.z, v.z);
-        acc.w = __fadd_rn(acc.w, v.w);
+      // up to four parts loaded before the first add (the loop is bound by load latency), added
+      // in ascending part order all the same
+      int p[4];
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        p[k] = m ? __ffs(m) - 1 : -1;
+        m &= m - 1;  // 0 stays 0
+        if (p[k] >= 0) v[k] = __ldg(reinterpret_cast<const float4*>(s0 + p[k] * part_stride));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (p[k] < 0) break;
+        if (first) {
+          acc = v[k];
+          first = false;
+        } else {
+          acc.x = __fadd_rn(acc.x, v[k].x);
+          acc.y = __fadd_rn(acc.y, v[k].y);
+          acc.z = __fadd_rn(acc.z, v[k].z);
+          acc.w = __fadd_rn(acc.w, v[k].w);
+        }
       }
     }
     if (mean_off) {  // mean pooling: the sum times 1/len(bag), like the reference's second pass

@@ -79,6 +79,7 @@ struct Exchange {
   long long pos_n = 0;
   long long begun = 0, pooled = 0, finished = 0;  // steps that passed each phase
   unsigned long long limit_ns = 2000000000ull;
+  int pool_ctas_per_sm = 0;  // 0: as many as fit; -n: n fewer
   bool profiling = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   bool ev_valid = false;
@@ -108,7 +109,9 @@ static void launch_pool(const Exchange& x, cudaStream_t s) {
   }
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, slot);
-  pool_kernel<LANES, VPL, TILES, INFLIGHT, MINB><<<(unsigned)(sms * per_sm[slot]), 256, 0, s>>>(x.pool, x.err);
+  const int ctas = x.pool_ctas_per_sm > 0 ? std::min(x.pool_ctas_per_sm, per_sm[slot])
+                                          : std::max(1, per_sm[slot] + x.pool_ctas_per_sm);
+  pool_kernel<LANES, VPL, TILES, INFLIGHT, MINB><<<(unsigned)(sms * ctas), 256, 0, s>>>(x.pool, x.err);
 }
 
 static int run_pool(const Exchange& x, cudaStream_t s) {
@@ -305,6 +308,13 @@ int annc_row_exchange_destroy(annc_row_exchange* ex) {
 int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms) {
   ANNC_REQUIRE(ex && ms >= 1, ANNC_ERR_INVALID_ARGUMENT, "row exchange: bad timeout");
   reinterpret_cast<Exchange*>(ex)->limit_ns = (unsigned long long)ms * 1000000ull;
+  return ANNC_OK;
+}
+
+int annc_row_exchange_set_pool_ctas_per_sm(annc_row_exchange* ex, int ctas_per_sm) {
+  auto* x = reinterpret_cast<Exchange*>(ex);
+  ANNC_REQUIRE(x, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null object");
+  x->pool_ctas_per_sm = ctas_per_sm;
   return ANNC_OK;
 }
 

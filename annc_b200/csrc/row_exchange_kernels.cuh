@@ -145,6 +145,9 @@ scatter_kernel(ClassifyParams p, const unsigned char* __restrict__ owner_in,
                RecordDest dst, unsigned* __restrict__ mask, int* __restrict__ err) {
   constexpr int kWarps = kClassifyThreads / 32;
   __shared__ int wcnt[kClassifyTiles * kWarps][kMaxWorld];
+  __shared__ int blk_base[kMaxWorld];       // the block's first place in every owner's list
+  __shared__ int seg_start[kMaxWorld + 1];  // where each owner's records start in `stage`
+  __shared__ int2 stage[kClassifyItems];    // the block's records, grouped by owner, in list order
   const int t = blockIdx.y;
   const ClassifyTable& T = p.t[t];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -191,18 +194,35 @@ scatter_kernel(ClassifyParams p, const unsigned char* __restrict__ owner_in,
   if (threadIdx.x < p.world) {  // exclusive prefix over (tile, warp) in lookup order
     // position inside the owner's list: the scan runs over all owners' counts
     const long long g0 = (long long)threadIdx.x * p.num_tables * p.blocks_x;
-    int run = pos[g0 + (long long)t * p.blocks_x + blockIdx.x] - pos[g0];
+    blk_base[threadIdx.x] = pos[g0 + (long long)t * p.blocks_x + blockIdx.x] - pos[g0];
+    int run = 0;  // place inside the block's records for this owner
     for (int e = 0; e < kClassifyTiles * kWarps; ++e) {
       const int c = wcnt[e][threadIdx.x];
       wcnt[e][threadIdx.x] = run;
       run += c;
     }
+    seg_start[threadIdx.x + 1] = run;  // count, turned into a prefix below
   }
   __syncthreads();
+  if (threadIdx.x == 0) {
+    seg_start[0] = 0;
+    for (int g = 0; g < p.world; ++g) seg_start[g + 1] += seg_start[g];
+  }
+  __syncthreads();
+  // The records are grouped by owner in shared memory first and leave the block as one run of
+  // consecutive 8-byte stores per owner: written one by one they were isolated 8-byte stores
+  // into seven peers' memory (a third of the split's time on eight GPUs).
 #pragma unroll
   for (int j = 0; j < kClassifyTiles; ++j) {
     if (owner[j] >= 0)
-      dst.list[owner[j]][wcnt[j * kWarps + warp][owner[j]] + rank_in_warp[j]] = make_int2(local[j], key[j]);
+      stage[seg_start[owner[j]] + wcnt[j * kWarps + warp][owner[j]] + rank_in_warp[j]] = make_int2(local[j], key[j]);
+  }
+  __syncthreads();
+  const int total = seg_start[p.world];
+  for (int i = threadIdx.x; i < total; i += kClassifyThreads) {
+    int g = 0;
+    while (i >= seg_start[g + 1]) ++g;
+    dst.list[g][blk_base[g] + (i - seg_start[g])] = stage[i];
   }
 }
 

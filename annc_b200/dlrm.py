@@ -13,8 +13,11 @@ forward() runs one step and leaves its result ordered on the current stream.
 forward_pipelined() is the throughput form for back-to-back batches: the embedding part of a
 step (gather-latency bound, tensor cores idle) runs on the current stream while the dense part
 of the previous step (interaction + top MLP, tensor-core work) runs on a second stream; two
-sets of intermediate buffers alternate.  Results are the same; sync_pipeline() orders the
-current stream after the last step.
+sets of intermediate buffers alternate.  Where the embedding part has a separate closing pass
+(row-sharded tables: second barrier + sum of the parts), forward_pipelined(split=True) moves
+that pass to the dense stream as well, so the current stream carries nothing but the pooling
+kernels, back to back (they are bound by their NVLink stores on four and more GPUs).  Results
+are the same; sync_pipeline() orders the current stream after the last step.
 """
 from __future__ import annotations
 
@@ -91,6 +94,11 @@ class DlrmPipeline:
         self._select(0)
         self.dense_stream = torch.cuda.Stream(device=device)
         self._dense_done = [torch.cuda.Event() for _ in range(2)]
+        self._sum_done = [torch.cuda.Event() for _ in range(2)]
+        self._bottom_done = [torch.cuda.Event() for _ in range(2)]
+        self._begin_done = torch.cuda.Event()
+        self._pooled = torch.cuda.Event()
+        self.split_finish = False  # embed() = embed_pool() + embed_finish(), the latter movable
         self._pstep = 0
         self.kernel_names: List[str] = []
         self.launches_per_step = 0
@@ -136,6 +144,13 @@ class DlrmPipeline:
 
     def embed(self) -> None:
         self.plan.run()
+
+    def embed_pool(self) -> None:
+        """embed() without its closing pass (pipelines with split_finish)."""
+        self.embed()
+
+    def embed_finish(self) -> None:
+        """The closing pass of embed(): completes z.  May run on another stream than embed_pool."""
 
     def embed_error_bits(self) -> int:
         bits = 0
@@ -190,10 +205,55 @@ class DlrmPipeline:
         self._dense_part(names)
         return self.out
 
-    def forward_pipelined(self) -> torch.Tensor:
+    def _forward_split(self) -> torch.Tensor:
+        """forward_pipelined with the closing pass of the embedding part on the dense stream.
+        Stream plan of step i (buffers i % 2):
+          current  pooling(i)                                   [needs split(i), issued in step i-1]
+          side     bottom MLP(i), then split(i+1)               [split(i+1) after sum(i-1): same buffers]
+          dense    sum(i), interaction(i), top MLP(i)           [after pooling(i) and bottom MLP(i)]"""
+        buf = self._pstep % 2
+        self._pstep += 1
+        self._select(buf)
+        main = torch.cuda.current_stream()
+        main.wait_event(self._dense_done[buf])  # the step before last has finished with this set
+        names = []
+        B, F, D = self.batch, self.F, self.dim
+        self.embed_prefetch()                   # first step only: nothing has been split ahead
+        self.side_stream.wait_stream(main)
+        with torch.cuda.stream(self.side_stream):
+            x = self.dense
+            nb = len(self.bottom)
+            for i, (w, b) in enumerate(self.bottom):
+                last = i == nb - 1
+                y = self.z if last else self.acts_b[i]
+                names.append(dev.gemm(x, w, y, m=B, n=w.shape[1], k=w.shape[0], bias=b,
+                                      activation=ACT_RELU, ldc=(F * D if last else None),
+                                      math=self.math))
+                x = y
+            self._bottom_done[buf].record(self.side_stream)
+            # the next step's split reuses the masks and lists of the step before this one
+            self.side_stream.wait_event(self._sum_done[1 - buf])
+            self.embed_prefetch_next()
+            self._begin_done.record(self.side_stream)
+        self.embed_pool()
+        self._pooled.record(main)
+        main.wait_event(self._begin_done)       # the next pooling starts after its split
+        self.dense_stream.wait_event(self._pooled)
+        self.dense_stream.wait_event(self._bottom_done[buf])
+        with torch.cuda.stream(self.dense_stream):
+            self.embed_finish()
+            self._sum_done[buf].record(self.dense_stream)
+            self._dense_part(names)
+            self._dense_done[buf].record(self.dense_stream)
+        return self.out
+
+    def forward_pipelined(self, split: bool = False) -> torch.Tensor:
         """One step of a back-to-back sequence: its dense part is queued on `dense_stream` and
         overlaps the next step's embedding part.  The returned tensor is valid after
-        sync_pipeline() (or a device synchronize)."""
+        sync_pipeline() (or a device synchronize).  split=True (pipelines with split_finish):
+        the closing pass of the embedding part runs on the dense stream too."""
+        if split and self.split_finish:
+            return self._forward_split()
         buf = self._pstep % 2
         self._pstep += 1
         self._select(buf)
@@ -209,7 +269,9 @@ class DlrmPipeline:
 
     def sync_pipeline(self) -> None:
         """Orders the current stream after every queued dense part."""
-        torch.cuda.current_stream().wait_stream(self.dense_stream)
+        main = torch.cuda.current_stream()
+        main.wait_stream(self.dense_stream)
+        main.wait_stream(self.side_stream)
 
     def _issue_copy(self, i: int) -> None:
         st = self.sets[i]

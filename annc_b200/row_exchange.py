@@ -41,6 +41,7 @@ lib.annc_row_exchange_check.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_in
 lib.annc_row_exchange_clear_errors.argtypes = [C.c_void_p, C.c_void_p]
 lib.annc_row_exchange_set_timeout_ms.argtypes = [C.c_void_p, C.c_int64]
 lib.annc_row_exchange_set_profiling.argtypes = [C.c_void_p, C.c_int]
+lib.annc_row_exchange_set_pool_ctas_per_sm.argtypes = [C.c_void_p, C.c_int]
 lib.annc_row_exchange_phase_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
 lib.annc_row_exchange_stats.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
 
@@ -120,6 +121,9 @@ class RowExchange:
 
     def set_timeout_ms(self, ms: int) -> None:
         check(lib.annc_row_exchange_set_timeout_ms(self.h, C.c_int64(ms)))
+
+    def set_pool_ctas_per_sm(self, n: int) -> None:
+        check(lib.annc_row_exchange_set_pool_ctas_per_sm(self.h, C.c_int(int(n))))
 
     def set_profiling(self, on: bool) -> None:
         check(lib.annc_row_exchange_set_profiling(self.h, C.c_int(int(on))))

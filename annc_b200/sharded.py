@@ -180,6 +180,19 @@ class RowShardedBags:
         self.ex.finish(out_ptr, out_stride, out_bf16)
         self._begun_set, self._ahead_set = self._ahead_set, None
 
+    def run_pool(self, set_index: int) -> None:
+        """First half of run(): pooling + exchange of input set `set_index` on the current stream."""
+        if self._begun_set is not None and self._begun_set != set_index:
+            raise ValueError("a step of another input set is published: complete it with run() first")
+        self.prefetch(set_index)
+        self.ex.pool()
+
+    def run_finish(self, out_ptr: int, out_stride: int, out_bf16: bool = False) -> None:
+        """Second half of run(): second barrier + sum of the parts, on the current stream (which
+        may be another stream than run_pool's, ordered after it by the caller)."""
+        self.ex.finish(out_ptr, out_stride, out_bf16)
+        self._begun_set, self._ahead_set = self._ahead_set, None
+
     def exchange_stats(self) -> dict:
         """Last step: records pooled per source, parts received per owner, and the bytes that
         crossed NVLink into and out of this rank (records read from peers, parts stored)."""
@@ -430,6 +443,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             self.peer = self.rowbags.peer
             self.embed_launches = self.rowbags.launches_per_step
             self.exchange_bytes = 0
+            self.split_finish = True  # forward_pipelined may run the sum of the parts on the dense stream
 
         def embed(self) -> None:
             plan = self.shard
@@ -472,6 +486,16 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                     dev.copy_rows(self.z.data_ptr() + (1 + first) * D * 4, F * D,
                                   self.back.data_ptr() + off * 4, tp * D, tp * D, B)
                 off += self.back_counts[p]
+
+        def embed_pool(self) -> None:
+            if mode == "row":
+                self.rowbags.run_pool(self.cur)
+            else:
+                self.embed()
+
+        def embed_finish(self) -> None:
+            if mode == "row":
+                self.rowbags.run_finish(self.z.data_ptr() + self.dim * 4, self.F * self.dim)
 
         def embed_prefetch(self) -> None:
             """Starts the exchange (row: split + publish; table: ids into peer-visible memory;

@@ -69,10 +69,10 @@ def parse_args():
     ap.add_argument("--hot-rows", type=int, default=65536,
                     help="row sharding: rows of each table's this many most popular ids are replicated "
                          "on every rank and pooled where the sample is (0 = pure row sharding)")
-    ap.add_argument("--extras", default="row_k0,table,replica",
+    ap.add_argument("--extras", default="row_k0,row_k262144,table,replica",
                     help="--gpus > 1: other partitionings timed after the headline and reported as "
-                         "labelled sub-records (comma list of row_k0, row_nccl, table, table_nccl, replica; "
-                         "empty = none)")
+                         "labelled sub-records (comma list of row_k0, row_k<K> = row sharding with K "
+                         "replicated rows per table, row_nccl, table, table_nccl, replica; empty = none)")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operator record at N=1")
     ap.add_argument("--no-abi", action="store_true", help="skip the host-buffer ABI leg at N=1")
     args = ap.parse_args()
@@ -91,11 +91,13 @@ def parallelism_label(args, world, mode=None):
                "partial sums stored into the sample owner's memory by the pooling kernel, flag barriers"
                % (world, world, hot),
         "row_k0": "dp%d MLP + row-sharded tables (owner = row %% %d), no replicated rows" % (world, world),
+        "row_kK": "dp%d MLP + row-sharded tables (owner = row %% %d) + rows of each table's %s most popular "
+                  "ids replicated" % (world, world, (mode or "")[5:]),
         "row_nccl": "dp%d MLP + row-sharded tables, all-gathered ids + NCCL all-to-all of partial sums" % world,
         "table": "dp%d MLP + whole tables per rank, pooled vectors stored into the sample owner's memory" % world,
         "table_nccl": "dp%d MLP + whole tables per rank, NCCL all-to-all of ids and pooled vectors" % world,
         "replica": "dp%d MLP + every table on every rank (no exchange)" % world,
-    }[mode]
+    }["row_kK" if mode.startswith("row_k") and mode != "row_k0" else mode]
 
 
 def workload_config(args, world):
@@ -383,12 +385,16 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, sync=None):
+        """Device time of `steps` calls, max over ranks.  `sync` orders the timing stream after
+        work the calls queued on other streams, so that all of it lies inside the timed region."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if sync is not None:
+            sync()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -434,8 +440,8 @@ def run_gpu(args):
             if world == 1:
                 return DlrmPipeline(model, devi, keep_host_inputs=True)
             from annc_b200.sharded import ShardedDlrmPipeline
-            if mode == "row_k0":
-                return ShardedDlrmPipeline(model, devi, "row", keep_host_inputs=True, hot_rows=0)
+            if mode.startswith("row_k"):
+                return ShardedDlrmPipeline(model, devi, "row", keep_host_inputs=True, hot_rows=int(mode[5:]))
             return ShardedDlrmPipeline(model, devi, mode, keep_host_inputs=True,
                                        hot_rows=args.hot_rows if mode == "row" else 0)
 
@@ -457,14 +463,32 @@ def run_gpu(args):
     # step's embedding part and, under row sharding, the split of the next step under this
     # step's pooling (DlrmPipeline.forward_pipelined).  Which one is faster depends on how much
     # of the GPU the embedding part leaves free; five steps of each decide, the same on all ranks.
-    step_fn = pipe.forward
+    # Under row sharding there is a third order (forward_pipelined(split=True)): the sum of the
+    # parts moves to the dense stream as well, so the pooling kernels, bound by their NVLink
+    # stores, follow one another on the main stream; optionally with one block per SM fewer
+    # in the pooling grid, which leaves room for the kernels of the other streams.
+    step_fn, issue_order, order_ms = pipe.forward, "none", {}
     if hasattr(pipe, "forward_pipelined"):
-        for _ in range(3):
-            pipe.forward_pipelined()
-        t_pipe = timed(pipe.forward_pipelined, 5)
-        t_plain = timed(pipe.forward, 5)
-        if t_pipe < t_plain:
-            step_fn = pipe.forward_pipelined
+        rowex = getattr(getattr(pipe, "rowbags", None), "ex", None)
+        cands = [("none", pipe.forward, 0), ("dense_part_under_next_embedding", pipe.forward_pipelined, 0)]
+        if getattr(pipe, "split_finish", False) and rowex is not None:
+            fs = lambda: pipe.forward_pipelined(split=True)
+            cands += [("sum_and_dense_part_under_next_pooling", fs, 0),
+                      ("sum_and_dense_part_under_next_pooling_grid_minus_1", fs, -1),
+                      ("sum_and_dense_part_under_next_pooling_grid_minus_2", fs, -2)]
+        best, order_ms = None, {}
+        for name, fn, ctas in cands:
+            if rowex is not None:
+                rowex.set_pool_ctas_per_sm(ctas)
+            for _ in range(3):
+                fn()
+            t = timed(fn, 5, pipe.sync_pipeline)
+            order_ms[name] = round(t / 5, 4)
+            if best is None or t < best[0]:
+                best = (t, name, fn, ctas)
+        _, issue_order, step_fn, ctas = best
+        if rowex is not None:
+            rowex.set_pool_ctas_per_sm(ctas)
 
     def step_with_hooks():
         a, b = next(it)
@@ -475,7 +499,7 @@ def run_gpu(args):
     for _ in range(3):
         step_fn()
     torch.cuda.synchronize()
-    ms_total = timed(step_with_hooks if hooks else step_fn, args.steps)
+    ms_total = timed(step_with_hooks if hooks else step_fn, args.steps, getattr(pipe, "sync_pipeline", None))
     lib.annc_embed_bag_set_timing_events(None, None)
     bag_ms = []
     for a, b in pairs:
@@ -592,10 +616,12 @@ def run_gpu(args):
                         "h2d_gbs": pipe.h2d_bytes / (ms_e2e / 1e3) / 1e9,
                         "host_cores_local_to_gpu": numa_cores},
                 "ms_per_step_unpipelined": ms_alone,
-                "pipelining": "the timed steps are issued back to back; the interaction and top MLP of "
-                              "step i run on a second stream under the embedding part of step i + 1 "
-                              "(two sets of intermediate buffers); ms_per_step_unpipelined is one step "
-                              "with nothing overlapping it" if step_fn is not pipe.forward else "none",
+                "pipelining": ("the timed steps are issued back to back in the order '%s' (chosen by five "
+                               "calibration steps of each order): work of neighbouring steps overlaps on "
+                               "second and third streams, two sets of intermediate buffers; "
+                               "ms_per_step_unpipelined is one step with nothing overlapping it" % issue_order)
+                              if issue_order != "none" else "none",
+                "issue_orders_ms_per_step": order_ms,
                 "gpu_launches": pipe.launches_per_step * args.steps,
                 "gemm_kernels": sorted(set(pipe.kernel_names)),
                 "roofline": roofline, "clocks": sampler.summary()}
@@ -611,14 +637,22 @@ def run_gpu(args):
     if world > 1 and not recsys and args.extras:
         extras = {}
         for mode in [m for m in args.extras.split(",") if m and m != args.shard]:
-            if mode == "row_k0" and args.hot_rows == 0:
+            if mode.startswith("row_k") and int(mode[5:]) == args.hot_rows:
                 continue
             p2 = build(mode)
             for _ in range(3):
                 p2.forward()
             torch.cuda.synchronize()
             assert p2.embed_error_bits() == 0
-            ms2 = min(timed(p2.forward, args.steps), timed(p2.forward_pipelined, args.steps)) / args.steps
+            ms2 = min(timed(p2.forward, args.steps),
+                      timed(p2.forward_pipelined, args.steps, p2.sync_pipeline)) / args.steps
+            if getattr(p2, "split_finish", False):
+                p2.rowbags.ex.set_pool_ctas_per_sm(-1)
+                split = lambda: p2.forward_pipelined(split=True)
+                for _ in range(3):
+                    split()
+                ms2 = min(ms2, timed(split, args.steps, p2.sync_pipeline) / args.steps)
+                p2.rowbags.ex.set_pool_ctas_per_sm(0)
             rec = {"value": args.batch * world / (ms2 / 1e3), "unit": UNIT, "ms_per_step": ms2,
                    "parallelism": parallelism_label(args, world, mode)}
             rb = getattr(p2, "rowbags", None)
@@ -626,6 +660,7 @@ def run_gpu(args):
                 st = rb.exchange_stats()
                 rec["remote_parts_per_bag"] = st["remote_parts_per_bag"]
                 rec["nvlink_bytes_per_gpu_per_step"] = st["nvlink_bytes"]
+                rec["hot_bytes_per_gpu"] = st["hot_bytes"]
             extras[mode] = rec
             close(p2)
             del p2

@@ -429,6 +429,12 @@ int annc_row_exchange_step(annc_row_exchange* ex, const annc_bag_table* inputs, 
 int annc_row_exchange_check(annc_row_exchange* ex, void* stream, int* error_bits);
 int annc_row_exchange_clear_errors(annc_row_exchange* ex, void* stream);
 int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms);
+/* Blocks of the pooling kernel per SM (a persistent grid; 0 = as many as fit, the default;
+ * -n = n fewer than fit).
+ * With several GPUs the kernel is bound by its NVLink stores, and one block per SM fewer leaves
+ * room for kernels of other streams (the next step's split, the previous step's sum and dense
+ * layers) to run under it. */
+int annc_row_exchange_set_pool_ctas_per_sm(annc_row_exchange* ex, int ctas_per_sm);
 /* With profiling on, every step records CUDA events between its phases; phase_ms returns the
  * last step's {split, first barrier, pool + exchange, second barrier, sum} in milliseconds. */
 int annc_row_exchange_set_profiling(annc_row_exchange* ex, int on);

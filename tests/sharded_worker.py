@@ -34,6 +34,22 @@ def main():
             again = pipe.forward().cpu().numpy()
             assert np.array_equal(again, got), "row-sharded steps differ from one step to the next"
     if mode in ("row", "row_hot"):
+        # the issue orders for back-to-back batches: dense part under the next embedding part,
+        # then also the sum of the parts on the dense stream (pooling kernels back to back on
+        # the main stream, with and without a block per SM left free); same predictions
+        for split, ctas in ((False, 0), (True, 0), (True, -1), (False, 0)):
+            pipe.rowbags.ex.set_pool_ctas_per_sm(ctas)
+            outs = []
+            for _ in range(5):
+                outs.append(pipe.forward_pipelined(split=split))
+            pipe.sync_pipeline()
+            torch.cuda.synchronize()
+            for o in outs[-2:]:  # the two buffer sets
+                assert np.array_equal(o.cpu().numpy(), got), f"pipelined steps (split={split}) differ"
+            assert pipe.embed_error_bits() == 0
+        pipe.rowbags.ex.set_pool_ctas_per_sm(0)
+        again = pipe.forward().cpu().numpy()
+        assert np.array_equal(again, got), "a plain step after pipelined ones differs"
         st = pipe.rowbags.exchange_stats()
         print(f"rank {rank} {mode}: remote parts per bag {st['remote_parts_per_bag']:.2f}, "
               f"NVLink bytes {st['nvlink_bytes']}, hot bytes {st['hot_bytes']}")
