@@ -72,6 +72,8 @@ def _load() -> C.CDLL:
     lib.annc_timer_destroy.argtypes = [C.c_void_p]
     lib.annc_timer_elapsed_ms.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
     lib.annc_embed_bag_set_timing_events.argtypes = [C.c_void_p, C.c_void_p]
+    lib.annc_embed_bag_set_stream_ctas_per_sm.argtypes = [C.c_int]
+    lib.annc_embed_bag_set_stream_ctas_per_sm.restype = None
     lib.annc_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
     lib.annc_peer_buffer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     lib.annc_peer_buffer_close.argtypes = [C.c_void_p]

@@ -30,6 +30,11 @@ static void launch_bag(const BagParams& p, BagHeader* hdr, int* offsets, cudaStr
   else bag_reduce_kernel<LANES, VPL, false><<<(unsigned)blocks, 256, 0, s>>>(p, hdr, offsets);
 }
 
+// Blocks per SM of the persistent lookup-granular kernel (0: as many as fit, -n: n fewer), per
+// calling thread: a caller that runs the kernel beside another gather-bound kernel of its own
+// (the pooling kernel of the row exchange on a second stream) splits the SMs' slots between them.
+static thread_local int t_stream_ctas_per_sm = 0;
+
 template <int LANES, int VW, int VPL, int TILES, int INFLIGHT, int MINB>
 static void launch_stream(const BagParams& p, BagHeader* hdr, cudaStream_t s) {
   static int per_sm[kMaxDevices] = {0};
@@ -53,7 +58,9 @@ static void launch_stream(const BagParams& p, BagHeader* hdr, cudaStream_t s) {
   sc.first[p.num_tables] = (int)total;
   // a persistent grid, no larger than the chunks there are
   const long long groups_per_block = (256 / 32) * (32 / LANES);
-  long long blocks = std::min<long long>((long long)sms * per_sm[slot], (total + groups_per_block - 1) / groups_per_block);
+  const int ctas = t_stream_ctas_per_sm > 0 ? std::min(t_stream_ctas_per_sm, per_sm[slot])
+                                            : std::max(1, per_sm[slot] + t_stream_ctas_per_sm);
+  long long blocks = std::min<long long>((long long)sms * ctas, (total + groups_per_block - 1) / groups_per_block);
   bag_stream_kernel<LANES, VW, VPL, TILES, INFLIGHT, MINB><<<(unsigned)std::max<long long>(blocks, 1), 256, 0, s>>>(p, sc, hdr);
 }
 
@@ -247,6 +254,8 @@ size_t annc_embed_bag_workspace_bytes(int num_tables, int64_t batch) {
   size_t off = (size_t)num_tables * (size_t)(batch + 1) * sizeof(int);
   return kHeaderBytes + ((off + 255) & ~size_t(255));
 }
+
+void annc_embed_bag_set_stream_ctas_per_sm(int ctas_per_sm) { t_stream_ctas_per_sm = ctas_per_sm; }
 
 int annc_embed_bags_dev(const annc_bag_table* tables, int num_tables, int64_t dim, int id_kind,
                         int64_t ncols, int32_t col, int combiner, int64_t batch,

@@ -12,9 +12,10 @@
 #include "row_exchange_kernels.cuh"
 
 extern "C" int annc_sum_partials_masked_slot_major_dev(const float* src, const uint32_t* mask, int parts,
-                                            int64_t part_stride, int64_t rows, int slots,
-                                            int64_t slot_width, const int32_t* mean_offsets, void* out,
-                                            int64_t out_stride, int out_bf16, void* stream);
+                                                       int64_t part_stride, int64_t rows, int slots,
+                                                       int64_t slot_width, const int32_t* mean_offsets,
+                                                       const int32_t* out_slots, void* out,
+                                                       int64_t out_stride, int out_bf16, void* stream);
 extern "C" size_t annc_embed_bag_workspace_bytes(int num_tables, int64_t batch);
 extern "C" int annc_embed_bag_prepass_dev(const annc_bag_table* tables, int num_tables, int64_t ncols,
                                           int32_t col, int64_t batch, void* workspace,
@@ -80,6 +81,9 @@ struct Exchange {
   long long begun = 0, pooled = 0, finished = 0;  // steps that passed each phase
   unsigned long long limit_ns = 2000000000ull;
   int pool_ctas_per_sm = 0;  // 0: as many as fit; -n: n fewer
+  int* out_slots = nullptr;  // device i32[T]: output slot of every table
+  std::vector<int32_t> out_slots_host;
+  bool out_slots_set = false;
   bool profiling = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   bool ev_valid = false;
@@ -139,6 +143,7 @@ static void destroy(Exchange* x) {
   cudaFree(x->mask[0]);
   cudaFree(x->mask[1]);
   cudaFree(x->meta);
+  cudaFree(x->out_slots);
   cudaFree(x->err);
   cudaFree(x->offsets_ws[0]);
   cudaFree(x->offsets_ws[1]);
@@ -216,6 +221,7 @@ int annc_row_exchange_create(const annc_row_exchange_config* c, void* const* pee
   alloc((void**)&x->mask[0], (size_t)x->T * (size_t)x->batch * sizeof(unsigned));
   alloc((void**)&x->mask[1], (size_t)x->T * (size_t)x->batch * sizeof(unsigned));
   alloc((void**)&x->meta, 2 * kMaxWorld * sizeof(int));
+  alloc((void**)&x->out_slots, (size_t)std::max(1, x->T) * sizeof(int));
   alloc((void**)&x->err, 256);
   if (c->combiner == 1) {
     x->offsets_ws_bytes = annc_embed_bag_workspace_bytes(x->T, x->batch);
@@ -308,6 +314,23 @@ int annc_row_exchange_destroy(annc_row_exchange* ex) {
 int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms) {
   ANNC_REQUIRE(ex && ms >= 1, ANNC_ERR_INVALID_ARGUMENT, "row exchange: bad timeout");
   reinterpret_cast<Exchange*>(ex)->limit_ns = (unsigned long long)ms * 1000000ull;
+  return ANNC_OK;
+}
+
+int annc_row_exchange_set_output_slots(annc_row_exchange* ex, const int32_t* slots, void* stream) {
+  auto* x = reinterpret_cast<Exchange*>(ex);
+  ANNC_REQUIRE(x, ANNC_ERR_INVALID_ARGUMENT, "row exchange: null object");
+  if (!slots) {
+    x->out_slots_set = false;
+    return ANNC_OK;
+  }
+  for (int t = 0; t < x->T; ++t)
+    ANNC_REQUIRE(slots[t] >= 0, ANNC_ERR_INVALID_ARGUMENT, "row exchange: negative output slot");
+  // staged through an owned host copy: the caller's array need not outlive the call
+  x->out_slots_host.assign(slots, slots + x->T);
+  ANNC_CUDA(cudaMemcpyAsync(x->out_slots, x->out_slots_host.data(), sizeof(int32_t) * (size_t)x->T,
+                            cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  x->out_slots_set = true;
   return ANNC_OK;
 }
 
@@ -426,8 +449,10 @@ int annc_row_exchange_finish(annc_row_exchange* ex, void* out, int64_t out_strid
                                 ? reinterpret_cast<const int32_t*>(static_cast<char*>(x->offsets_ws[buf]) + 512)  // header of the bag workspace
                                 : nullptr;
   x->finished += 1;
-  ANNC_TRY(annc_sum_partials_masked_slot_major_dev(recv, x->mask[buf], x->world, (int64_t)x->lay.slab_floats, x->batch,
-                                        x->T, x->dim, mean_off, out, out_stride, out_bf16, s));
+  ANNC_TRY(annc_sum_partials_masked_slot_major_dev(recv, x->mask[buf], x->world, (int64_t)x->lay.slab_floats,
+                                                   x->batch, x->T, x->dim, mean_off,
+                                                   x->out_slots_set ? x->out_slots : nullptr, out, out_stride,
+                                                   out_bf16, s));
   if (prof) {
     cudaEventRecord(x->ev[5], s);
     x->ev_valid = true;

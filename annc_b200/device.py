@@ -24,14 +24,15 @@ class BagPlan:
     def __init__(self, tables: Sequence[torch.Tensor], ids: Sequence[torch.Tensor],
                  slice_inputs: Sequence[torch.Tensor], out: torch.Tensor, out_slot0: int,
                  batch: int, id_kind: int = 2, col: int = 0, combiner: int = 0,
-                 num_buckets: Optional[Sequence[int]] = None):
+                 num_buckets: Optional[Sequence[int]] = None,
+                 out_slots: Optional[Sequence[int]] = None):
         self.n = len(tables)
         self.dim = int(tables[0].shape[1])
         self.batch = int(batch)
         self.id_kind, self.col, self.combiner = id_kind, col, combiner
         self.ncols = int(slice_inputs[0].shape[1])
         self.out = out
-        # out is [batch, slots, dim]; table t writes slot out_slot0 + t
+        # out is [batch, slots, dim]; table t writes slot out_slot0 + t (or out_slot0 + out_slots[t])
         slots = int(out.shape[1]) if out.dim() == 3 else 1
         self.out_stride = slots * self.dim
         self.keep = (list(tables), list(ids), list(slice_inputs))
@@ -45,7 +46,7 @@ class BagPlan:
             d.ids = ids[t].data_ptr()
             d.slice_input = slice_inputs[t].data_ptr()
             d.nnz = int(ids[t].shape[0])
-            d.out = out.data_ptr() + (out_slot0 + t) * self.dim * esz
+            d.out = out.data_ptr() + (out_slot0 + (out_slots[t] if out_slots is not None else t)) * self.dim * esz
         self.ws_bytes = int(lib.annc_embed_bag_workspace_bytes(self.n, self.batch))
         self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=out.device)
 

@@ -149,6 +149,10 @@ class DlrmPipeline:
         """embed() without its closing pass (pipelines with split_finish)."""
         self.embed()
 
+    def embed_side(self) -> None:
+        """Part of the embedding work that forward_pipelined(split=True) may run on the side
+        stream, beside embed_pool() on the current stream (nothing by default)."""
+
     def embed_finish(self) -> None:
         """The closing pass of embed(): completes z.  May run on another stream than embed_pool."""
 
@@ -230,6 +234,7 @@ class DlrmPipeline:
                                       activation=ACT_RELU, ldc=(F * D if last else None),
                                       math=self.math))
                 x = y
+            self.embed_side()                   # embedding work that needs no peer (writes z too)
             self._bottom_done[buf].record(self.side_stream)
             # the next step's split reuses the masks and lists of the step before this one
             self.side_stream.wait_event(self._sum_done[1 - buf])

@@ -42,6 +42,7 @@ lib.annc_row_exchange_clear_errors.argtypes = [C.c_void_p, C.c_void_p]
 lib.annc_row_exchange_set_timeout_ms.argtypes = [C.c_void_p, C.c_int64]
 lib.annc_row_exchange_set_profiling.argtypes = [C.c_void_p, C.c_int]
 lib.annc_row_exchange_set_pool_ctas_per_sm.argtypes = [C.c_void_p, C.c_int]
+lib.annc_row_exchange_set_output_slots.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
 lib.annc_row_exchange_phase_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
 lib.annc_row_exchange_stats.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
 
@@ -121,6 +122,14 @@ class RowExchange:
 
     def set_timeout_ms(self, ms: int) -> None:
         check(lib.annc_row_exchange_set_timeout_ms(self.h, C.c_int64(ms)))
+
+    def set_output_slots(self, slots) -> None:
+        """Table t of the exchange goes to slot slots[t] of the output rows (None: identity)."""
+        if slots is None:
+            check(lib.annc_row_exchange_set_output_slots(self.h, None, _stream()))
+            return
+        arr = (C.c_int32 * len(slots))(*[int(v) for v in slots])
+        check(lib.annc_row_exchange_set_output_slots(self.h, arr, _stream()))
 
     def set_pool_ctas_per_sm(self, n: int) -> None:
         check(lib.annc_row_exchange_set_pool_ctas_per_sm(self.h, C.c_int(int(n))))

@@ -26,7 +26,7 @@ ShardPlan is pure numpy so that the partitioning logic is testable on CPU ranks.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import numpy as np
 
@@ -115,7 +115,11 @@ class RowShardedBags:
     None = no hot rows."""
 
     def __init__(self, world: int, rank: int, device, local_tables, local_rows, table_rows, batch: int,
-                 dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2, hot=None):
+                 dim: int, nnz_all, id_sets, combiner: int = 0, id_kind: int = 2, hot=None,
+                 out_slots=None, bags_per_sample: Optional[int] = None):
+        """out_slots: table t of the exchange is written to slot out_slots[t] of the output rows
+        (the caller pools other tables into the remaining slots itself); bags_per_sample: the
+        number of tables of the whole model, for the per-bag figures of exchange_stats()."""
         import torch
         import torch.distributed as dist
 
@@ -142,6 +146,9 @@ class RowShardedBags:
                                    combiner=combiner, id_kind=id_kind)
         self.peer = dev.PeerBuffers(rx.peer_bytes(cfg), world, rank)
         self.ex = rx.RowExchange(cfg, keep, self.peer.ptrs)
+        if out_slots is not None:
+            self.ex.set_output_slots(out_slots)
+        self.bags_per_sample = int(bags_per_sample) if bags_per_sample else T
         if world > 1:
             dist.barrier()  # every rank's flags are cleared before anybody's first step
         self.inputs = [rx.StepInputs([x.data_ptr() for x in st["ids"]], [x.data_ptr() for x in st["segs"]],
@@ -201,7 +208,8 @@ class RowShardedBags:
         remote_parts = sum(p for q, p in enumerate(parts) if q != self.rank)
         self.exchange_bytes = remote_recs * 8 + remote_parts * self.D * 4
         return dict(records_per_source=recs, parts_per_owner=parts, remote_records=remote_recs,
-                    remote_parts_received=remote_parts, remote_parts_per_bag=remote_parts / (self.B * self.T),
+                    remote_parts_received=remote_parts,
+                    remote_parts_per_bag=remote_parts / (self.B * self.bags_per_sample),
                     nvlink_bytes=self.exchange_bytes, hot_bytes=self.hot_bytes)
 
     def error_bits(self) -> int:
@@ -332,7 +340,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
     import torch.distributed as dist
 
     from . import device as dev
-    from ._lib import MATH_AUTO
+    from ._lib import MATH_AUTO, lib
     from .dlrm import DlrmPipeline
 
     world, rank = dist.get_world_size(), dist.get_rank()
@@ -430,18 +438,39 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             emb = m.emb
             # Per table: this rank's shard, then the replicated hot set behind it: the rows of
             # the table's most popular ids (its own popularity map, identical on every rank).
+            # A table with no more rows than the replicated set is replicated whole: it stays
+            # out of the exchange altogether (no split, no parts, no sum) and is pooled by the
+            # one-GPU kernel straight into its slots of z.  The exchange takes the other tables.
+            whole = [t for t in range(self.T) if 0 < emb.tables[t].shape[0] <= hot_rows]
+            part = [t for t in range(self.T) if t not in whole]
+            if not part:  # nothing left to shard: keep every table in the exchange
+                whole, part = [], list(range(self.T))
+            self.whole_tables, self.part_tables = whole, part
             self.tables, hot = [], []
-            for t, (tab, bag) in enumerate(zip(emb.tables, emb.bags)):
+            for t in part:
+                tab, bag = emb.tables[t], emb.bags[t]
                 rows_t = tab.shape[0]
                 hr = bag.popular_rows(hot_rows, rows_t) if hot_rows > 0 else np.zeros(0, np.int64)
                 self.tables.append(self._up(np.concatenate([plan.local_shard(tab), tab[hr]])))
                 hot.append((int(hr.shape[0]), self._up(hr) if 0 < hr.shape[0] < rows_t else None))
             self.rowbags = RowShardedBags(
-                world, rank, self.device, self.tables, [plan.local_rows(t) for t in range(self.T)],
-                plan.table_rows, self.batch, self.dim, plan.nnz,
-                [dict(ids=st["ids"], segs=st["segs"]) for st in self.sets], combiner=0, hot=hot)
+                world, rank, self.device, self.tables, [plan.local_rows(t) for t in part],
+                [plan.table_rows[t] for t in part], self.batch, self.dim, plan.nnz[:, part],
+                [dict(ids=[st["ids"][t] for t in part], segs=[st["segs"][t] for t in part])
+                 for st in self.sets], combiner=0, hot=hot,
+                out_slots=part if whole else None, bags_per_sample=self.T)
+            self.whole_bytes = 0
+            self.whole_on_side = 0
+            if whole:
+                self.tables_whole = [self._up(emb.tables[t]) for t in whole]
+                self.whole_bytes = int(sum(x.numel() * 4 for x in self.tables_whole))
+                for st in self.sets:
+                    st["whole_plans"] = [dev.BagPlan(self.tables_whole, [st["ids"][t] for t in whole],
+                                                     [st["segs"][t] for t in whole], b["z"], 1, self.batch,
+                                                     id_kind=2, col=0, combiner=0, out_slots=whole)
+                                         for b in self._bufs]
             self.peer = self.rowbags.peer
-            self.embed_launches = self.rowbags.launches_per_step
+            self.embed_launches = self.rowbags.launches_per_step + (3 if whole else 0)
             self.exchange_bytes = 0
             self.split_finish = True  # forward_pipelined may run the sum of the parts on the dense stream
 
@@ -451,6 +480,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "replica":
                 return DlrmPipeline.embed(self)
             if mode == "row":
+                self._pool_whole_tables()
                 self.rowbags.run(self.cur, self.z.data_ptr() + D * 4, F * D)
                 return
             if mode == "row_nccl":
@@ -487,11 +517,32 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
                                   self.back.data_ptr() + off * 4, tp * D, tp * D, B)
                 off += self.back_counts[p]
 
+        def _pool_whole_tables(self) -> None:
+            """The tables replicated whole, by the one-GPU kernel, before the exchange's pooling
+            (it runs while the peers' lists are still on their way)."""
+            plans = self.sets[self.cur].get("whole_plans")
+            if plans:
+                plans[self._buf].run()
+
         def embed_pool(self) -> None:
             if mode == "row":
+                if not self.whole_on_side:
+                    self._pool_whole_tables()
                 self.rowbags.run_pool(self.cur)
             else:
                 self.embed()
+
+        def embed_side(self) -> None:
+            """With whole_on_side = k > 0: the tables replicated whole are pooled on the side
+            stream with k blocks per SM, beside the exchange's pooling kernel on the main stream
+            (which is bound by its NVLink stores from four GPUs on and should be given k blocks
+            per SM fewer: RowExchange.set_pool_ctas_per_sm(-k))."""
+            if mode == "row" and self.whole_on_side:
+                lib.annc_embed_bag_set_stream_ctas_per_sm(int(self.whole_on_side))
+                try:
+                    self._pool_whole_tables()
+                finally:
+                    lib.annc_embed_bag_set_stream_ctas_per_sm(0)
 
         def embed_finish(self) -> None:
             if mode == "row":
@@ -524,7 +575,11 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             if mode == "replica":
                 return DlrmPipeline.embed_error_bits(self)
             if mode == "row":
-                return self.rowbags.error_bits()
+                bits = self.rowbags.error_bits()
+                for st in self.sets:
+                    for p in st.get("whole_plans", []):
+                        bits |= p.error_bits()
+                return bits
             if mode == "table":
                 return self.tbags.error_bits()
             return self.launch.error_bits() if self.launch is not None else 0

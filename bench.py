@@ -85,7 +85,8 @@ def parallelism_label(args, world, mode=None):
     mode = mode or args.shard
     if world == 1 and args.workload == "dlrm":
         return "single"
-    hot = (" + rows of each table's %d most popular ids replicated" % args.hot_rows) if args.hot_rows > 0 else ""
+    hot = (" + rows of each table's %d most popular ids replicated (a table with no more rows than that is "
+           "replicated whole and pooled outside the exchange)" % args.hot_rows) if args.hot_rows > 0 else ""
     return {
         "row": "dp%d MLP + row-sharded tables (owner = row %% %d)%s; lookups split by owner at their source, "
                "partial sums stored into the sample owner's memory by the pooling kernel, flag barriers"
@@ -476,10 +477,17 @@ def run_gpu(args):
             cands += [("sum_and_dense_part_under_next_pooling", fs, 0),
                       ("sum_and_dense_part_under_next_pooling_grid_minus_1", fs, -1),
                       ("sum_and_dense_part_under_next_pooling_grid_minus_2", fs, -2)]
+        if getattr(pipe, "whole_tables", None) and rowex is not None:
+            # the tables replicated whole pooled on the side stream with k blocks per SM, the
+            # exchange's pooling kernel with k fewer
+            cands += [("sum_and_dense_part_under_next_pooling_whole_tables_beside_it_%d_blocks" % k, fs, -k)
+                      for k in (2, 3)]
         best, order_ms = None, {}
         for name, fn, ctas in cands:
             if rowex is not None:
                 rowex.set_pool_ctas_per_sm(ctas)
+            if hasattr(pipe, "whole_on_side"):
+                pipe.whole_on_side = -ctas if "whole_tables_beside" in name else 0
             for _ in range(3):
                 fn()
             t = timed(fn, 5, pipe.sync_pipeline)
@@ -489,6 +497,8 @@ def run_gpu(args):
         _, issue_order, step_fn, ctas = best
         if rowex is not None:
             rowex.set_pool_ctas_per_sm(ctas)
+        if hasattr(pipe, "whole_on_side"):
+            pipe.whole_on_side = -ctas if "whole_tables_beside" in issue_order else 0
 
     def step_with_hooks():
         a, b = next(it)
@@ -510,6 +520,8 @@ def run_gpu(args):
         lib.annc_timer_destroy(a)
         lib.annc_timer_destroy(b)
     ms_step = ms_total / args.steps
+    if getattr(getattr(pipe, "rowbags", None), "ex", None) is not None:
+        pipe.rowbags.ex.set_pool_ctas_per_sm(0)  # the single steps below use the whole grid
     assert pipe.embed_error_bits() == 0, "embedding kernels flagged an error in the timed steps"
     # one step alone, nothing of a neighbouring step under it (latency rather than throughput)
     ms_alone = timed(pipe.forward, args.steps) / args.steps
@@ -562,7 +574,9 @@ def run_gpu(args):
             "phases": list(PHASES),
             "phase_ms_per_rank": [[round(v, 4) for v in x[:5]] for x in allr],
             "phase_ms_max_over_ranks": [round(max(x[i] for x in allr), 4) for i in range(5)],
-            "hot_rows_per_table": args.hot_rows, "hot_bytes_per_gpu": st["hot_bytes"],
+            "hot_rows_per_table": args.hot_rows,
+            "tables_replicated_whole": len(getattr(pipe, "whole_tables", [])),
+            "hot_bytes_per_gpu": st["hot_bytes"] + getattr(pipe, "whole_bytes", 0),
             "remote_parts_per_bag": st["remote_parts_per_bag"],
             "nvlink_bytes_per_gpu_per_step": nv_bytes,
             "nvlink_gbs_in_pool_kernel": nv_bytes / (pool_ms / 1e3) / 1e9 if pool_ms > 0 else None,
@@ -660,7 +674,7 @@ def run_gpu(args):
                 st = rb.exchange_stats()
                 rec["remote_parts_per_bag"] = st["remote_parts_per_bag"]
                 rec["nvlink_bytes_per_gpu_per_step"] = st["nvlink_bytes"]
-                rec["hot_bytes_per_gpu"] = st["hot_bytes"]
+                rec["hot_bytes_per_gpu"] = st["hot_bytes"] + getattr(p2, "whole_bytes", 0)
             extras[mode] = rec
             close(p2)
             del p2

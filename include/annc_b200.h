@@ -316,11 +316,14 @@ int annc_sum_partials_masked_dev(const float* src, const uint32_t* mask, int par
                                  const int32_t* mean_offsets, void* out, int64_t out_stride,
                                  int out_bf16, void* stream);
 /* The same with every part laid out f32[slots, rows, slot_width] (the receive slabs of
- * annc_row_exchange_*: a part's place follows its key = slot * rows + r). */
+ * annc_row_exchange_*: a part's place follows its key = slot * rows + r).  out_slots (device
+ * i32[slots], or NULL for the identity) names the slot of the output row that slot t of the
+ * parts is written to: the output may hold more slots than the parts. */
 int annc_sum_partials_masked_slot_major_dev(const float* src, const uint32_t* mask, int parts,
                                             int64_t part_stride, int64_t rows, int slots,
-                                            int64_t slot_width, const int32_t* mean_offsets, void* out,
-                                            int64_t out_stride, int out_bf16, void* stream);
+                                            int64_t slot_width, const int32_t* mean_offsets,
+                                            const int32_t* out_slots, void* out, int64_t out_stride,
+                                            int out_bf16, void* stream);
 
 /* out[r, 0:width] = sum over p < parts of src[p][r, 0:width], added in ascending p (the
  * reduce step after the all-to-all of partial sums).  src part p starts at
@@ -429,6 +432,12 @@ int annc_row_exchange_step(annc_row_exchange* ex, const annc_bag_table* inputs, 
 int annc_row_exchange_check(annc_row_exchange* ex, void* stream, int* error_bits);
 int annc_row_exchange_clear_errors(annc_row_exchange* ex, void* stream);
 int annc_row_exchange_set_timeout_ms(annc_row_exchange* ex, int64_t ms);
+/* Output slots: table t of the exchange is written to out[:, slots[t], :] by finish (host
+ * array of num_tables ints, ascending or not; NULL restores the identity).  For a caller that
+ * keeps some tables outside the exchange (small tables replicated whole and pooled by
+ * annc_embed_bags_dev straight into the same output rows).  Synchronises nothing; the map is
+ * read by the finish calls issued after it. */
+int annc_row_exchange_set_output_slots(annc_row_exchange* ex, const int32_t* slots, void* stream);
 /* Blocks of the pooling kernel per SM (a persistent grid; 0 = as many as fit, the default;
  * -n = n fewer than fit).
  * With several GPUs the kernel is bound by its NVLink stores, and one block per SM fewer leaves
@@ -487,6 +496,11 @@ void* annc_timer_create(void);
 void annc_timer_destroy(void* event);
 int annc_timer_elapsed_ms(void* start, void* stop, float* ms);
 void annc_embed_bag_set_timing_events(void* start, void* stop);
+/* Blocks per SM of the persistent lookup-granular bag kernel for the calls of this thread
+ * (0 = as many as fit, the default; n > 0 = at most n; -n = n fewer than fit).  For a caller
+ * that runs annc_embed_bags_dev on one stream beside another kernel of its own on a second
+ * stream and wants both resident (see annc_row_exchange_set_pool_ctas_per_sm). */
+void annc_embed_bag_set_stream_ctas_per_sm(int ctas_per_sm);
 
 /* GEMM core: C = act(alpha * op(A) * op(B) + beta * C + addend + bias), row-major. */
 enum { ANNC_ACT_NONE = 0, ANNC_ACT_RELU = 1, ANNC_ACT_SIGMOID = 2 };

@@ -23,9 +23,14 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     model = synth.dlrm_model(seed=5, batch=2048, tables=7, max_rows=2e5, input_seed=100 + rank)
-    # "row_hot": row sharding with the rows of each table's 300 most popular ids replicated
-    hot = 300 if mode == "row_hot" else 0
-    pipe = ShardedDlrmPipeline(model, dev, "row" if mode == "row_hot" else mode, hot_rows=hot)
+    # "row_hot": row sharding with the rows of each table's 300 most popular ids replicated;
+    # "row_whole": 20000 replicated rows, which is all of the smaller tables: those stay out of
+    # the exchange and are pooled by the one-GPU kernel into their own slots of z
+    hot = {"row_hot": 300, "row_whole": 20000}.get(mode, 0)
+    pipe = ShardedDlrmPipeline(model, dev, "row" if mode.startswith("row_") and hot else mode, hot_rows=hot)
+    if mode == "row_whole":
+        assert pipe.whole_tables and pipe.part_tables, (pipe.whole_tables, pipe.part_tables)
+    mode = "row_hot" if mode == "row_whole" else mode
     got = pipe.forward().cpu().numpy()
     assert pipe.embed_error_bits() == 0
     if mode in ("row", "row_hot", "table"):
@@ -37,8 +42,10 @@ def main():
         # the issue orders for back-to-back batches: dense part under the next embedding part,
         # then also the sum of the parts on the dense stream (pooling kernels back to back on
         # the main stream, with and without a block per SM left free); same predictions
-        for split, ctas in ((False, 0), (True, 0), (True, -1), (False, 0)):
+        for split, ctas, side in ((False, 0, 0), (True, 0, 0), (True, -1, 0), (True, -2, 2), (False, 0, 0)):
             pipe.rowbags.ex.set_pool_ctas_per_sm(ctas)
+            # side: the tables replicated whole pooled on the side stream beside the exchange
+            pipe.whole_on_side = side if pipe.whole_tables else 0
             outs = []
             for _ in range(5):
                 outs.append(pipe.forward_pipelined(split=split))
@@ -48,6 +55,7 @@ def main():
                 assert np.array_equal(o.cpu().numpy(), got), f"pipelined steps (split={split}) differ"
             assert pipe.embed_error_bits() == 0
         pipe.rowbags.ex.set_pool_ctas_per_sm(0)
+        pipe.whole_on_side = 0
         again = pipe.forward().cpu().numpy()
         assert np.array_equal(again, got), "a plain step after pipelined ones differs"
         st = pipe.rowbags.exchange_stats()

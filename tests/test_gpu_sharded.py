@@ -12,7 +12,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("mode", ["row", "row_hot", "row_nccl", "table", "table_nccl", "replica"])
+@pytest.mark.parametrize("mode", ["row", "row_hot", "row_whole", "row_nccl", "table", "table_nccl", "replica"])
 def test_sharded_pipeline_matches_oracle(mode):
     n = torch.cuda.device_count()
     if n < 2:
