@@ -435,7 +435,7 @@ def run_gpu(args):
                                  input_seed=(1000 + rank) if world > 1 else None)
         emb_bytes = model.emb.algorithmic_bytes()
         nnz = model.emb.nnz
-        bag_kernel = "bag_stream_kernel<16,4,1,8,4,5> (hash-bucket + gather + segment sum, 26 tables in one launch)"
+        bag_kernel = "bag_stream_kernel<8,4,2,16,2,5> (hash-bucket + gather + segment sum, 26 tables in one launch)"
 
         def build(mode):
             if world == 1:
@@ -482,12 +482,14 @@ def run_gpu(args):
             # exchange's pooling kernel with k fewer
             cands += [("sum_and_dense_part_under_next_pooling_whole_tables_beside_it_%d_blocks" % k, fs, -k)
                       for k in (2, 3)]
+            # the same with one block slot per SM left free for the split and the sum
+            cands += [("sum_and_dense_part_under_next_pooling_whole_tables_beside_it_2_blocks_pooling_2", fs, 2)]
         best, order_ms = None, {}
         for name, fn, ctas in cands:
             if rowex is not None:
                 rowex.set_pool_ctas_per_sm(ctas)
             if hasattr(pipe, "whole_on_side"):
-                pipe.whole_on_side = -ctas if "whole_tables_beside" in name else 0
+                pipe.whole_on_side = (-ctas if ctas < 0 else 2) if "whole_tables_beside" in name else 0
             for _ in range(3):
                 fn()
             t = timed(fn, 5, pipe.sync_pipeline)
@@ -498,7 +500,7 @@ def run_gpu(args):
         if rowex is not None:
             rowex.set_pool_ctas_per_sm(ctas)
         if hasattr(pipe, "whole_on_side"):
-            pipe.whole_on_side = -ctas if "whole_tables_beside" in issue_order else 0
+            pipe.whole_on_side = (-ctas if ctas < 0 else 2) if "whole_tables_beside" in issue_order else 0
 
     def step_with_hooks():
         a, b = next(it)
