@@ -175,20 +175,26 @@ scatter_kernel(ClassifyParams p, const unsigned char* __restrict__ owner_in,
     long long prev = __shfl_up_sync(0xffffffffu, seg, 1);
     if (lane == 0) prev = (i > 0 && i < T.nnz) ? T.seg[(long long)(i - 1) * p.ncols + p.col] : -1;
     if (i < T.nnz && i > 0 && seg < prev) atomicOr(err, kErrUnsorted);
+    // the run of adjacent lanes that hold this lane's key (a bag's lookups are adjacent)
+    const int prev_key = __shfl_up_sync(0xffffffffu, key[j], 1);
+    const bool head = lane == 0 || key[j] != prev_key;
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    const unsigned le = (2u << lane) - 1u;  // lanes 0..lane
+    const int run_start = 31 - __clz(heads & le);
+    const unsigned above = heads & ~le;
+    const unsigned run = (above ? (1u << (__ffs(above) - 1)) - 1u : 0xffffffffu) & ~((1u << run_start) - 1u);
     int r = 0, cnt = 0;
+    unsigned bits = 0;
     for (int g = 0; g < p.world; ++g) {
       const unsigned m = __ballot_sync(0xffffffffu, owner[j] == g);
       if (owner[j] == g) r = __popc(m & ((1u << lane) - 1u));
       if (lane == g) cnt = __popc(m);
+      if (m & run) bits |= 1u << g;
     }
     rank_in_warp[j] = r;
     if (lane < kMaxWorld) wcnt[j * kWarps + warp][lane] = cnt;
-    // one atomicOr per (bag, warp): the lanes that hold the same key combine their owner bits
-    if (key[j] >= 0) {
-      const unsigned peers = __match_any_sync(__activemask(), key[j]);
-      const unsigned bits = __reduce_or_sync(peers, 1u << owner[j]);
-      if ((int)(__ffs(peers) - 1) == lane) atomicOr(mask + key[j], bits);
-    }
+    // one atomicOr per (bag, warp), by the first lane of the run, with the owners of the run
+    if (head && key[j] >= 0) atomicOr(mask + key[j], bits);
   }
   __syncthreads();
   if (threadIdx.x < p.world) {  // exclusive prefix over (tile, warp) in lookup order
