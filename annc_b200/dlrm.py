@@ -181,6 +181,8 @@ class DlrmPipeline:
                                       math=self.math))
                 x = y
             if lookahead:
+                # after a step issued with split=True the previous sum ran on the dense stream
+                self.side_stream.wait_event(self._sum_done[1 - self._buf])
                 self.embed_prefetch_next()
         self.embed()
         main.wait_stream(self.side_stream)
