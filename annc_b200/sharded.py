@@ -81,6 +81,17 @@ class ShardPlan:
         return int(sum(rc[:s]) + self.nnz[s, mine[:j]].sum())
 
 
+def whole_and_sharded_tables(table_rows, hot_rows: int):
+    """Tables of a row-sharded model that are replicated whole (no more rows than the replicated
+    set of `hot_rows` rows per table: they stay out of the exchange) and the tables that are
+    sharded.  When nothing would be left to shard, every table stays in the exchange."""
+    whole = [t for t, r in enumerate(table_rows) if 0 < int(r) <= int(hot_rows)]
+    part = [t for t in range(len(table_rows)) if t not in whole]
+    if not part:
+        return [], list(range(len(table_rows)))
+    return whole, part
+
+
 def partition_lookups(raw_ids, seg_ids, table_rows: int, shards: int, source: int = 0, hot_rows=None,
                       local_rows_of_source: int = 0):
     """Host statement of the split the row exchange makes for one table of one source rank
@@ -441,10 +452,7 @@ def _make_pipeline(model, device, mode: str, math=None, keep_host_inputs: bool =
             # A table with no more rows than the replicated set is replicated whole: it stays
             # out of the exchange altogether (no split, no parts, no sum) and is pooled by the
             # one-GPU kernel straight into its slots of z.  The exchange takes the other tables.
-            whole = [t for t in range(self.T) if 0 < emb.tables[t].shape[0] <= hot_rows]
-            part = [t for t in range(self.T) if t not in whole]
-            if not part:  # nothing left to shard: keep every table in the exchange
-                whole, part = [], list(range(self.T))
+            whole, part = whole_and_sharded_tables([t.shape[0] for t in emb.tables], hot_rows)
             self.whole_tables, self.part_tables = whole, part
             self.tables, hot = [], []
             for t in part:

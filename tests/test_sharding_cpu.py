@@ -129,6 +129,18 @@ def test_local_rows_rule():
             assert tot == rows
 
 
+def test_tables_replicated_whole_stay_out_of_the_exchange():
+    from annc_b200.sharded import whole_and_sharded_tables
+    rows = [1000, 65536, 65537, 10_000_000, 5]
+    assert whole_and_sharded_tables(rows, 0) == ([], [0, 1, 2, 3, 4])          # no replicated rows at all
+    assert whole_and_sharded_tables(rows, 65536) == ([0, 1, 4], [2, 3])        # up to and including K rows
+    assert whole_and_sharded_tables(rows, 999) == ([4], [0, 1, 2, 3])
+    # nothing left to shard: every table stays in the exchange (which then replicates them all)
+    assert whole_and_sharded_tables([10, 20], 100) == ([], [0, 1])
+    whole, part = whole_and_sharded_tables(rows, 70000)
+    assert sorted(whole + part) == list(range(len(rows))) and not set(whole) & set(part)
+
+
 # ---------------------------------------------------------------- partition-at-source protocol
 
 def _worker_partitioned(rank, world, port, q):
