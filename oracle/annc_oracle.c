@@ -15,9 +15,13 @@
  * Pinning: the E3/E4/E5/E6/G9 functions are checked against the literal
  * known-answer tensors of the reference's own unit tests
  * (the _test.cc files under annc/tensorflow/kernels) in tests/test_oracle_golden.py.
- * The GEMM custom calls, __pooling, softmax, argmax and the hash-bucket
- * ops have no test in the reference: parity unpinned for those; they
- * follow the cited source text.
+ * The GEMM custom calls, __pooling, __reduce_mean and the sequential
+ * KernelSelector GEMM / batch / GEMV / ArgMax3D symbols are checked against
+ * the reference's own function bodies, cut from the reference tree and
+ * compiled beside this file (xla_ref_shim.cc, tests/test_oracle_xla_ref.py).
+ * Softmax, the kn4 GEMM's kp_sgemm, the hash-bucket ops and sparse_embedding2
+ * have no test in the reference and bodies that cannot be compiled here:
+ * parity unpinned for those; they follow the cited source text.
  */
 #include <math.h>
 #include <stdint.h>

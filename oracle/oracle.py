@@ -480,6 +480,8 @@ def xla_ref() -> C.CDLL:
         l = C.CDLL(_XLA_REF_PATH)
         b = openblas()
         l.annc_xla_ref_set_blas(C.cast(b.scipy_cblas_sgemm, C.c_void_p), C.cast(b.scipy_cblas_sasum, C.c_void_p))
+        if hasattr(l, "annc_xla_ref_set_sgemv"):
+            l.annc_xla_ref_set_sgemv(C.cast(b.scipy_cblas_sgemv, C.c_void_p))
         _xla_ref = l
     return _xla_ref
 
@@ -496,6 +498,54 @@ def xla_ref_call(name: str, out: np.ndarray, operands) -> np.ndarray:
     arr = (C.c_void_p * len(keep))(*[C.c_void_p(o.ctypes.data) for o in keep])
     getattr(xla_ref(), "annc_ref_" + name)(C.c_void_p(out.ctypes.data), arr)
     return out
+
+
+def xla_ref_kernel_selector_available() -> bool:
+    return xla_ref_available() and hasattr(xla_ref(), "annc_ref_ks_gemm")
+
+
+def ks_ref_gemm(trA, trB, A, B, M, N, K, alpha=1.0, beta=0.0, Cin=None) -> np.ndarray:
+    """The reference's own __xla_cpu_runtime_KernelSelectorGEMMSequential
+    (annc/service/cpu/xla/kernel_selector.cc:31-43)."""
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    out = np.zeros((M, N), np.float32) if Cin is None else _c(Cin, np.float32).reshape(M, N).copy()
+    xla_ref().annc_ref_ks_gemm(C.c_int(int(trA)), C.c_int(int(trB)), _p(A, f32p), _p(B, f32p), C.c_int(M),
+                               C.c_int(N), C.c_int(K), C.c_float(alpha), C.c_float(beta), _p(out, f32p))
+    return out
+
+
+def ks_ref_batch(trA, trB, A, B, lead, M, N, K) -> np.ndarray:
+    """...KernelSelectorBatch3DSequential (lead = (P,)) or ...Batch4DSequential (lead = (Q, P))
+    (kernel_selector.cc:99-116, 234-251)."""
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    out = np.empty(tuple(lead) + (M, N), np.float32)
+    if len(lead) == 1:
+        xla_ref().annc_ref_ks_batch3d(C.c_int(int(trA)), C.c_int(int(trB)), _p(A, f32p), _p(B, f32p),
+                                      C.c_int(lead[0]), C.c_int(M), C.c_int(N), C.c_int(K), _p(out, f32p))
+    else:
+        xla_ref().annc_ref_ks_batch4d(C.c_int(int(trA)), C.c_int(int(trB)), _p(A, f32p), _p(B, f32p),
+                                      C.c_int(lead[0]), C.c_int(lead[1]), C.c_int(M), C.c_int(N), C.c_int(K),
+                                      _p(out, f32p))
+    return out
+
+
+def ks_ref_gemv(trA, A, X, M, N, alpha=1.0, beta=0.0, Y=None) -> np.ndarray:
+    """...KernelSelectorGEMV (kernel_selector.cc:168-178): cblas_sgemv with lda = trA ? M : N."""
+    A, X = _c(A, np.float32), _c(X, np.float32)
+    out = np.zeros(N if trA else M, np.float32) if Y is None else _c(Y, np.float32).copy()
+    xla_ref().annc_ref_ks_gemv(C.c_int(int(trA)), _p(A, f32p), _p(X, f32p), C.c_int(M), C.c_int(N),
+                               C.c_float(alpha), C.c_float(beta), _p(out, f32p))
+    return out
+
+
+def ks_ref_argmax3d(invals, inidxs, init_value, init_idx):
+    """...ArgMax3DSequential over f32/i32 [B, M, N] (kernel_selector.cc:317-339, 376-389)."""
+    v, ix = _c(invals, np.float32), _c(inidxs, np.int32)
+    Bn, M, N = v.shape
+    ov, oi = np.empty((Bn, M), np.float32), np.empty((Bn, M), np.int32)
+    xla_ref().annc_ref_ks_argmax3d(C.c_int(Bn), C.c_int(M), C.c_int(N), _p(v, f32p), _p(ix, i32p),
+                                   C.c_float(init_value), C.c_int32(init_idx), _p(ov, f32p), _p(oi, i32p))
+    return ov, oi
 
 
 # ---------------------------------------------------------------- ANNC_FLAGS (real reference)
