@@ -46,6 +46,14 @@ def test_library_exports_every_declared_symbol(annc):
         assert hasattr(annc.lib, n), f"missing export {n}"
 
 
+def test_header_is_plain_c():
+    """The boundary is a C ABI: the header must compile as C99 as well as C++ (a cgo / JNI / ctypes
+    binding generator reads it as C)."""
+    for cc, std, lang in (("gcc", "-std=c99", "c"), ("g++", "-std=c++17", "c++")):
+        r = subprocess.run([cc, std, "-fsyntax-only", "-Wall", "-x", lang, HEADER], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+
+
 def test_mangled_aliases_exported(annc):
     out = subprocess.run(["nm", "-D", "--defined-only", annc._lib.LIB_PATH], capture_output=True, text=True).stdout
     # names the reference's MLIR lowering calls (install/xla/matmul_lower.patch:65-68)
