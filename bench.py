@@ -585,6 +585,9 @@ def run_gpu(args):
             "nvlink_peak_gbs": 900.0, "nvlink_measured_peer_copy_gbs": 770.0,
             "limiting_kernel": "pool_kernel (pooling + peer stores)" if pool_ms >= max(x[0] for x in allr)
                                else "classify + scan + scatter",
+            "limiting_kernel_ms": round(max(pool_ms, max(x[0] for x in allr)), 4),
+            "nvlink_frac_of_nominal_in_pool_kernel": (nv_bytes / (pool_ms / 1e3) / 1e9 / 900.0) if pool_ms > 0 else None,
+            "note": "phase 'barrier1' also holds the pooling of the tables replicated whole (one-GPU kernel, no peer)",
         }
 
     roofline = None
