@@ -87,3 +87,47 @@ def test_dot_interaction(F, D, math, tol):
     got = out.cpu().numpy()
     np.testing.assert_array_equal(got[:, :D], z[:, 0, :])  # the copied row is never rounded
     assert np.abs(got - want).max() <= tol * np.abs(want).max()
+
+
+@pytest.mark.parametrize("use_map,bf16", [(False, False), (True, False), (True, True)])
+def test_masked_sum_of_slot_major_parts_with_output_slots(use_map, bf16):
+    """annc_sum_partials_masked_slot_major_dev: parts laid out [slots, rows, width] (a part's place
+    follows its key), summed in ascending part order where the mask names them, written to
+    out[r, out_slots[slot], :]; the slots of the output that no table maps to stay untouched."""
+    import ctypes as C
+    from annc_b200._lib import check, lib
+    lib.annc_sum_partials_masked_slot_major_dev.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_void_p, C.c_void_p,
+        C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    rng = np.random.default_rng(12)
+    parts, rows, slots, width, out_slots_n = 5, 300, 3, 16, 6
+    src = rng.standard_normal((parts, slots, rows, width)).astype(np.float32)
+    mask = rng.integers(0, 1 << parts, (slots, rows)).astype(np.uint32)
+    mask[0, :10] = 0                                   # bags nobody contributes to: zeros
+    slot_map = np.array([4, 0, 2], np.int32) if use_map else np.arange(slots, dtype=np.int32)
+    width_out = out_slots_n if use_map else slots
+    want = np.full((rows, width_out, width), 7.0, np.float32)
+    for s in range(slots):
+        for r in range(rows):
+            acc = None
+            for p in range(parts):                     # ascending part order, fp32 adds
+                if (mask[s, r] >> p) & 1:
+                    acc = src[p, s, r].copy() if acc is None else (acc + src[p, s, r]).astype(np.float32)
+            want[r, slot_map[s]] = 0.0 if acc is None else acc
+    dsrc = torch.from_numpy(src).cuda()
+    dmask = torch.from_numpy(mask.view(np.int32)).cuda()
+    dmap = torch.from_numpy(slot_map).cuda()
+    out = torch.full((rows, width_out, width), 7.0, device="cuda",
+                     dtype=torch.bfloat16 if bf16 else torch.float32)
+    check(lib.annc_sum_partials_masked_slot_major_dev(
+        C.c_void_p(dsrc.data_ptr()), C.c_void_p(dmask.data_ptr()), C.c_int(parts),
+        C.c_int64(slots * rows * width), C.c_int64(rows), C.c_int(slots), C.c_int64(width), None,
+        C.c_void_p(dmap.data_ptr()) if use_map else None, C.c_void_p(out.data_ptr()),
+        C.c_int64(width_out * width), C.c_int(int(bf16)), None))
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    if bf16:
+        ref = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+        assert np.array_equal(got, ref)
+    else:
+        assert np.array_equal(got, want)
